@@ -1,0 +1,118 @@
+/* mam_b200.h -- C ABI of the B200 (sm_100a) Multiply-And-Max/min library, libmam_b200.so.
+ *
+ * Plain C types only: device pointers, sizes, a CUDA stream passed as void*.  No entry point
+ * allocates or frees device memory; the caller owns every buffer, including the workspace whose
+ * size the *_workspace_bytes queries return.  Every entry point returns a mam_status code; text for
+ * it comes from mam_status_str().  All launches go to the stream given (0 = legacy default
+ * stream) on the device that is current for the calling thread.
+ *
+ * Each function names the interface of SSIGPRO/mamtorch it stands in for (path:line inside that
+ * project).  Layout notation: a[M,K] activations, row-major; the weight operand is either
+ * b[K,N] row-major (MAM_B_KN, what the torch ops receive) or W[N,K] row-major (MAM_B_NK, how
+ * nn.FullyConnected stores its parameter); y, grad, argmax, argmin are [M,N] row-major.
+ */
+#ifndef MAM_B200_H
+#define MAM_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MAM_ABI_VERSION 1
+
+enum mam_status {
+    MAM_OK = 0,
+    MAM_ERR_INVALID_ARGUMENT = 1, /* null pointer, non-positive extent, bad layout code          */
+    MAM_ERR_UNSUPPORTED = 2,      /* extent beyond what the kernels index (see each function)     */
+    MAM_ERR_WORKSPACE = 3,        /* workspace missing, too small or not 256-byte aligned         */
+    MAM_ERR_CUDA = 4,             /* a CUDA runtime/driver call failed; see mam_last_cuda_error() */
+    MAM_ERR_DEVICE_TIMEOUT = 5,   /* a bounded wait inside a kernel gave up (results invalid)     */
+    MAM_ERR_NOT_SM100 = 6         /* the current device is not compute capability 10.x            */
+};
+
+#define MAM_B_KN 0
+#define MAM_B_NK 1
+
+/* Text for a status code (static storage). */
+const char* mam_status_str(int status);
+/* MAM_ABI_VERSION the library was built with. */
+int mam_abi_version(void);
+/* cudaGetErrorString of the last CUDA error seen by this library on the calling thread. */
+const char* mam_last_cuda_error(void);
+/* Synchronises the device and returns MAM_ERR_DEVICE_TIMEOUT if any kernel of this library has
+ * recorded a wait that ran out since the flag was last cleared (it clears the flag). */
+int mam_check_device_flag(void);
+
+/* Selects the tile configuration of the tiled forward kernels: -1 (default) picks by shape,
+ * other values index mam_fwd_variant_name().  A tuning / benchmarking knob, process-wide. */
+int mam_set_fwd_variant(int with_indices, int variant);
+const char* mam_fwd_variant_name(int with_indices, int variant);
+
+/* Per-kernel timing without a profiler.  While armed, every launch of the kernel class `kernel_id`
+ * is bracketed by cudaEventRecord(starts[i]) / cudaEventRecord(stops[i]) on the launch stream,
+ * i = 0,1,... up to `capacity` (later launches are not timed).  The caller creates the events
+ * (cudaEvent_t passed as void*), synchronises, and reads cudaEventElapsedTime itself.
+ * mam_timer_disarm() returns how many pairs were recorded.  Process-wide; not thread-safe. */
+#define MAM_KERNEL_FWD_TILED 0   /* mam_fwd_tiled_kernel, the main forward loop       */
+#define MAM_KERNEL_FWD_RESOLVE 1 /* chunk id -> exact index                              */
+#define MAM_KERNEL_FWD_GENERIC 2 /* any-shape forward                                    */
+#define MAM_KERNEL_BWD 3         /* selected-pair scatter                                */
+#define MAM_KERNEL_SELCOUNT 4    /* selection hits                                       */
+int mam_timer_arm(void** starts, void** stops, int capacity, int kernel_id);
+int mam_timer_disarm(void);
+
+/* Workspace needed by mam_fwd_f32 for these extents (0 is possible). */
+size_t mam_fwd_workspace_bytes(int64_t M, int64_t K, int64_t N, int b_layout, int want_indices);
+
+/* MAM forward.
+ *   s[m,n] = max_k fl32(a[m,k]*b[k,n]) + min_k fl32(a[m,k]*b[k,n])
+ *   y[m,n] = s                                   if blend == 0
+ *          = alpha*s + beta*dense[m,n]           if blend != 0   (dense may be NULL: alpha*s)
+ *          (+ bias[n] when bias != NULL)
+ *   argmax/argmin: the k attaining max/min, lowest k on ties, int32.  Pass both NULL for the
+ *   values-only form.
+ * Stands in for fullyconnected_cuda (mamtorch/kernel/v1/csrc/cuda/fullyconnected.cu:177-291 and
+ * mamtorch/kernel/v4/csrc/cuda/fullyconnected.cu:41-149), fullyconnected_fast_cuda
+ * (mamtorch/kernel/v4/csrc/cuda/fullyconnected_fast.cu:39-137) and, through alpha/beta/bias/dense,
+ * the blend of the v2/v3 host code (mamtorch/kernel/v3/csrc/cuda/fullyconnected.cu:153-160).
+ * Limits: M*N < 2^31 * 64, K < 2^31; K == 0 is MAM_ERR_INVALID_ARGUMENT (a maximum over nothing). */
+int mam_fwd_f32(const float* a, const float* b, int b_layout,
+                const float* bias, const float* dense, int blend, float alpha, float beta,
+                float* y, int32_t* argmax, int32_t* argmin,
+                int64_t M, int64_t K, int64_t N,
+                void* workspace, size_t workspace_bytes, void* stream);
+
+/* MAM backward through the selected pairs.
+ *   da[m,k]  = scale * sum_n grad[m,n] * b[k,n] * ([k==argmax[m,n]] + [k==argmin[m,n]])
+ *   db (same layout as b) = scale * sum_m grad[m,n] * a[m,k] * (same selector)
+ * Both outputs are overwritten.  Stands in for fullyconnected_backward_cuda
+ * (mamtorch/kernel/v4/csrc/cuda/fullyconnected_backward.cu:80-135); scale carries the (1-beta)
+ * of the v2/v3 variant (mamtorch/kernel/v3/csrc/cuda/fullyconnected_backward.cu:138-145).
+ * Limit: K*4 bytes must fit the shared memory of one CTA (K <= 56000). */
+int mam_bwd_f32(const float* a, const float* b, int b_layout, const float* grad,
+                const int32_t* argmax, const int32_t* argmin,
+                float* da, float* db, float scale,
+                int64_t M, int64_t K, int64_t N, void* stream);
+
+/* Selection hits: hit_max[n,k] += #rows m with argmax[m,n]==k, hit_min likewise ([N,K] int32,
+ * accumulated into, so zero them first for per-call counts).  The device-side form of the
+ * bookkeeping in FullyConnected.update_selection_count (mamtorch/nn/v4/fullyconnected.py:114-131). */
+int mam_selcount_i32(const int32_t* argmax, const int32_t* argmin,
+                     int32_t* hit_max, int32_t* hit_min,
+                     int64_t M, int64_t K, int64_t N, void* stream);
+/* count[i] += (hit_max[i]>0) + (hit_min[i]>0): exactly what one update_selection_count() call of
+ * the reference adds to max_selection_count (mamtorch/nn/v4/fullyconnected.py:125-129). */
+int mam_selcount_indicator_i32(const int32_t* hit_max, const int32_t* hit_min,
+                               int32_t* count, int64_t n_elems, void* stream);
+
+/* out[C,R] = transpose(in[R,C]); replaces the .T.contiguous() copies of the reference's glue
+ * (mamtorch/nn/v4/fullyconnected.py:141, mamtorch/kernel/v4/csrc/cuda/fullyconnected.cu:66). */
+int mam_transpose_f32(const float* in, float* out, int64_t R, int64_t C, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MAM_B200_H */

@@ -1,0 +1,97 @@
+// Selected-pair backward of the MAM layer and the per-weight selection count.
+//
+// Replaces fullyconnected_backward_cuda_kernel of the reference
+// (mamtorch/kernel/v4/csrc/cuda/fullyconnected_backward.cu:23-78; identical in v1), which runs one
+// thread per 16x16 patch of outputs and issues four dependent global atomics per output.
+// Here a CTA owns a block of rows of a: it sweeps all N outputs of those rows with coalesced reads
+// of grad / argmax / argmin, accumulates the rows' da in shared memory (written out once, no
+// global atomics, no zero-fill pass) and sends the dW contributions to L2 with red.global.add.f32.
+// Sums are formed in a different order than the reference's, so gradients agree to rounding
+// (1e-5 relative in the tests), not bit for bit.
+#pragma once
+#include "mam_ptx.cuh"
+
+namespace mamb200 {
+
+constexpr int BWD_THREADS = 256;
+
+// B_NK: w is W[N,K] and dw has the same layout; otherwise b[K,N].
+template <bool B_NK>
+__global__ void __launch_bounds__(BWD_THREADS)
+mam_bwd_kernel(const float* __restrict__ a, const float* __restrict__ w, const float* __restrict__ g,
+               const int* __restrict__ argmax, const int* __restrict__ argmin,
+               float* __restrict__ da, float* __restrict__ dw,
+               long long M, long long K, long long N, int rows_per_cta, float scale) {
+    extern __shared__ float da_s[];  // [rows_per_cta][K]
+    const long long m0 = (long long)blockIdx.x * rows_per_cta;
+    const int rows = (int)min((long long)rows_per_cta, M - m0);
+    for (long long i = threadIdx.x; i < (long long)rows * K; i += BWD_THREADS) da_s[i] = 0.f;
+    __syncthreads();
+    for (int r = 0; r < rows; ++r) {
+        const long long m = m0 + r;
+        const float* arow = a + m * K;
+        float* dar = da_s + (long long)r * K;
+        for (long long n = threadIdx.x; n < N; n += BWD_THREADS) {
+            const float gv = __fmul_rn(g[m * N + n], scale);
+            int k1 = argmax[m * N + n], k2 = argmin[m * N + n];
+            // an index outside [0,K) cannot come from the forward; skip it rather than fault
+            const bool ok1 = (unsigned)k1 < (unsigned long long)K, ok2 = (unsigned)k2 < (unsigned long long)K;
+            if (ok1) {
+                const long long wi = B_NK ? n * K + k1 : (long long)k1 * N + n;
+                atomicAdd(&dar[k1], __fmul_rn(w[wi], gv));
+                atomicAdd(&dw[wi], __fmul_rn(arow[k1], gv));
+            }
+            if (ok2) {
+                const long long wi = B_NK ? n * K + k2 : (long long)k2 * N + n;
+                atomicAdd(&dar[k2], __fmul_rn(w[wi], gv));
+                atomicAdd(&dw[wi], __fmul_rn(arow[k2], gv));
+            }
+        }
+    }
+    __syncthreads();
+    for (long long i = threadIdx.x; i < (long long)rows * K; i += BWD_THREADS) da[m0 * K + i] = da_s[i];
+}
+
+// True selection counts: cnt_max[n,k] += #rows with argmax[m,n]==k, same for min.  A CTA owns
+// `cols` consecutive outputs n and keeps their [cols][K] int32 counters for max and for min in
+// shared memory (integer shared-memory atomics are an order of magnitude faster than fp32 ones),
+// sweeps all M rows, then adds the counters to the caller's [N,K] matrices.
+// The module-level rule of the reference (mamtorch/nn/v4/fullyconnected.py:114-131) is derived
+// from these on the host side: +1 where cnt_max>0, +1 where cnt_min>0.
+__global__ void __launch_bounds__(256)
+mam_selcount_kernel(const int* __restrict__ argmax, const int* __restrict__ argmin,
+                    int* __restrict__ cnt_max, int* __restrict__ cnt_min,
+                    long long M, long long K, long long N, int cols) {
+    extern __shared__ int cnt_s[];  // [2][cols][K]
+    const long long n0 = (long long)blockIdx.x * cols;
+    const int nc = (int)min((long long)cols, N - n0);
+    const long long tot = 2LL * cols * K;
+    for (long long i = threadIdx.x; i < tot; i += 256) cnt_s[i] = 0;
+    __syncthreads();
+    // threads: c = tid % nc fastest so that the nc consecutive ints of a row are read together
+    const long long work = M * nc;
+    for (long long t = threadIdx.x; t < work; t += 256) {
+        const long long m = t / nc;
+        const int c = (int)(t % nc);
+        const int k1 = argmax[m * N + n0 + c], k2 = argmin[m * N + n0 + c];
+        if ((unsigned)k1 < (unsigned long long)K) atomicAdd(&cnt_s[(long long)c * K + k1], 1);
+        if ((unsigned)k2 < (unsigned long long)K) atomicAdd(&cnt_s[((long long)cols + c) * K + k2], 1);
+    }
+    __syncthreads();
+    for (long long i = threadIdx.x; i < (long long)nc * K; i += 256) {
+        const int vmax = cnt_s[i], vmin = cnt_s[(long long)cols * K + i];
+        if (vmax) cnt_max[n0 * K + i] += vmax;
+        if (vmin) cnt_min[n0 * K + i] += vmin;
+    }
+}
+
+// count[n,k] += (hit_max[n,k] > 0) + (hit_min[n,k] > 0): one update_selection_count() call of the
+// reference module, which adds both indicators into max_selection_count
+// (mamtorch/nn/v4/fullyconnected.py:125-129).
+__global__ void mam_selcount_indicator_kernel(const int* __restrict__ hit_max, const int* __restrict__ hit_min,
+                                              int* __restrict__ count, long long n) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) count[i] += (hit_max[i] > 0) + (hit_min[i] > 0);
+}
+
+}  // namespace mamb200

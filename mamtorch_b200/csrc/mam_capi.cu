@@ -1,0 +1,361 @@
+// C ABI of libmam_b200.so: argument checking, path selection, tensor-map encoding and launches.
+// Declarations and the reference interfaces each entry point replaces are in include/mam_b200.h.
+#include <cstdio>
+#include <cstring>
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "../../include/mam_b200.h"
+#include "mam_bwd.cuh"
+#include "mam_fwd_generic.cuh"
+#include "mam_fwd_tiled.cuh"
+
+using namespace mamb200;
+
+namespace {
+
+thread_local cudaError_t t_last_cuda = cudaSuccess;
+__device__ int g_wait_gave_up = 0;  // set by kernels whose bounded wait ran out
+
+int cuda_fail(cudaError_t e) {
+    t_last_cuda = e;
+    return MAM_ERR_CUDA;
+}
+#define MAM_CUDA(x)                                  \
+    do {                                             \
+        cudaError_t e_ = (x);                        \
+        if (e_ != cudaSuccess) return cuda_fail(e_); \
+    } while (0)
+
+struct DevInfo {
+    int valid = 0, sms = 0, major = 0, minor = 0, max_smem = 0;
+};
+DevInfo g_dev[64];
+
+int device_info(const DevInfo** out) {
+    int dev = 0;
+    MAM_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return MAM_ERR_UNSUPPORTED;
+    DevInfo& d = g_dev[dev];
+    if (!d.valid) {
+        MAM_CUDA(cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev));
+        MAM_CUDA(cudaDeviceGetAttribute(&d.major, cudaDevAttrComputeCapabilityMajor, dev));
+        MAM_CUDA(cudaDeviceGetAttribute(&d.minor, cudaDevAttrComputeCapabilityMinor, dev));
+        MAM_CUDA(cudaDeviceGetAttribute(&d.max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+        d.valid = 1;
+    }
+    *out = &d;
+    return d.major == 10 ? MAM_OK : MAM_ERR_NOT_SM100;
+}
+
+// ---- optional per-kernel event timing (mam_timer_arm) ----
+struct KernelTimer {
+    void** starts = nullptr;
+    void** stops = nullptr;
+    int capacity = 0, count = 0, kernel_id = -1;
+} g_timer;
+
+struct TimedLaunch {
+    bool on;
+    cudaStream_t st;
+    TimedLaunch(int kernel_id, cudaStream_t s) : st(s) {
+        on = g_timer.kernel_id == kernel_id && g_timer.count < g_timer.capacity;
+        if (on) cudaEventRecord((cudaEvent_t)g_timer.starts[g_timer.count], st);
+    }
+    ~TimedLaunch() {
+        if (on) {
+            cudaEventRecord((cudaEvent_t)g_timer.stops[g_timer.count], st);
+            ++g_timer.count;
+        }
+    }
+};
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+
+int get_encode() {
+    if (g_encode) return MAM_OK;
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    MAM_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
+    if (q != cudaDriverEntryPointSuccess || !fn) return cuda_fail(cudaErrorNotSupported);
+    g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    return MAM_OK;
+}
+
+// [rows, K] fp32 row-major matrix -> boxes of [box_rows][32 floats], 128-byte swizzle, zero fill.
+int encode_rows_k(CUtensorMap* tm, const float* base, long long rows, long long K, int box_rows) {
+    int st = get_encode();
+    if (st != MAM_OK) return st;
+    cuuint64_t gdim[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t gstr[1] = {(cuuint64_t)K * 4};
+    cuuint32_t box[2] = {(cuuint32_t)FWD_BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = g_encode(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), gdim, gstr, box,
+                          estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return cuda_fail(cudaErrorInvalidValue);
+    return MAM_OK;
+}
+
+template <class Cfg>
+int launch_tiled(const float* a, const float* w, const FwdParams& prm, const DevInfo& d, cudaStream_t st) {
+    if (Cfg::SMEM_BYTES > d.max_smem) return MAM_ERR_UNSUPPORTED;
+    CUtensorMap tmA, tmW;
+    int s = encode_rows_k(&tmA, a, prm.M, prm.K, Cfg::BM);
+    if (s != MAM_OK) return s;
+    s = encode_rows_k(&tmW, w, prm.N, prm.K, Cfg::BN);
+    if (s != MAM_OK) return s;
+    MAM_CUDA(cudaFuncSetAttribute(mam_fwd_tiled_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  Cfg::SMEM_BYTES));
+    const long long ntiles = ((prm.M + Cfg::BM - 1) / Cfg::BM) * ((prm.N + Cfg::BN - 1) / Cfg::BN);
+    const int grid = (int)(ntiles < d.sms ? ntiles : d.sms);
+    {
+        TimedLaunch t(MAM_KERNEL_FWD_TILED, st);
+        mam_fwd_tiled_kernel<Cfg><<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(tmA, tmW, prm);
+    }
+    MAM_CUDA(cudaGetLastError());
+    return MAM_OK;
+}
+
+//                         TM TN WM WN ST track
+using ValCfg0 = FwdCfg<8, 8, 4, 2, 4, false>;   // 128x128 tile, 256 consumers
+using ValCfg1 = FwdCfg<4, 8, 8, 2, 4, false>;   // 128x128 tile, 512 consumers
+using ValCfg2 = FwdCfg<8, 4, 4, 4, 4, false>;   // 128x128 tile, 512 consumers
+using ValCfg3 = FwdCfg<4, 4, 8, 2, 6, false>;   // 128x64 tile, 512 consumers
+using IdxCfg0 = FwdCfg<4, 8, 4, 2, 4, true>;    // 64x128 tile, 256 consumers
+using IdxCfg1 = FwdCfg<4, 4, 8, 2, 4, true>;    // 128x64 tile, 512 consumers
+using IdxCfg2 = FwdCfg<8, 4, 2, 4, 4, true>;    // 64x128 tile, 256 consumers
+using IdxCfg3 = FwdCfg<4, 4, 4, 4, 4, true>;    // 64x128 tile, 512 consumers
+constexpr int N_VARIANTS = 4;
+const char* kValNames[N_VARIANTS] = {"val_8x8_128x128_c256", "val_4x8_128x128_c512", "val_8x4_128x128_c512",
+                                     "val_4x4_128x64_c512"};
+const char* kIdxNames[N_VARIANTS] = {"idx_4x8_64x128_c256", "idx_4x4_128x64_c512", "idx_8x4_64x128_c256",
+                                     "idx_4x4_64x128_c512"};
+int g_variant[2] = {-1, -1};  // [with_indices]
+
+int bad_ptr(const void* p) { return p == nullptr; }
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+size_t round256(size_t x) { return (x + 255) & ~size_t(255); }
+
+}  // namespace
+
+extern "C" {
+
+const char* mam_status_str(int status) {
+    switch (status) {
+        case MAM_OK: return "ok";
+        case MAM_ERR_INVALID_ARGUMENT: return "invalid argument (null pointer, non-positive extent or bad layout code)";
+        case MAM_ERR_UNSUPPORTED: return "extent outside what the kernels support";
+        case MAM_ERR_WORKSPACE: return "workspace missing, too small or not 256-byte aligned";
+        case MAM_ERR_CUDA: return "a CUDA call failed (see mam_last_cuda_error)";
+        case MAM_ERR_DEVICE_TIMEOUT: return "a bounded wait inside a kernel gave up; results are invalid";
+        case MAM_ERR_NOT_SM100: return "the current device is not compute capability 10.x (B200)";
+        default: return "unknown status";
+    }
+}
+
+int mam_abi_version(void) { return MAM_ABI_VERSION; }
+
+const char* mam_last_cuda_error(void) { return cudaGetErrorString(t_last_cuda); }
+
+int mam_check_device_flag(void) {
+    MAM_CUDA(cudaDeviceSynchronize());
+    int flag = 0;
+    MAM_CUDA(cudaMemcpyFromSymbol(&flag, g_wait_gave_up, sizeof(int)));
+    if (flag) {
+        int zero = 0;
+        MAM_CUDA(cudaMemcpyToSymbol(g_wait_gave_up, &zero, sizeof(int)));
+        return MAM_ERR_DEVICE_TIMEOUT;
+    }
+    return MAM_OK;
+}
+
+int mam_timer_arm(void** starts, void** stops, int capacity, int kernel_id) {
+    if (!starts || !stops || capacity <= 0) return MAM_ERR_INVALID_ARGUMENT;
+    g_timer.starts = starts;
+    g_timer.stops = stops;
+    g_timer.capacity = capacity;
+    g_timer.count = 0;
+    g_timer.kernel_id = kernel_id;
+    return MAM_OK;
+}
+
+int mam_timer_disarm(void) {
+    const int n = g_timer.count;
+    g_timer = KernelTimer();
+    return n;
+}
+
+int mam_set_fwd_variant(int with_indices, int variant) {
+    if (variant < -2 || variant >= N_VARIANTS) return MAM_ERR_INVALID_ARGUMENT;
+    g_variant[with_indices ? 1 : 0] = variant;
+    return MAM_OK;
+}
+
+const char* mam_fwd_variant_name(int with_indices, int variant) {
+    if (variant == -1) return "auto";
+    if (variant == -2) return "generic";
+    if (variant < 0 || variant >= N_VARIANTS) return "";
+    return with_indices ? kIdxNames[variant] : kValNames[variant];
+}
+
+size_t mam_fwd_workspace_bytes(int64_t M, int64_t K, int64_t N, int b_layout, int want_indices) {
+    (void)M;
+    (void)want_indices;
+    if (b_layout == MAM_B_KN && K > 0 && N > 0 && K % 4 == 0) return round256((size_t)K * (size_t)N * 4);
+    return 0;
+}
+
+int mam_transpose_f32(const float* in, float* out, int64_t R, int64_t C, void* stream) {
+    if (bad_ptr(in) || bad_ptr(out) || R <= 0 || C <= 0) return MAM_ERR_INVALID_ARGUMENT;
+    const long long gx = (C + 31) / 32, gy = (R + 31) / 32;
+    if (gy > 65535 || gx > 2147483647LL) return MAM_ERR_UNSUPPORTED;
+    mam_transpose_kernel<<<dim3((unsigned)gx, (unsigned)gy), 256, 0, (cudaStream_t)stream>>>(in, out, R, C);
+    MAM_CUDA(cudaGetLastError());
+    return MAM_OK;
+}
+
+int mam_fwd_f32(const float* a, const float* b, int b_layout, const float* bias, const float* dense, int blend,
+                float alpha, float beta, float* y, int32_t* argmax, int32_t* argmin, int64_t M, int64_t K,
+                int64_t N, void* workspace, size_t workspace_bytes, void* stream) {
+    if (bad_ptr(a) || bad_ptr(b) || bad_ptr(y) || M <= 0 || K <= 0 || N <= 0) return MAM_ERR_INVALID_ARGUMENT;
+    if (b_layout != MAM_B_KN && b_layout != MAM_B_NK) return MAM_ERR_INVALID_ARGUMENT;
+    if ((argmax == nullptr) != (argmin == nullptr)) return MAM_ERR_INVALID_ARGUMENT;
+    if (K >= (1LL << 31) || N >= (1LL << 31) || M >= (1LL << 31)) return MAM_ERR_UNSUPPORTED;
+    const DevInfo* d = nullptr;
+    int st = device_info(&d);
+    if (st != MAM_OK) return st;
+    cudaStream_t cs = (cudaStream_t)stream;
+    const bool want_idx = argmax != nullptr;
+    EpilogueArgs ep{bias, dense, alpha, beta, blend};
+
+    int variant = g_variant[want_idx ? 1 : 0];
+    const bool tma_ok = (K % 4 == 0) && aligned16(a) && aligned16(b) && K / FWD_BK < 65535;
+    if (variant == -1) variant = (tma_ok && M * N >= 4096) ? 0 : -2;
+    if (variant >= 0 && !tma_ok) variant = -2;
+
+    if (variant == -2) {
+        const long long gx = (N + GEN_TILE - 1) / GEN_TILE, gy = (M + GEN_TILE - 1) / GEN_TILE;
+        if (gy > 65535) return MAM_ERR_UNSUPPORTED;
+        dim3 grid((unsigned)gx, (unsigned)gy);
+        TimedLaunch t(MAM_KERNEL_FWD_GENERIC, cs);
+        if (b_layout == MAM_B_NK)
+            mam_fwd_generic_kernel<true><<<grid, 256, 0, cs>>>(a, b, y, argmax, argmin, M, K, N, ep);
+        else
+            mam_fwd_generic_kernel<false><<<grid, 256, 0, cs>>>(a, b, y, argmax, argmin, M, K, N, ep);
+        MAM_CUDA(cudaGetLastError());
+        return MAM_OK;
+    }
+
+    const float* w = b;
+    if (b_layout == MAM_B_KN) {
+        const size_t need = round256((size_t)K * (size_t)N * 4);
+        if (workspace == nullptr || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255u))
+            return MAM_ERR_WORKSPACE;
+        st = mam_transpose_f32(b, static_cast<float*>(workspace), K, N, stream);
+        if (st != MAM_OK) return st;
+        w = static_cast<const float*>(workspace);
+    }
+    int* flag = nullptr;
+    MAM_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&flag), g_wait_gave_up));
+    FwdParams prm{y, argmax, argmin, M, K, N, ep, 1.0f, flag};
+    if (!want_idx) {
+        switch (variant) {
+            case 0: st = launch_tiled<ValCfg0>(a, w, prm, *d, cs); break;
+            case 1: st = launch_tiled<ValCfg1>(a, w, prm, *d, cs); break;
+            case 2: st = launch_tiled<ValCfg2>(a, w, prm, *d, cs); break;
+            default: st = launch_tiled<ValCfg3>(a, w, prm, *d, cs); break;
+        }
+        return st;
+    }
+    switch (variant) {
+        case 0: st = launch_tiled<IdxCfg0>(a, w, prm, *d, cs); break;
+        case 1: st = launch_tiled<IdxCfg1>(a, w, prm, *d, cs); break;
+        case 2: st = launch_tiled<IdxCfg2>(a, w, prm, *d, cs); break;
+        default: st = launch_tiled<IdxCfg3>(a, w, prm, *d, cs); break;
+    }
+    if (st != MAM_OK) return st;
+    const long long total = M * N;
+    const long long blocks = (total + 255) / 256;
+    if (blocks > 2147483647LL) return MAM_ERR_UNSUPPORTED;
+    {
+        TimedLaunch t(MAM_KERNEL_FWD_RESOLVE, cs);
+        mam_resolve_kernel<<<(unsigned)blocks, 256, 0, cs>>>(a, w, argmax, argmin, M, K, N);
+    }
+    MAM_CUDA(cudaGetLastError());
+    return MAM_OK;
+}
+
+int mam_bwd_f32(const float* a, const float* b, int b_layout, const float* grad, const int32_t* argmax,
+                const int32_t* argmin, float* da, float* db, float scale, int64_t M, int64_t K, int64_t N,
+                void* stream) {
+    if (bad_ptr(a) || bad_ptr(b) || bad_ptr(grad) || bad_ptr(argmax) || bad_ptr(argmin) || bad_ptr(da) ||
+        bad_ptr(db) || M <= 0 || K <= 0 || N <= 0)
+        return MAM_ERR_INVALID_ARGUMENT;
+    if (b_layout != MAM_B_KN && b_layout != MAM_B_NK) return MAM_ERR_INVALID_ARGUMENT;
+    const DevInfo* d = nullptr;
+    int st = device_info(&d);
+    if (st != MAM_OK) return st;
+    if (K * 4 > d->max_smem - 1024) return MAM_ERR_UNSUPPORTED;
+    cudaStream_t cs = (cudaStream_t)stream;
+    int rows = (int)((32 * 1024) / (K * 4));
+    if (rows < 1) rows = 1;
+    if (rows > 8) rows = 8;
+    const size_t smem = (size_t)rows * (size_t)K * 4;
+    const long long grid = (M + rows - 1) / rows;
+    if (grid > 2147483647LL) return MAM_ERR_UNSUPPORTED;
+    MAM_CUDA(cudaMemsetAsync(db, 0, (size_t)K * (size_t)N * 4, cs));
+    TimedLaunch t(MAM_KERNEL_BWD, cs);
+    if (b_layout == MAM_B_NK) {
+        MAM_CUDA(cudaFuncSetAttribute(mam_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        mam_bwd_kernel<true><<<(unsigned)grid, BWD_THREADS, smem, cs>>>(a, b, grad, argmax, argmin, da, db, M, K, N,
+                                                                        rows, scale);
+    } else {
+        MAM_CUDA(cudaFuncSetAttribute(mam_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        mam_bwd_kernel<false><<<(unsigned)grid, BWD_THREADS, smem, cs>>>(a, b, grad, argmax, argmin, da, db, M, K,
+                                                                         N, rows, scale);
+    }
+    MAM_CUDA(cudaGetLastError());
+    return MAM_OK;
+}
+
+int mam_selcount_i32(const int32_t* argmax, const int32_t* argmin, int32_t* hit_max, int32_t* hit_min, int64_t M,
+                     int64_t K, int64_t N, void* stream) {
+    if (bad_ptr(argmax) || bad_ptr(argmin) || bad_ptr(hit_max) || bad_ptr(hit_min) || M <= 0 || K <= 0 || N <= 0)
+        return MAM_ERR_INVALID_ARGUMENT;
+    const DevInfo* d = nullptr;
+    int st = device_info(&d);
+    if (st != MAM_OK) return st;
+    const long long budget = (long long)d->max_smem - 1024;
+    if (2 * K * 4 > budget) return MAM_ERR_UNSUPPORTED;
+    int cols = (int)(budget / (2 * K * 4));
+    if (cols > 8) cols = 8;
+    // keep at least ~2 CTAs per SM worth of blocks when N allows it
+    while (cols > 1 && (N + cols - 1) / cols < 2LL * d->sms) cols >>= 1;
+    const size_t smem = 2ull * cols * (size_t)K * 4;
+    const long long grid = (N + cols - 1) / cols;
+    MAM_CUDA(cudaFuncSetAttribute(mam_selcount_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    {
+        TimedLaunch t(MAM_KERNEL_SELCOUNT, (cudaStream_t)stream);
+        mam_selcount_kernel<<<(unsigned)grid, 256, smem, (cudaStream_t)stream>>>(argmax, argmin, hit_max, hit_min, M,
+                                                                                 K, N, cols);
+    }
+    MAM_CUDA(cudaGetLastError());
+    return MAM_OK;
+}
+
+int mam_selcount_indicator_i32(const int32_t* hit_max, const int32_t* hit_min, int32_t* count, int64_t n_elems,
+                               void* stream) {
+    if (bad_ptr(hit_max) || bad_ptr(hit_min) || bad_ptr(count) || n_elems <= 0) return MAM_ERR_INVALID_ARGUMENT;
+    const long long blocks = (n_elems + 255) / 256;
+    mam_selcount_indicator_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(hit_max, hit_min, count,
+                                                                                      n_elems);
+    MAM_CUDA(cudaGetLastError());
+    return MAM_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,262 @@
+// PyTorch operator shim over the C ABI of libmam_b200.so.
+//
+// Defines the same operator schemas as the reference's extension modules
+//   mamtorch/kernel/v1/csrc/register_functions.cpp:21-24
+//   mamtorch/kernel/v2/csrc/register_functions.cpp:28-32
+//   mamtorch/kernel/v3/csrc/register_functions.cpp:30-34
+//   mamtorch/kernel/v4/csrc/register_functions.cpp:10-14
+// so torch.ops.mamtorch_kernel_v{1,2,3,4}.* keep their names, argument order and return types,
+// plus a `mamtorch_b200` namespace with the weight-as-stored ([N,K]) forms the nn modules use to
+// skip the reference's per-call transposes.  Only CUDA implementations are registered: a CPU
+// tensor gets the dispatcher's NotImplementedError instead of the reference's "print a warning and
+// return uninitialised memory" (mamtorch/kernel/v1/csrc/fullyconnected.cpp:24-32).
+// Nothing here computes: it validates, allocates outputs and workspace with the caching
+// allocator, and forwards raw pointers and the current stream to the C ABI.
+#include <ATen/ATen.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/library.h>
+
+#include <vector>
+
+#include "../../include/mam_b200.h"
+
+namespace {
+
+void check_status(int st, const char* what) {
+    if (st == MAM_OK) return;
+    if (st == MAM_ERR_CUDA) {
+        TORCH_CHECK(false, what, ": ", mam_status_str(st), ": ", mam_last_cuda_error());
+    }
+    TORCH_CHECK(false, what, ": ", mam_status_str(st));
+}
+
+void check_matrix(const at::Tensor& t, const char* name, at::ScalarType dt = at::kFloat) {
+    TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
+    TORCH_CHECK(t.dim() == 2, name, " must be 2-D");
+    TORCH_CHECK(t.scalar_type() == dt, name, " has the wrong dtype");
+    TORCH_CHECK(t.is_contiguous(), name, " must be contiguous");
+}
+
+struct Fwd {
+    at::Tensor y, argmax, argmin;
+};
+
+// b_layout: MAM_B_KN -> w is b[K,N]; MAM_B_NK -> w is W[N,K]
+Fwd forward_impl(const at::Tensor& a, const at::Tensor& w, int b_layout, const c10::optional<at::Tensor>& bias,
+                 const c10::optional<at::Tensor>& dense, bool blend, double alpha, double beta, bool want_idx) {
+    check_matrix(a, "a");
+    check_matrix(w, "b");
+    const int64_t M = a.size(0), K = a.size(1);
+    const int64_t N = b_layout == MAM_B_KN ? w.size(1) : w.size(0);
+    TORCH_CHECK((b_layout == MAM_B_KN ? w.size(0) : w.size(1)) == K, "inner dimensions of a and b differ");
+    TORCH_CHECK(a.device() == w.device(), "a and b must be on the same device");
+    TORCH_CHECK(K > 0, "the reduction dimension must not be empty");
+    c10::cuda::CUDAGuard guard(a.device());
+    Fwd out;
+    out.y = at::empty({M, N}, a.options());
+    if (want_idx) {
+        out.argmax = at::empty({M, N}, a.options().dtype(at::kInt));
+        out.argmin = at::empty({M, N}, a.options().dtype(at::kInt));
+    }
+    if (M == 0 || N == 0) return out;
+    const float* bias_p = nullptr;
+    at::Tensor bias_c;
+    if (bias.has_value() && bias->defined()) {
+        TORCH_CHECK(bias->is_cuda() && bias->scalar_type() == at::kFloat && bias->numel() == N,
+                    "bias must be a float CUDA tensor with one value per output");
+        bias_c = bias->contiguous();
+        bias_p = bias_c.data_ptr<float>();
+    }
+    const float* dense_p = nullptr;
+    at::Tensor dense_c;
+    if (dense.has_value() && dense->defined()) {
+        TORCH_CHECK(dense->sizes() == out.y.sizes() && dense->scalar_type() == at::kFloat, "dense term shape");
+        dense_c = dense->contiguous();
+        dense_p = dense_c.data_ptr<float>();
+    }
+    const size_t ws_bytes = mam_fwd_workspace_bytes(M, K, N, b_layout, want_idx);
+    at::Tensor ws;
+    void* ws_p = nullptr;
+    if (ws_bytes) {
+        ws = at::empty({(int64_t)ws_bytes}, a.options().dtype(at::kByte));
+        ws_p = ws.data_ptr();
+    }
+    auto stream = at::cuda::getCurrentCUDAStream();
+    const int st = mam_fwd_f32(a.data_ptr<float>(), w.data_ptr<float>(), b_layout, bias_p, dense_p, blend ? 1 : 0,
+                               (float)alpha, (float)beta, out.y.data_ptr<float>(),
+                               want_idx ? out.argmax.data_ptr<int32_t>() : nullptr,
+                               want_idx ? out.argmin.data_ptr<int32_t>() : nullptr, M, K, N, ws_p, ws_bytes,
+                               stream.stream());
+    check_status(st, "mam_fwd_f32");
+    return out;
+}
+
+std::vector<at::Tensor> backward_impl(const at::Tensor& a, const at::Tensor& w, int b_layout, const at::Tensor& grad,
+                                      const at::Tensor& argmax, const at::Tensor& argmin, double scale) {
+    check_matrix(a, "a");
+    check_matrix(w, "b");
+    check_matrix(grad, "grad");
+    check_matrix(argmax, "argmax", at::kInt);
+    check_matrix(argmin, "argmin", at::kInt);
+    const int64_t M = a.size(0), K = a.size(1);
+    const int64_t N = b_layout == MAM_B_KN ? w.size(1) : w.size(0);
+    TORCH_CHECK((b_layout == MAM_B_KN ? w.size(0) : w.size(1)) == K, "inner dimensions of a and b differ");
+    TORCH_CHECK(grad.size(0) == M && grad.size(1) == N, "grad must be [M,N]");
+    TORCH_CHECK(argmax.sizes() == grad.sizes() && argmin.sizes() == grad.sizes(), "index shapes must match grad");
+    c10::cuda::CUDAGuard guard(a.device());
+    auto da = at::empty_like(a);
+    auto dw = at::empty_like(w);
+    if (M == 0 || N == 0 || K == 0) {
+        da.zero_();
+        dw.zero_();
+        return {da, dw};
+    }
+    auto stream = at::cuda::getCurrentCUDAStream();
+    const int st = mam_bwd_f32(a.data_ptr<float>(), w.data_ptr<float>(), b_layout, grad.data_ptr<float>(),
+                               argmax.data_ptr<int32_t>(), argmin.data_ptr<int32_t>(), da.data_ptr<float>(),
+                               dw.data_ptr<float>(), (float)scale, M, K, N, stream.stream());
+    check_status(st, "mam_bwd_f32");
+    return {da, dw};
+}
+
+// ------------------------------------------------------------------ reference-named operators
+std::vector<at::Tensor> fullyconnected(const at::Tensor& a, const at::Tensor& b) {
+    auto r = forward_impl(a, b, MAM_B_KN, c10::nullopt, c10::nullopt, false, 1.0, 0.0, true);
+    return {r.y, r.argmax, r.argmin};
+}
+at::Tensor fullyconnected_fast(const at::Tensor& a, const at::Tensor& b) {
+    return forward_impl(a, b, MAM_B_KN, c10::nullopt, c10::nullopt, false, 1.0, 0.0, false).y;
+}
+std::vector<at::Tensor> fullyconnected_backward(const at::Tensor& a, const at::Tensor& b, const at::Tensor& grad,
+                                                const at::Tensor& argmax, const at::Tensor& argmin) {
+    return backward_impl(a, b, MAM_B_KN, grad, argmax, argmin, 1.0);
+}
+
+// v2/v3: C = (1-beta)*mam + beta*(a.b) + bias  (mamtorch/kernel/v3/csrc/cuda/fullyconnected.cu:153-160)
+at::Tensor dense(const at::Tensor& a, const at::Tensor& b) {
+    check_matrix(a, "a");
+    check_matrix(b, "b");
+    return at::matmul(a, b);
+}
+std::vector<at::Tensor> fullyconnected_beta(const at::Tensor& a, const at::Tensor& b, const at::Tensor& bias,
+                                            double beta) {
+    c10::optional<at::Tensor> d;
+    if (beta != 0.0) d = dense(a, b);
+    auto r = forward_impl(a, b, MAM_B_KN, bias, d, true, 1.0 - beta, beta, true);
+    return {r.y, r.argmax, r.argmin};
+}
+at::Tensor fullyconnected_fast_beta(const at::Tensor& a, const at::Tensor& b, const at::Tensor& bias, double beta) {
+    c10::optional<at::Tensor> d;
+    if (beta != 0.0) d = dense(a, b);
+    return forward_impl(a, b, MAM_B_KN, bias, d, true, 1.0 - beta, beta, false).y;
+}
+// (mamtorch/kernel/v3/csrc/cuda/fullyconnected_backward.cu:138-145)
+std::vector<at::Tensor> fullyconnected_backward_beta(const at::Tensor& a, const at::Tensor& b, const at::Tensor& grad,
+                                                     const at::Tensor& argmax, const at::Tensor& argmin, double beta) {
+    auto r = backward_impl(a, b, MAM_B_KN, grad, argmax, argmin, 1.0 - beta);
+    if (beta != 0.0) {
+        r[0].addmm_(grad, b.t(), 1.0, beta);
+        r[1].addmm_(a.t(), grad, 1.0, beta);
+    }
+    return r;
+}
+
+// ------------------------------------------------------------------ weight-as-stored forms
+std::vector<at::Tensor> linear_forward(const at::Tensor& x, const at::Tensor& weight,
+                                       const c10::optional<at::Tensor>& bias, const c10::optional<at::Tensor>& dense_t,
+                                       double alpha, double beta, bool want_idx) {
+    const bool blend = !(alpha == 1.0 && beta == 0.0);
+    auto r = forward_impl(x, weight, MAM_B_NK, bias, dense_t, blend, alpha, beta, want_idx);
+    if (!want_idx) return {r.y};
+    return {r.y, r.argmax, r.argmin};
+}
+std::vector<at::Tensor> linear_backward(const at::Tensor& x, const at::Tensor& weight, const at::Tensor& grad,
+                                        const at::Tensor& argmax, const at::Tensor& argmin, double scale) {
+    return backward_impl(x, weight, MAM_B_NK, grad, argmax, argmin, scale);
+}
+// hits[0] = hit_max[N,K], hits[1] = hit_min[N,K]: how many rows selected each weight
+std::vector<at::Tensor> selection_hits(const at::Tensor& argmax, const at::Tensor& argmin, int64_t K) {
+    check_matrix(argmax, "argmax", at::kInt);
+    check_matrix(argmin, "argmin", at::kInt);
+    TORCH_CHECK(argmax.sizes() == argmin.sizes(), "argmax/argmin shapes differ");
+    c10::cuda::CUDAGuard guard(argmax.device());
+    const int64_t M = argmax.size(0), N = argmax.size(1);
+    auto hmax = at::zeros({N, K}, argmax.options());
+    auto hmin = at::zeros({N, K}, argmax.options());
+    if (M == 0 || N == 0 || K == 0) return {hmax, hmin};
+    auto stream = at::cuda::getCurrentCUDAStream();
+    check_status(mam_selcount_i32(argmax.data_ptr<int32_t>(), argmin.data_ptr<int32_t>(), hmax.data_ptr<int32_t>(),
+                                  hmin.data_ptr<int32_t>(), M, K, N, stream.stream()),
+                 "mam_selcount_i32");
+    return {hmax, hmin};
+}
+// count += (hit_max>0) + (hit_min>0), in place; returns count
+at::Tensor selection_count_update_(at::Tensor count, const at::Tensor& hit_max, const at::Tensor& hit_min) {
+    TORCH_CHECK(count.is_cuda() && count.scalar_type() == at::kInt && count.is_contiguous(), "count: int32 CUDA");
+    TORCH_CHECK(hit_max.sizes() == count.sizes() && hit_min.sizes() == count.sizes(), "shape mismatch");
+    c10::cuda::CUDAGuard guard(count.device());
+    if (count.numel() == 0) return count;
+    auto stream = at::cuda::getCurrentCUDAStream();
+    check_status(mam_selcount_indicator_i32(hit_max.data_ptr<int32_t>(), hit_min.data_ptr<int32_t>(),
+                                            count.data_ptr<int32_t>(), count.numel(), stream.stream()),
+                 "mam_selcount_indicator_i32");
+    return count;
+}
+
+}  // namespace
+
+TORCH_LIBRARY(mamtorch_kernel_v1, m) {
+    m.def("fullyconnected(Tensor a, Tensor b) -> Tensor[]");
+    m.def("fullyconnected_backward(Tensor a, Tensor b, Tensor grad, Tensor argmax, Tensor argmin) -> Tensor[]");
+}
+TORCH_LIBRARY_IMPL(mamtorch_kernel_v1, CUDA, m) {
+    m.impl("fullyconnected", &fullyconnected);
+    m.impl("fullyconnected_backward", &fullyconnected_backward);
+}
+
+TORCH_LIBRARY(mamtorch_kernel_v2, m) {
+    m.def("fullyconnected(Tensor a, Tensor b, Tensor bias, float beta) -> Tensor[]");
+    m.def("fullyconnected_backward(Tensor a, Tensor b, Tensor grad, Tensor argmax, Tensor argmin, float beta) -> Tensor[]");
+    m.def("dense(Tensor a, Tensor b) -> Tensor");
+}
+TORCH_LIBRARY_IMPL(mamtorch_kernel_v2, CUDA, m) {
+    m.impl("fullyconnected", &fullyconnected_beta);
+    m.impl("fullyconnected_backward", &fullyconnected_backward_beta);
+    m.impl("dense", &dense);
+}
+
+TORCH_LIBRARY(mamtorch_kernel_v3, m) {
+    m.def("fullyconnected(Tensor a, Tensor b, Tensor bias, float beta) -> Tensor[]");
+    m.def("fullyconnected_fast(Tensor a, Tensor b, Tensor bias, float beta) -> Tensor");
+    m.def("fullyconnected_backward(Tensor a, Tensor b, Tensor grad, Tensor argmax, Tensor argmin, float beta) -> Tensor[]");
+}
+TORCH_LIBRARY_IMPL(mamtorch_kernel_v3, CUDA, m) {
+    m.impl("fullyconnected", &fullyconnected_beta);
+    m.impl("fullyconnected_fast", &fullyconnected_fast_beta);
+    m.impl("fullyconnected_backward", &fullyconnected_backward_beta);
+}
+
+TORCH_LIBRARY(mamtorch_kernel_v4, m) {
+    m.def("fullyconnected(Tensor a, Tensor b) -> Tensor[]");
+    m.def("fullyconnected_fast(Tensor a, Tensor b) -> Tensor");
+    m.def("fullyconnected_backward(Tensor a, Tensor b, Tensor grad, Tensor argmax, Tensor argmin) -> Tensor[]");
+}
+TORCH_LIBRARY_IMPL(mamtorch_kernel_v4, CUDA, m) {
+    m.impl("fullyconnected", &fullyconnected);
+    m.impl("fullyconnected_fast", &fullyconnected_fast);
+    m.impl("fullyconnected_backward", &fullyconnected_backward);
+}
+
+TORCH_LIBRARY(mamtorch_b200, m) {
+    m.def("linear_forward(Tensor x, Tensor weight, Tensor? bias, Tensor? dense, float alpha, float beta, bool want_idx) -> Tensor[]");
+    m.def("linear_backward(Tensor x, Tensor weight, Tensor grad, Tensor argmax, Tensor argmin, float scale) -> Tensor[]");
+    m.def("selection_hits(Tensor argmax, Tensor argmin, int K) -> Tensor[]");
+    m.def("selection_count_update_(Tensor(a!) count, Tensor hit_max, Tensor hit_min) -> Tensor(a!)");
+}
+TORCH_LIBRARY_IMPL(mamtorch_b200, CUDA, m) {
+    m.impl("linear_forward", &linear_forward);
+    m.impl("linear_backward", &linear_backward);
+    m.impl("selection_hits", &selection_hits);
+    m.impl("selection_count_update_", &selection_count_update_);
+}

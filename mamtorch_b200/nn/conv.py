@@ -1,0 +1,187 @@
+"""MAM convolutions as im2col + the fully-connected kernels.
+
+The reference carries convolution only as never-compiled text backups
+(`mamtorch/nn/backup/mamconv2d.txt:20-177`, `mamconv1d.txt`, kernels in
+`mamtorch/kernel/backup/mamconv2d_forward.txt`).  These modules keep those constructor signatures
+and attributes (weight [F,C,kH,kW], bias, beta schedule, argmax/argmin, selection counts) but:
+
+  * integer `padding` is the usual symmetric convolution padding (the backup pads p//2 on the
+    left and p-p//2 on the right, `mamconv2d.txt:133-139`);
+  * the reduction index is k = (c*kH + kh)*kW + kw, the order of `weight.view(F, -1)` and of
+    F.unfold, not the backup's k = c + C*(kh + kH*kw) (`mamconv2d_forward.txt:128`);
+    `to_legacy_index` converts.
+
+Each output pixel is one row of a GEMM-shaped MAM problem: M = B*Ho*Wo, K = C*kH*kW, N = F.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as F
+
+from . import functional as MF
+
+__all__ = ["MAMConv1d", "MAMConv2d", "mam_conv2d"]
+
+
+def _pair(v):
+    return tuple(v) if isinstance(v, (tuple, list)) else (v, v)
+
+
+def mam_conv2d(x, weight, bias=None, stride=1, padding=0, dense=None, alpha=1.0, beta=0.0, need_indices=True):
+    """x[B,C,H,W], weight[F,C,kH,kW] -> (y[B,F,Ho,Wo], argmax, argmin) with indices into C*kH*kW."""
+    B, C, H, W = x.shape
+    Fo, _, kH, kW = weight.shape
+    sh, sw = _pair(stride)
+    ph, pw = _pair(padding)
+    Ho = (H + 2 * ph - kH) // sh + 1
+    Wo = (W + 2 * pw - kW) // sw + 1
+    cols = F.unfold(x, (kH, kW), padding=(ph, pw), stride=(sh, sw))          # [B, K, L]
+    rows = cols.transpose(1, 2).reshape(B * Ho * Wo, C * kH * kW)            # one row per pixel
+    dflat = None
+    if dense is not None:
+        dflat = dense.permute(0, 2, 3, 1).reshape(B * Ho * Wo, Fo)
+    y, amax, amin = MF.mam_linear(rows, weight.reshape(Fo, -1), bias, dflat, alpha, beta, need_indices)
+    img = lambda t: None if t is None else t.view(B, Ho, Wo, Fo).permute(0, 3, 1, 2)
+    return img(y), img(amax), img(amin)
+
+
+def to_legacy_index(idx, in_channels, kH, kW):
+    """(c*kH + kh)*kW + kw  ->  c + C*(kh + kH*kw), the order of the reference's backup kernels."""
+    kw = idx % kW
+    kh = (idx // kW) % kH
+    c = idx // (kW * kH)
+    return c + in_channels * (kh + kH * kw)
+
+
+class _ConvBase(torch.nn.Module):
+    def _init_common(self, bias, beta, beta_decay, beta_epochs, out_channels):
+        self.beta_decay, self.beta_epochs = beta_decay, beta_epochs
+        if bias:
+            self.bias = torch.nn.Parameter(torch.empty(out_channels))
+        else:
+            self.register_parameter("bias", None)
+        self.beta = 1.0 if beta else 0.0
+        self.max_selection_count = self.min_selection_count = None
+        self.argmax = self.argmin = None
+        self.reset_parameters()
+
+    def reset_parameters(self):
+        torch.nn.init.kaiming_uniform_(self.weight, a=math.sqrt(5))
+        if self.bias is not None:
+            fan_in = self.weight[0].numel()
+            bound = 1 / math.sqrt(fan_in) if fan_in > 0 else 0
+            torch.nn.init.uniform_(self.bias, -bound, bound)
+
+    def adjust_beta(self, epoch):
+        if self.beta_epochs <= 0:
+            raise Exception("Invalid value for beta_epochs. Please use a positive integer.")
+        t = epoch / self.beta_epochs
+        if epoch >= self.beta_epochs:
+            self.beta = 0
+        elif self.beta_decay == "linear":
+            self.beta = 1 - t
+        elif self.beta_decay == "descending-parabola":
+            self.beta = 1 - t ** 2
+        elif self.beta_decay == "ascending-parabola":
+            self.beta = 1 + t ** 2 - 2 * t
+
+    def reset_selection_count(self):
+        self.max_selection_count = torch.zeros(self.weight.shape, dtype=torch.int32, device=self.weight.device)
+        self.min_selection_count = torch.zeros_like(self.max_selection_count)
+
+    def update_selection_count(self):
+        """Adds the number of output pixels that selected each weight: max hits into
+        max_selection_count, min hits into min_selection_count (`mamconv2d.txt:90-114` keeps the
+        two apart, unlike the fully-connected module)."""
+        if self.argmax is None or self.argmin is None:
+            raise Exception("No argmax or argmin values have been evaluated yet.")
+        if self.max_selection_count is None:
+            self.reset_selection_count()
+        Fo = self.weight.size(0)
+        K = self.weight[0].numel()
+        flat = lambda t: t.movedim(1, -1).reshape(-1, Fo).contiguous()
+        hmax, hmin = MF.selection_hits(flat(self.argmax), flat(self.argmin), K)
+        self.max_selection_count += (hmax > 0).view_as(self.max_selection_count).to(torch.int32)
+        self.min_selection_count += (hmin > 0).view_as(self.min_selection_count).to(torch.int32)
+
+
+class MAMConv2d(_ConvBase):
+    def __init__(self, in_channels, out_channels, kernel_size, bias=True, stride=1, padding=0,
+                 padding_mode="zeros", beta=False, beta_decay="linear", beta_epochs=1):
+        super().__init__()
+        self.in_channels, self.out_channels = in_channels, out_channels
+        self.kernel_size, self.stride, self.padding, self.padding_mode = kernel_size, stride, padding, padding_mode
+        kH, kW = _pair(kernel_size)
+        self.weight = torch.nn.Parameter(torch.empty(out_channels, in_channels, kH, kW))
+        self.hstride, self.wstride = _pair(stride)
+        self._init_common(bias, beta, beta_decay, beta_epochs, out_channels)
+
+    def _padding(self):
+        kH, kW = self.weight.shape[2:]
+        if self.padding == "same":
+            if (self.hstride, self.wstride) != (1, 1):
+                raise Exception("Cannot apply 'same' padding with stride > 1.")
+            if kH % 2 == 0 or kW % 2 == 0:
+                raise Exception("'same' padding needs odd kernel sizes here.")
+            return (kH // 2, kW // 2)
+        if self.padding == "valid":
+            return (0, 0)
+        return _pair(self.padding)
+
+    def forward(self, input):
+        ph, pw = self._padding()
+        x = input
+        if self.padding_mode != "zeros" and (ph or pw):
+            x = F.pad(x, (pw, pw, ph, ph), mode=self.padding_mode)
+            ph = pw = 0
+        dense = None
+        blend = self.beta >= 10e-5
+        if blend:
+            dense = F.conv2d(x, self.weight, stride=(self.hstride, self.wstride), padding=(ph, pw))
+        y, self.argmax, self.argmin = mam_conv2d(x, self.weight, self.bias, (self.hstride, self.wstride), (ph, pw),
+                                                 dense, 1 - self.beta if blend else 1.0,
+                                                 self.beta if blend else 0.0)
+        return y
+
+
+class MAMConv1d(_ConvBase):
+    """1-D form (`mamtorch/nn/backup/mamconv1d.txt`): a 2-D convolution with a height of one."""
+
+    def __init__(self, in_channels, out_channels, kernel_size, bias=True, stride=1, padding=0,
+                 padding_mode="zeros", beta=False, beta_decay="linear", beta_epochs=1):
+        super().__init__()
+        self.in_channels, self.out_channels = in_channels, out_channels
+        self.kernel_size, self.stride, self.padding, self.padding_mode = kernel_size, stride, padding, padding_mode
+        self.weight = torch.nn.Parameter(torch.empty(out_channels, in_channels, kernel_size))
+        self._init_common(bias, beta, beta_decay, beta_epochs, out_channels)
+
+    def forward(self, input):
+        k = self.weight.size(2)
+        if self.padding == "same":
+            if self.stride != 1 or k % 2 == 0:
+                raise Exception("'same' padding needs stride 1 and an odd kernel size.")
+            p = k // 2
+        elif self.padding == "valid":
+            p = 0
+        else:
+            p = int(self.padding)
+        x = input
+        if self.padding_mode != "zeros" and p:
+            x = F.pad(x, (p, p), mode=self.padding_mode)
+            p = 0
+        blend = self.beta >= 10e-5
+        dense = F.conv1d(x, self.weight, stride=self.stride, padding=p).unsqueeze(2) if blend else None
+        y, amax, amin = mam_conv2d(x.unsqueeze(2), self.weight.unsqueeze(2), self.bias, (1, self.stride), (0, p),
+                                   dense, 1 - self.beta if blend else 1.0, self.beta if blend else 0.0)
+        self.argmax, self.argmin = amax.squeeze(2), amin.squeeze(2)
+        return y.squeeze(2)
+
+    def update_selection_count(self):
+        am, an = self.argmax, self.argmin
+        self.argmax, self.argmin = am.unsqueeze(2), an.unsqueeze(2)
+        try:
+            super().update_selection_count()
+        finally:
+            self.argmax, self.argmin = am, an

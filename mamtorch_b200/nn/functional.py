@@ -1,0 +1,92 @@
+"""Differentiable MAM primitives on the weight as a module stores it (W[out,in], K-contiguous).
+
+`mam_linear` is what the modules call.  It hands W to the kernels in place -- the reference
+transposes it into a fresh [K,N] copy on every forward (`mamtorch/nn/v4/fullyconnected.py:141`) and
+its host code transposes the activations again (`mamtorch/kernel/v4/csrc/cuda/fullyconnected.cu:66`)
+-- and folds the alpha/beta blend and the bias add into the kernel epilogue.
+"""
+from __future__ import annotations
+
+import torch
+from torch import Tensor
+
+_ops = torch.ops.mamtorch_b200
+
+
+@torch.library.register_fake("mamtorch_b200::linear_forward")
+def _(x, weight, bias, dense, alpha, beta, want_idx):
+    torch._check(x.dim() == 2 and weight.dim() == 2 and x.size(1) == weight.size(1))
+    shape = (x.size(0), weight.size(0))
+    out = [x.new_empty(shape)]
+    if want_idx:
+        out += [x.new_empty(shape, dtype=torch.int), x.new_empty(shape, dtype=torch.int)]
+    return out
+
+
+@torch.library.register_fake("mamtorch_b200::linear_backward")
+def _(x, weight, grad, argmax, argmin, scale):
+    return [torch.empty_like(x), torch.empty_like(weight)]
+
+
+@torch.library.register_fake("mamtorch_b200::selection_hits")
+def _(argmax, argmin, K):
+    shape = (argmax.size(1), K)
+    return [argmax.new_empty(shape), argmax.new_empty(shape)]
+
+
+class _MamLinear(torch.autograd.Function):
+    """y = alpha*(max_k x*w + min_k x*w) + beta*dense + bias, gradient through the selected pairs."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, dense, alpha, beta):
+        y, argmax, argmin = _ops.linear_forward(x, weight, bias, dense, alpha, beta, True)
+        ctx.save_for_backward(x, weight, argmax, argmin)
+        ctx.alpha, ctx.beta = alpha, beta
+        ctx.has_bias, ctx.has_dense = bias is not None, dense is not None
+        ctx.mark_non_differentiable(argmax, argmin)
+        return y, argmax, argmin
+
+    @staticmethod
+    def backward(ctx, gy, _g1, _g2):
+        x, weight, argmax, argmin = ctx.saved_tensors
+        gy = gy.contiguous()
+        dx = dw = dbias = ddense = None
+        if ctx.needs_input_grad[0] or ctx.needs_input_grad[1]:
+            dx, dw = _ops.linear_backward(x, weight, gy, argmax, argmin, ctx.alpha)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            dbias = gy.sum(0)
+        if ctx.has_dense and ctx.needs_input_grad[3]:
+            ddense = gy * ctx.beta
+        return dx, dw, dbias, ddense, None, None
+
+
+def mam_linear(x: Tensor, weight: Tensor, bias: Tensor | None = None, dense: Tensor | None = None,
+               alpha: float = 1.0, beta: float = 0.0, need_indices: bool = True):
+    """x[M,K], weight[N,K] -> (y[M,N], argmax, argmin) or (y, None, None).
+
+    With `need_indices=False` the values-only kernel runs (no autograd: use it for inference)."""
+    x = x.contiguous()
+    weight = weight.contiguous()
+    if not need_indices and torch.is_grad_enabled() and (
+            x.requires_grad or weight.requires_grad or (bias is not None and bias.requires_grad)
+            or (dense is not None and dense.requires_grad)):
+        need_indices = True  # a gradient is wanted: only the index-producing kernel can route it
+        y, _, _ = _MamLinear.apply(x, weight, bias, dense, float(alpha), float(beta))
+        return y, None, None
+    if need_indices:
+        return _MamLinear.apply(x, weight, bias, dense, float(alpha), float(beta))
+    y, = _ops.linear_forward(x, weight, bias, dense, float(alpha), float(beta), False)
+    return y, None, None
+
+
+def selection_hits(argmax: Tensor, argmin: Tensor, in_features: int):
+    """(hit_max[N,K], hit_min[N,K]): how many rows picked each weight as max / as min."""
+    return _ops.selection_hits(argmax.contiguous(), argmin.contiguous(), int(in_features))
+
+
+def selection_count_update_(count: Tensor, argmax: Tensor, argmin: Tensor) -> Tensor:
+    """In-place equivalent of one `update_selection_count()` of the reference module
+    (`mamtorch/nn/v4/fullyconnected.py:114-131`): +1 for every weight any row selected as max and
+    +1 for every weight any row selected as min, both added to the same matrix."""
+    hmax, hmin = selection_hits(argmax, argmin, count.size(1))
+    return _ops.selection_count_update_(count, hmax, hmin)

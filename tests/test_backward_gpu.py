@@ -1,0 +1,79 @@
+"""Backward and selection-count parity on the GPU through the C ABI."""
+import numpy as np
+import pytest
+import torch
+
+import capi
+from conftest import assert_grad_close, golden_names, load_golden
+from oracle import c_oracle, mam_oracle
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("layout", [capi.KN, capi.NK])
+@pytest.mark.parametrize("name", [n for n in golden_names() if not n.startswith("blend")])
+def test_golden_backward(name, layout, cuda):
+    g = load_golden(name)
+    a = torch.from_numpy(g["a"]).to(cuda)
+    b = torch.from_numpy(np.ascontiguousarray(g["b"].T) if layout == capi.NK else g["b"]).to(cuda)
+    grad = torch.from_numpy(g["g"]).to(cuda)
+    imax = torch.from_numpy(g["argmax"]).to(torch.int32).to(cuda)
+    imin = torch.from_numpy(g["argmin"]).to(torch.int32).to(cuda)
+    da, db = capi.backward(a, b, grad, imax, imin, layout)
+    db = db.T if layout == capi.NK else db
+    assert_grad_close(da.cpu().numpy(), g["agrad"])
+    assert_grad_close(db.cpu().numpy(), g["bgrad"])
+
+
+def test_blend_scale(cuda):
+    g = load_golden("blend_40x64x48")
+    beta = float(g["beta"])
+    a, b, grad = (torch.from_numpy(g[k]).to(cuda) for k in ("a", "b", "g"))
+    imax = torch.from_numpy(g["argmax"]).to(torch.int32).to(cuda)
+    imin = torch.from_numpy(g["argmin"]).to(torch.int32).to(cuda)
+    da, db = capi.backward(a, b, grad, imax, imin, capi.KN, scale=1 - beta)
+    da = da + beta * (grad @ b.T)
+    db = db + beta * (a.T @ grad)
+    assert_grad_close(da.cpu().numpy(), g["agrad"])
+    assert_grad_close(db.cpu().numpy(), g["bgrad"])
+
+
+@pytest.mark.parametrize("shape", [(700, 768, 520), (33, 3000, 40), (2048, 64, 96)])
+def test_random_backward_against_c_oracle(shape, cuda):
+    M, K, N = shape
+    gen = torch.Generator().manual_seed(M + K + N)
+    a = torch.randn(M, K, generator=gen)
+    w = torch.randn(N, K, generator=gen) * K ** -0.5
+    grad = torch.randn(M, N, generator=gen)
+    _, imax, imin = c_oracle.forward(a.numpy(), w.numpy(), b_is_nk=True)
+    # a few coincident selections: the pair must then be counted twice
+    imin[0, :] = imax[0, :]
+    da_ref, dw_ref = c_oracle.backward(a.numpy(), w.numpy(), grad.numpy(), imax, imin, b_is_nk=True)
+    da, dw = capi.backward(a.to(cuda), w.to(cuda), grad.to(cuda),
+                           torch.from_numpy(imax).to(torch.int32).to(cuda),
+                           torch.from_numpy(imin).to(torch.int32).to(cuda), capi.NK)
+    assert_grad_close(da.cpu().numpy(), da_ref)
+    assert_grad_close(dw.cpu().numpy(), dw_ref)
+
+
+@pytest.mark.parametrize("name", ["relu_pruned_64x96x64", "edge_128x160x128"])
+def test_selection_count_golden(name, cuda):
+    g = load_golden(name)
+    imax = torch.from_numpy(g["argmax"]).to(torch.int32).to(cuda)
+    imin = torch.from_numpy(g["argmin"]).to(torch.int32).to(cuda)
+    K = g["a"].shape[1]
+    hmax, hmin = capi.selcount(imax, imin, K)
+    rmax, rmin = mam_oracle.selection_hits(torch.from_numpy(g["argmax"]), torch.from_numpy(g["argmin"]), K)
+    assert torch.equal(hmax.cpu(), rmax) and torch.equal(hmin.cpu(), rmin)
+    ind = (hmax > 0).int() + (hmin > 0).int()
+    assert np.array_equal(ind.cpu().numpy(), g["max_selection_count"])
+
+
+def test_selection_count_large(cuda):
+    M, K, N = 5000, 3072, 300
+    gen = torch.Generator().manual_seed(2)
+    imax = torch.randint(0, K, (M, N), generator=gen, dtype=torch.int32)
+    imin = torch.randint(0, K, (M, N), generator=gen, dtype=torch.int32)
+    hmax, hmin = capi.selcount(imax.to(cuda), imin.to(cuda), K)
+    rmax, rmin = mam_oracle.selection_hits(imax, imin, K)
+    assert torch.equal(hmax.cpu(), rmax) and torch.equal(hmin.cpu(), rmin)

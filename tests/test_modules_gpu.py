@@ -1,0 +1,184 @@
+"""The reference-facing Python surface on the GPU: torch.ops schemas under opcheck, autograd, the
+nn modules and the im2col convolution, checked against the oracle."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import assert_grad_close, load_golden
+from oracle import mam_oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def _rand(shape, seed, dev, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dev)
+
+
+@pytest.mark.parametrize("ns", ["mamtorch_kernel_v1", "mamtorch_kernel_v4"])
+def test_opcheck_plain_ops(ns, cuda):
+    import mamtorch_b200  # noqa: F401
+
+    a = _rand((37, 52), 1, cuda).requires_grad_()
+    b = _rand((52, 29), 2, cuda).requires_grad_()
+    ops = getattr(torch.ops, ns)
+    torch.library.opcheck(ops.fullyconnected, (a, b))
+    if ns.endswith("v4"):
+        torch.library.opcheck(ops.fullyconnected_fast, (a.detach(), b.detach()))
+    c, imax, imin = ops.fullyconnected(a.detach(), b.detach())
+    torch.library.opcheck(ops.fullyconnected_backward, (a.detach(), b.detach(), torch.ones_like(c), imax, imin))
+
+
+@pytest.mark.parametrize("ns", ["mamtorch_kernel_v2", "mamtorch_kernel_v3"])
+def test_blended_ops_match_reference_formula(ns, cuda):
+    import mamtorch_b200  # noqa: F401
+
+    g = load_golden("blend_40x64x48")
+    a, b, bias, grad = (torch.from_numpy(g[k]).to(cuda) for k in ("a", "b", "bias", "g"))
+    beta = float(g["beta"])
+    ops = getattr(torch.ops, ns)
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        c, imax, imin = ops.fullyconnected(a, b, bias, beta)
+        da, db = ops.fullyconnected_backward(a, b, grad, imax, imin, beta)
+        if ns.endswith("v3"):
+            cf = ops.fullyconnected_fast(a, b, bias, beta)
+            assert torch.equal(cf, c)
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+    assert np.array_equal(imax.cpu().numpy(), g["argmax"]) and np.array_equal(imin.cpu().numpy(), g["argmin"])
+    np.testing.assert_allclose(c.cpu().numpy(), g["y"], rtol=1e-5, atol=1e-5)
+    assert_grad_close(da.cpu().numpy(), g["agrad"])
+    assert_grad_close(db.cpu().numpy(), g["bgrad"])
+
+
+def test_autograd_through_v4_wrapper(cuda):
+    import mamtorch_b200 as mamtorch
+
+    g = load_golden("random_37x70x29")
+    a = torch.from_numpy(g["a"]).to(cuda).requires_grad_()
+    b = torch.from_numpy(g["b"]).to(cuda).requires_grad_()
+    c, imax, imin = mamtorch.kernel.v4.fullyconnected(a, b)
+    assert torch.equal(c.detach().cpu(), torch.from_numpy(g["y"]))
+    c.backward(torch.from_numpy(g["g"]).to(cuda))
+    assert_grad_close(a.grad.cpu().numpy(), g["agrad"])
+    assert_grad_close(b.grad.cpu().numpy(), g["bgrad"])
+
+
+def test_fullyconnected_module_matches_oracle(cuda):
+    import mamtorch_b200 as mamtorch
+
+    torch.manual_seed(0)
+    layer = mamtorch.nn.FullyConnected(96, 40, store_args=True).to(cuda)
+    x = _rand((3, 17, 96), 4, cuda).requires_grad_()
+    y = layer(x)
+    y_ref, imax_ref, imin_ref = mam_oracle.mam_forward(x.detach().reshape(-1, 96).cpu(),
+                                                       layer.weight.detach().T.contiguous().cpu(),
+                                                       layer.bias.detach().cpu())
+    assert y.shape == (3, 17, 40)
+    assert torch.equal(y.detach().reshape(-1, 40).cpu(), y_ref)
+    assert torch.equal(layer.argmax.cpu().long(), imax_ref) and torch.equal(layer.argmin.cpu().long(), imin_ref)
+    gy = _rand((3, 17, 40), 5, cuda)
+    y.backward(gy)
+    da_ref, db_ref = mam_oracle.mam_backward(x.detach().reshape(-1, 96).cpu(), layer.weight.detach().T.cpu(),
+                                             gy.reshape(-1, 40).cpu(), imax_ref, imin_ref)
+    assert_grad_close(x.grad.reshape(-1, 96).cpu().numpy(), da_ref.numpy())
+    assert_grad_close(layer.weight.grad.cpu().numpy(), db_ref.T.numpy())
+    assert_grad_close(layer.bias.grad.cpu().numpy(), gy.reshape(-1, 40).sum(0).cpu().numpy())
+    # selection count: two calls accumulate, exactly as the reference module's update does
+    layer.update_selection_count()
+    layer.update_selection_count()
+    want = mam_oracle.selection_count_update(torch.zeros(40, 96, dtype=torch.int32), imax_ref, imin_ref)
+    want = mam_oracle.selection_count_update(want, imax_ref, imin_ref)
+    assert torch.equal(layer.max_selection_count.cpu(), want)
+    assert int(layer.min_selection_count.abs().sum()) == 0
+    # eval mode without stored args uses the values-only kernel and gives the same numbers
+    layer2 = mamtorch.nn.FullyConnected(96, 40).to(cuda).eval()
+    layer2.load_state_dict(layer.state_dict())
+    with torch.no_grad():
+        assert torch.equal(layer2(x.detach()), y.detach())
+
+
+def test_module_beta_blend_splits_and_relu(cuda):
+    import mamtorch_b200 as mamtorch
+
+    torch.manual_seed(1)
+    x = _rand((50, 64), 6, cuda)
+    layer = mamtorch.nn.FullyConnected(64, 24, vcon_steps=4, relu_in=True).to(cuda)
+    layer.vcon_step()  # beta 0.75
+    y = layer(x)
+    xr = torch.relu(x).cpu()
+    y_ref, _, _ = mam_oracle.mam_forward(xr, layer.weight.detach().T.contiguous().cpu(), layer.bias.detach().cpu(), 0.75)
+    np.testing.assert_allclose(y.detach().cpu().numpy(), y_ref.numpy(), rtol=1e-4, atol=1e-5)
+    y.sum().backward()
+    assert layer.weight.grad is not None and torch.isfinite(layer.weight.grad).all()
+    # K cut into 3 slices: the sum of the three per-slice (max+min) terms
+    sp = mamtorch.nn.FullyConnected(64, 24, splits=3, bias=False).to(cuda)
+    ys = sp(x)
+    w = sp.weight.detach().cpu()
+    want = 0
+    for s0, width in [(0, 22), (22, 22), (44, 20)]:
+        part, _, _ = mam_oracle.mam_forward(x.cpu()[:, s0:s0 + width], w[:, s0:s0 + width].T.contiguous())
+        want = want + part
+    np.testing.assert_allclose(ys.detach().cpu().numpy(), want.numpy(), rtol=1e-6, atol=1e-6)
+
+
+def test_v1_module_and_mamdense(cuda):
+    import mamtorch_b200 as mamtorch
+
+    x = _rand((9, 32), 7, cuda)
+    for layer in (mamtorch.nn.v1.FullyConnected(32, 12).to(cuda), mamtorch.MAMDense(32, 12).to(cuda)):
+        y = layer(x)
+        bias = layer.bias.detach().cpu()
+        y_ref, imax, imin = mam_oracle.mam_forward(x.cpu(), layer.weight.detach().T.contiguous().cpu(), bias)
+        assert torch.equal(y.detach().cpu(), y_ref)
+        assert torch.equal(layer.argmax.cpu().long(), imax)
+        layer.update_selection_count()
+        assert int(layer.max_selection_count.sum()) > 0
+
+
+def test_conv2d_matches_im2col_oracle(cuda):
+    import mamtorch_b200 as mamtorch
+
+    torch.manual_seed(2)
+    conv = mamtorch.nn.MAMConv2d(5, 7, 3, padding=1).to(cuda)
+    x = _rand((2, 5, 9, 8), 8, cuda).requires_grad_()
+    y = conv(x)
+    y_ref, imax_ref, imin_ref = mam_oracle.mam_conv2d_forward(x.detach().cpu(), conv.weight.detach().cpu(),
+                                                              conv.bias.detach().cpu(), stride=1, padding=1)
+    assert y.shape == (2, 7, 9, 8)
+    assert torch.equal(y.detach().cpu(), y_ref)
+    assert torch.equal(conv.argmax.cpu().long(), imax_ref) and torch.equal(conv.argmin.cpu().long(), imin_ref)
+    y.sum().backward()
+    assert x.grad.shape == x.shape and conv.weight.grad.shape == conv.weight.shape
+    # gradient check against autograd through the oracle's selected products
+    xw = x.detach().cpu().requires_grad_()
+    ww = conv.weight.detach().cpu().requires_grad_()
+    rows = mam_oracle.conv2d_as_rows(xw, (3, 3), padding=1)
+    wf = ww.reshape(7, -1)
+    im = imax_ref.permute(0, 2, 3, 1).reshape(-1, 7)
+    imn = imin_ref.permute(0, 2, 3, 1).reshape(-1, 7)
+    r = torch.arange(rows.shape[0])[:, None].expand_as(im)
+    c = torch.arange(7)[None, :].expand_as(im)
+    (rows[r, im] * wf[c, im] + rows[r, imn] * wf[c, imn]).sum().backward()
+    assert_grad_close(x.grad.cpu().numpy(), xw.grad.numpy())
+    assert_grad_close(conv.weight.grad.cpu().numpy(), ww.grad.numpy())
+    conv.update_selection_count()
+    assert conv.max_selection_count.shape == conv.weight.shape and int(conv.max_selection_count.sum()) > 0
+
+
+def test_conv1d(cuda):
+    import mamtorch_b200 as mamtorch
+
+    conv = mamtorch.nn.MAMConv1d(4, 6, 3, padding=1, bias=False).to(cuda)
+    x = _rand((3, 4, 11), 9, cuda)
+    y = conv(x)
+    y_ref, imax_ref, _ = mam_oracle.mam_conv2d_forward(x.cpu().unsqueeze(2), conv.weight.detach().cpu().unsqueeze(2),
+                                                       stride=1, padding=0) if False else (None, None, None)
+    xp = torch.nn.functional.pad(x.cpu(), (1, 1))
+    w = conv.weight.detach().cpu()
+    for (b_, f, t) in [(0, 0, 0), (2, 5, 10), (1, 3, 4)]:
+        p = (xp[b_, :, t:t + 3] * w[f]).reshape(-1)
+        assert y[b_, f, t].item() == (p.max() + p.min()).item()
+        assert conv.argmax[b_, f, t].item() == int(p.argmax())
