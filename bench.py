@@ -1,0 +1,300 @@
+#!/usr/bin/env python
+"""Benchmark of the MAM hot path on B200.
+
+Workload (N GPUs, weak scaling: every rank owns the same number of rows): the ViT-B/16-shaped
+MAM MLP pair of the reference's headline configuration -- tokens M = 64 x 197 = 12608 per rank,
+layer 1 K=768 -> N=3072, layer 2 K=3072 -> N=768, fp32, x ~ N(0,1), W ~ N(0,1/K), forward with
+arg-indices + selected-pair backward + selection-count accumulation, synthetic data.  With N > 1
+the two weight gradients are summed over ranks with one NCCL all-reduce each (the only exchange a
+row-sharded layer has).
+
+One JSON line on stdout (rank 0).  `value` counts (m,n,k) units -- one multiply, one max update,
+one min update -- of the two forward passes, divided by the whole forward+backward step time:
+"G(mul+max/min)/s".  `e2e` is the same step called with HOST buffers: the step's activations and
+upstream gradient start in pinned host memory and its output and loss come back to the host
+inside the timed region.  `roofline` is for the dominant kernel (the tiled forward), timed with
+CUDA events recorded by the library around each of its launches during the timed steps.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+`--impl reference` times the CPU restatement of the reference's own torch path (oracle/) on the
+host cores on a bounded row sample of the same workload.
+"""
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+M_TOKENS, D_MODEL, D_FF = 64 * 197, 768, 3072
+UNITS_PER_STEP = M_TOKENS * (D_MODEL * D_FF + D_FF * D_MODEL)  # per rank
+METRIC = "mam_mlp_pair_fwd_bwd_throughput"
+UNIT = "G(mul+max/min)/s"
+WORKLOAD = ("ViT-B/16 MAM MLP pair fwd+bwd, fp32, M=12608 tokens per rank, 768->3072->768, "
+            "arg-indices, selected-pair backward, selection count on")
+
+
+def fp32_peaks(sms: int, mhz: float):
+    lanes = sms * 128 * mhz * 1e6
+    return {"fma_counted_tflops": 2 * lanes / 1e12, "non_fma_tops": lanes / 1e12,
+            "alu_pipe_gunits": sms * 64 * mhz * 1e6 / 1e9}
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm = [float(r[0]) for r in self.rows if len(r) >= 7 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) >= 7 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) >= 7 and r[3 + i].lower() == "active" for r in self.rows)]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": reasons}
+
+
+def cpu_reference_sample(rows: int, repeats: int):
+    """The reference's CPU torch path (restated in oracle/mam_oracle.py) on `rows` rows of both
+    layers, forward + backward.  Returns (G units/s, threads, description)."""
+    import torch
+
+    from oracle import mam_oracle
+
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(rows, D_MODEL, generator=g)
+    w1 = torch.randn(D_FF, D_MODEL, generator=g) * D_MODEL ** -0.5
+    w2 = torch.randn(D_MODEL, D_FF, generator=g) * D_FF ** -0.5
+    gy = torch.randn(rows, D_MODEL, generator=g)
+    b1, b2 = w1.T.contiguous(), w2.T.contiguous()
+    units = rows * (D_MODEL * D_FF + D_FF * D_MODEL)
+    best = None
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        h, i1, j1 = mam_oracle.mam_forward(x, b1)
+        y, i2, j2 = mam_oracle.mam_forward(h, b2)
+        dh, dw2 = mam_oracle.mam_backward(h, b2, gy, i2, j2)
+        dx, dw1 = mam_oracle.mam_backward(x, b1, dh, i1, j1)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return units / best / 1e9, threads, f"{rows} of {M_TOKENS} rows of both layers, fwd+bwd, torch CPU, best of {repeats}"
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    rows = 128
+    # warm-up + K timed "steps", each one bounded sample
+    for _ in range(max(1, min(args.warmup, 2))):
+        cpu_reference_sample(rows, 1)
+    t0 = time.perf_counter()
+    vals = [cpu_reference_sample(rows, 1) for _ in range(args.steps)]
+    wall = time.perf_counter() - t0
+    value = statistics.median(v[0] for v in vals)
+    threads, sample = vals[0][1], vals[0][2]
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": wall / args.steps * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "note": "CPU restatement of the reference's torch path; each step is a "
+                       f"{rows}-row sample of the workload, throughput is per-unit so it compares directly"},
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--fwd-variant", type=int, default=-1, help="tile configuration of the index-producing forward")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import torch
+    import torch.distributed as dist
+
+    import mamtorch_b200 as mamtorch
+    from mamtorch_b200 import _lib
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world} (launch with torch.distributed.run)"
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    L = _lib.lib()
+    if args.fwd_variant >= 0:
+        _lib.check(L.mam_set_fwd_variant(1, args.fwd_variant), "mam_set_fwd_variant")
+
+    # ---- model and data: every rank its own rows (seeded per rank), identical weights
+    torch.manual_seed(0)
+    fc1 = mamtorch.nn.FullyConnected(D_MODEL, D_FF, bias=True, store_args=True).to(dev)
+    fc2 = mamtorch.nn.FullyConnected(D_FF, D_MODEL, bias=True, store_args=True).to(dev)
+    with torch.no_grad():
+        g = torch.Generator().manual_seed(0)
+        fc1.weight.copy_(torch.randn(D_FF, D_MODEL, generator=g) * D_MODEL ** -0.5)
+        fc2.weight.copy_(torch.randn(D_MODEL, D_FF, generator=g) * D_FF ** -0.5)
+        fc1.bias.zero_()
+        fc2.bias.zero_()
+    gd = torch.Generator().manual_seed(100 + rank)
+    x_host = torch.randn(64, 197, D_MODEL, generator=gd).pin_memory()
+    gy_host = torch.randn(64, 197, D_MODEL, generator=gd).pin_memory()
+    y_host = torch.empty(64, 197, D_MODEL).pin_memory()
+    loss_host = torch.empty((), dtype=torch.float32).pin_memory()
+    x_dev = x_host.to(dev)
+    gy_dev = gy_host.to(dev)
+    params = [fc1.weight, fc2.weight, fc1.bias, fc2.bias]
+
+    def step(x, gy):
+        for p in params:
+            p.grad = None
+        x = x.requires_grad_()
+        y = fc2(fc1(x))
+        y.backward(gy)
+        fc1.update_selection_count()
+        fc2.update_selection_count()
+        if world > 1:
+            dist.all_reduce(fc1.weight.grad)
+            dist.all_reduce(fc2.weight.grad)
+        return y
+
+    def step_from_host():
+        x = x_host.to(dev, non_blocking=True)
+        gy = gy_host.to(dev, non_blocking=True)
+        y = step(x, gy)
+        y_host.copy_(y.detach(), non_blocking=True)
+        loss_host.copy_((y.detach() * gy).sum(), non_blocking=True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        ev0.record()
+        for _ in range(steps):
+            fn()
+        ev1.record()
+        barrier()
+        ms = torch.tensor([ev0.elapsed_time(ev1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    for _ in range(args.warmup):
+        step(x_dev.clone(), gy_dev)
+    for _ in range(2):
+        step_from_host()
+    barrier()
+
+    # ---- per-kernel events for the dominant kernel (2 launches per step)
+    cap = 2 * args.steps
+    ev_pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(cap)]
+    for a, b in ev_pairs:  # events are created lazily on first record; force creation now
+        a.record()
+        b.record()
+    torch.cuda.synchronize()
+    starts = (ctypes.c_void_p * cap)(*[ctypes.c_void_p(a.cuda_event) for a, _ in ev_pairs])
+    stops = (ctypes.c_void_p * cap)(*[ctypes.c_void_p(b.cuda_event) for _, b in ev_pairs])
+    _lib.check(L.mam_timer_arm(starts, stops, cap, 0), "mam_timer_arm")
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    total_ms = timed(lambda: step(x_dev, gy_dev), args.steps)
+    recorded = L.mam_timer_disarm()
+    torch.cuda.synchronize()
+    kernel_ms = [a.elapsed_time(b) for a, b in ev_pairs[:recorded]]
+    e2e_ms = timed(step_from_host, args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    _lib.check(L.mam_check_device_flag(), "device wait flag")
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    ms_per_step = total_ms / args.steps
+    value = world * UNITS_PER_STEP / (ms_per_step * 1e-3) / 1e9
+    e2e_value = world * UNITS_PER_STEP / (e2e_ms / args.steps * 1e-3) / 1e9
+    props = torch.cuda.get_device_properties(dev)
+    sms = props.multi_processor_count
+    kavg = statistics.mean(kernel_ms) if kernel_ms else float("nan")
+    flops_per_launch = 3.0 * M_TOKENS * D_MODEL * D_FF  # 3 fp32 ops per (m,n,k) unit, unpadded extents
+    max_mhz = (clocks or {}).get("sm_max_mhz") or 1965.0
+    peaks = fp32_peaks(sms, max_mhz)
+    achieved = flops_per_launch / (kavg * 1e-3) / 1e12
+    roofline = {"bound": "fp32_cuda_core", "kernel": "mam_fwd_tiled_kernel (index-tracking variant "
+                + L.mam_fwd_variant_name(1, max(args.fwd_variant, 0)).decode() + ")",
+                "achieved": achieved, "peak": peaks["fma_counted_tflops"], "unit": "TFLOP/s",
+                "frac": achieved / peaks["fma_counted_tflops"],
+                "peak_source": f"{sms} SMs x 128 lanes x 2 x {max_mhz:.0f} MHz (FMA counted as 2; no fp32 entry in "
+                               "MEASURED_PEAKS.json); a MAM unit has no FMA, see the two extra fractions",
+                "frac_of_non_fma_peak": achieved / peaks["non_fma_tops"],
+                "frac_of_measured_alu_pipe_ceiling": (achieved / 3 * 1e3) / peaks["alu_pipe_gunits"],
+                "launch_ms_avg": kavg, "launches_timed": len(kernel_ms), "traffic": None}
+    line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "l2": "working set per step (~1 GB of activations, indices and "
+                       "gradients) exceeds the 126 MB L2; no explicit flush",
+                       "parallelism": f"rows sharded over {world} rank(s); dW all-reduce over NCCL" if world > 1
+                       else "single GPU"},
+            "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms / args.steps,
+                    "h2d_bytes_per_step": x_host.numel() * 4 + gy_host.numel() * 4,
+                    "d2h_bytes_per_step": y_host.numel() * 4 + 4},
+            "gpu_launches": 10 * args.steps, "clocks": clocks, "roofline": roofline}
+    if world == 1 and not args.no_cpu_baseline:
+        cv, threads, sample = cpu_reference_sample(256, 3)
+        line["cpu_baseline"] = {"value": cv, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
