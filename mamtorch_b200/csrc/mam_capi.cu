@@ -86,8 +86,9 @@ int get_encode() {
     return MAM_OK;
 }
 
-// [rows, K] fp32 row-major matrix -> boxes of [box_rows][32 floats], 128-byte swizzle, zero fill.
-int encode_rows_k(CUtensorMap* tm, const float* base, long long rows, long long K, int box_rows) {
+// [rows, K] fp32 row-major matrix -> boxes of [box_rows][32 floats], 128-byte swizzle (or none), zero fill.
+int encode_rows_k(CUtensorMap* tm, const float* base, long long rows, long long K, int box_rows,
+                  bool swizzle = true) {
     int st = get_encode();
     if (st != MAM_OK) return st;
     cuuint64_t gdim[2] = {(cuuint64_t)K, (cuuint64_t)rows};
@@ -95,7 +96,8 @@ int encode_rows_k(CUtensorMap* tm, const float* base, long long rows, long long 
     cuuint32_t box[2] = {(cuuint32_t)FWD_BK, (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = g_encode(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), gdim, gstr, box,
-                          estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return cuda_fail(cudaErrorInvalidValue);
     return MAM_OK;
@@ -121,21 +123,32 @@ int launch_tiled(const float* a, const float* w, const FwdParams& prm, const Dev
     return MAM_OK;
 }
 
-//                         TM TN WM WN ST track
-using ValCfg0 = FwdCfg<8, 8, 4, 2, 4, false>;   // 128x128 tile, 256 consumers
-using ValCfg1 = FwdCfg<4, 8, 8, 2, 4, false>;   // 128x128 tile, 512 consumers
-using ValCfg2 = FwdCfg<8, 4, 4, 4, 4, false>;   // 128x128 tile, 512 consumers
-using ValCfg3 = FwdCfg<4, 4, 8, 2, 6, false>;   // 128x64 tile, 512 consumers
-using IdxCfg0 = FwdCfg<4, 8, 4, 2, 4, true>;    // 64x128 tile, 256 consumers
-using IdxCfg1 = FwdCfg<4, 4, 8, 2, 4, true>;    // 128x64 tile, 512 consumers
-using IdxCfg2 = FwdCfg<8, 4, 2, 4, 4, true>;    // 64x128 tile, 256 consumers
-using IdxCfg3 = FwdCfg<4, 4, 4, 4, 4, true>;    // 64x128 tile, 512 consumers
-constexpr int N_VARIANTS = 4;
-const char* kValNames[N_VARIANTS] = {"val_8x8_128x128_c256", "val_4x8_128x128_c512", "val_8x4_128x128_c512",
-                                     "val_4x4_128x64_c512"};
-const char* kIdxNames[N_VARIANTS] = {"idx_4x8_64x128_c256", "idx_4x4_128x64_c512", "idx_8x4_64x128_c256",
-                                     "idx_4x4_64x128_c512"};
+//                         TM TN WM WN ST track UQ batch
+using ValCfg0 = FwdCfg<8, 8, 4, 2, 4, false, 8, false>;  // 128x128 tile, 256 threads
+using ValCfg1 = FwdCfg<8, 8, 4, 2, 4, false, 2, false>;
+using ValCfg2 = FwdCfg<8, 8, 4, 2, 4, false, 1, false>;
+using ValCfg3 = FwdCfg<8, 8, 4, 2, 4, false, 2, true>;
+using ValCfg4 = FwdCfg<4, 8, 4, 2, 4, false, 8, false>;  // 64x128 tile, 256 threads
+using ValCfg5 = FwdCfg<4, 8, 4, 2, 4, false, 2, false>;
+using ValCfg6 = FwdCfg<4, 8, 4, 2, 4, false, 2, true>;
+using ValCfg7 = FwdCfg<8, 4, 2, 4, 4, false, 2, true>;   // 64x128 tile, 256 threads, A-heavy
+using IdxCfg0 = FwdCfg<4, 8, 4, 2, 4, true, 8, false>;   // 64x128 tile, 256 threads
+using IdxCfg1 = FwdCfg<4, 8, 4, 2, 4, true, 2, false>;
+using IdxCfg2 = FwdCfg<4, 8, 4, 2, 4, true, 1, false>;
+using IdxCfg3 = FwdCfg<4, 8, 4, 2, 4, true, 2, true>;
+using IdxCfg4 = FwdCfg<8, 4, 2, 4, 4, true, 8, false>;   // 64x128 tile, 256 threads, A-heavy
+using IdxCfg5 = FwdCfg<8, 4, 2, 4, 4, true, 2, false>;
+using IdxCfg6 = FwdCfg<4, 4, 4, 4, 4, true, 4, false>;   // 64x128 tile, 512 threads
+using IdxCfg7 = FwdCfg<4, 4, 4, 4, 4, true, 2, true>;
+constexpr int N_VARIANTS = 8;
+const char* kValNames[N_VARIANTS] = {"val_8x8_t128x128_c256_u8", "val_8x8_t128x128_c256_u2", "val_8x8_t128x128_c256_u1",
+                                     "val_8x8_t128x128_c256_u2b", "val_4x8_t64x128_c256_u8", "val_4x8_t64x128_c256_u2",
+                                     "val_4x8_t64x128_c256_u2b", "val_8x4_t64x128_c256_u2b"};
+const char* kIdxNames[N_VARIANTS] = {"idx_4x8_t64x128_c256_u8", "idx_4x8_t64x128_c256_u2", "idx_4x8_t64x128_c256_u1",
+                                     "idx_4x8_t64x128_c256_u2b", "idx_8x4_t64x128_c256_u8", "idx_8x4_t64x128_c256_u2",
+                                     "idx_4x4_t64x128_c512_u4", "idx_4x4_t64x128_c512_u2b"};
 int g_variant[2] = {-1, -1};  // [with_indices]
+int g_resolve_simple = 0;      // 1: use the thread-per-output resolver (cross-check)
 
 int bad_ptr(const void* p) { return p == nullptr; }
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -191,6 +204,10 @@ int mam_timer_disarm(void) {
 }
 
 int mam_set_fwd_variant(int with_indices, int variant) {
+    if (with_indices == 2) {  // selects the index resolver: 0 tiled (default), 1 thread-per-output
+        g_resolve_simple = variant ? 1 : 0;
+        return MAM_OK;
+    }
     if (variant < -2 || variant >= N_VARIANTS) return MAM_ERR_INVALID_ARGUMENT;
     g_variant[with_indices ? 1 : 0] = variant;
     return MAM_OK;
@@ -235,7 +252,22 @@ int mam_fwd_f32(const float* a, const float* b, int b_layout, const float* bias,
 
     int variant = g_variant[want_idx ? 1 : 0];
     const bool tma_ok = (K % 4 == 0) && aligned16(a) && aligned16(b) && K / FWD_BK < 65535;
-    if (variant == -1) variant = (tma_ok && M * N >= 4096) ? 0 : -2;
+    if (variant == -1) {
+        if (!(tma_ok && M * N >= 4096)) {
+            variant = -2;
+        } else if (want_idx) {
+            variant = 1;  // 4x8 outputs per thread, 64x128 tile
+        } else {
+            // 8x8 per thread on 128x128 tiles is ~10% faster per unit than 4x8 on 64x128 tiles, but its
+            // last wave of tiles can leave most SMs idle: weigh both by their wave efficiency
+            auto eff = [&](long long bm, long long bn) {
+                const long long tiles = ((M + bm - 1) / bm) * ((N + bn - 1) / bn);
+                const long long waves = (tiles + d->sms - 1) / d->sms;
+                return (double)tiles / (double)(waves * d->sms);
+            };
+            variant = (eff(128, 128) * 1.10 >= eff(64, 128)) ? 2 : 6;
+        }
+    }
     if (variant >= 0 && !tma_ok) variant = -2;
 
     if (variant == -2) {
@@ -268,7 +300,11 @@ int mam_fwd_f32(const float* a, const float* b, int b_layout, const float* bias,
             case 0: st = launch_tiled<ValCfg0>(a, w, prm, *d, cs); break;
             case 1: st = launch_tiled<ValCfg1>(a, w, prm, *d, cs); break;
             case 2: st = launch_tiled<ValCfg2>(a, w, prm, *d, cs); break;
-            default: st = launch_tiled<ValCfg3>(a, w, prm, *d, cs); break;
+            case 3: st = launch_tiled<ValCfg3>(a, w, prm, *d, cs); break;
+            case 4: st = launch_tiled<ValCfg4>(a, w, prm, *d, cs); break;
+            case 5: st = launch_tiled<ValCfg5>(a, w, prm, *d, cs); break;
+            case 6: st = launch_tiled<ValCfg6>(a, w, prm, *d, cs); break;
+            default: st = launch_tiled<ValCfg7>(a, w, prm, *d, cs); break;
         }
         return st;
     }
@@ -276,13 +312,31 @@ int mam_fwd_f32(const float* a, const float* b, int b_layout, const float* bias,
         case 0: st = launch_tiled<IdxCfg0>(a, w, prm, *d, cs); break;
         case 1: st = launch_tiled<IdxCfg1>(a, w, prm, *d, cs); break;
         case 2: st = launch_tiled<IdxCfg2>(a, w, prm, *d, cs); break;
-        default: st = launch_tiled<IdxCfg3>(a, w, prm, *d, cs); break;
+        case 3: st = launch_tiled<IdxCfg3>(a, w, prm, *d, cs); break;
+        case 4: st = launch_tiled<IdxCfg4>(a, w, prm, *d, cs); break;
+        case 5: st = launch_tiled<IdxCfg5>(a, w, prm, *d, cs); break;
+        case 6: st = launch_tiled<IdxCfg6>(a, w, prm, *d, cs); break;
+        default: st = launch_tiled<IdxCfg7>(a, w, prm, *d, cs); break;
     }
     if (st != MAM_OK) return st;
-    const long long total = M * N;
-    const long long blocks = (total + 255) / 256;
-    if (blocks > 2147483647LL) return MAM_ERR_UNSUPPORTED;
-    {
+    const int nkc = (int)((K + FWD_BK - 1) / FWD_BK);
+    if (nkc <= ResolveCfg::NK_MAX && g_resolve_simple == 0) {
+        CUtensorMap tmA, tmW;
+        st = encode_rows_k(&tmA, a, M, K, ResolveCfg::RM, false);
+        if (st != MAM_OK) return st;
+        st = encode_rows_k(&tmW, w, N, K, ResolveCfg::RN, false);
+        if (st != MAM_OK) return st;
+        const long long tiles = ((M + ResolveCfg::RM - 1) / ResolveCfg::RM) * ((N + ResolveCfg::RN - 1) / ResolveCfg::RN);
+        if (tiles > 2147483647LL) return MAM_ERR_UNSUPPORTED;
+        MAM_CUDA(cudaFuncSetAttribute(mam_resolve_tiled_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      ResolveCfg::SMEM_BYTES));
+        TimedLaunch t(MAM_KERNEL_FWD_RESOLVE, cs);
+        mam_resolve_tiled_kernel<<<(unsigned)tiles, ResolveCfg::THREADS, ResolveCfg::SMEM_BYTES, cs>>>(
+            tmA, tmW, argmax, argmin, M, K, N, flag);
+    } else {
+        const long long total = M * N;
+        const long long blocks = (total + 255) / 256;
+        if (blocks > 2147483647LL) return MAM_ERR_UNSUPPORTED;
         TimedLaunch t(MAM_KERNEL_FWD_RESOLVE, cs);
         mam_resolve_kernel<<<(unsigned)blocks, 256, 0, cs>>>(a, w, argmax, argmin, M, K, N);
     }

@@ -30,8 +30,10 @@ namespace mamb200 {
 
 constexpr int FWD_BK = 32;  // floats per row per stage = one 128-byte swizzle span
 
-template <int TM_, int TN_, int WM_, int WN_, int STAGES_, bool TRACK_>
+template <int TM_, int TN_, int WM_, int WN_, int STAGES_, bool TRACK_, int UQ_ = 8, bool BATCH_ = false>
 struct FwdCfg {
+    static constexpr int UQ = UQ_;          // 16-byte k groups per unrolled loop body
+    static constexpr bool BATCH = BATCH_;   // form all products of a W row before any max/min
     static constexpr int TM = TM_, TN = TN_, WM = WM_, WN = WN_, STAGES = STAGES_;
     static constexpr bool TRACK = TRACK_;
     static constexpr int BM = WM * 4 * TM;   // rows of a per tile
@@ -176,37 +178,45 @@ mam_fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
 #pragma unroll
                 for (int j = 0; j < TN; ++j) {
                     const ulonglong2 wv = lds128(wp + xw + j * 1024);
+                    float p[TM][4];
+                    if constexpr (Cfg::BATCH) {
+#pragma unroll
+                        for (int i = 0; i < TM; ++i) {
+                            unpack2(mul2(av[i].x, wv.x), p[i][0], p[i][1]);
+                            unpack2(mul2(av[i].y, wv.y), p[i][2], p[i][3]);
+                        }
+                    }
 #pragma unroll
                     for (int i = 0; i < TM; ++i) {
-                        float p0, p1, p2, p3;
-                        unpack2(mul2(av[i].x, wv.x), p0, p1);
-                        unpack2(mul2(av[i].y, wv.y), p2, p3);
+                        if constexpr (!Cfg::BATCH) {
+                            unpack2(mul2(av[i].x, wv.x), p[i][0], p[i][1]);
+                            unpack2(mul2(av[i].y, wv.y), p[i][2], p[i][3]);
+                        }
                         if constexpr (TRACK) {
                             if (first) {
-                                lmax[i][j] = fmaxf(p0, p1);
-                                lmin[i][j] = fminf(p0, p1);
+                                lmax[i][j] = fmaxf(p[i][0], p[i][1]);
+                                lmin[i][j] = fminf(p[i][0], p[i][1]);
                             } else {
-                                lmax[i][j] = fmax3(lmax[i][j], p0, p1);
-                                lmin[i][j] = fmin3(lmin[i][j], p0, p1);
+                                lmax[i][j] = fmax3(lmax[i][j], p[i][0], p[i][1]);
+                                lmin[i][j] = fmin3(lmin[i][j], p[i][0], p[i][1]);
                             }
-                            lmax[i][j] = fmax3(lmax[i][j], p2, p3);
-                            lmin[i][j] = fmin3(lmin[i][j], p2, p3);
+                            lmax[i][j] = fmax3(lmax[i][j], p[i][2], p[i][3]);
+                            lmin[i][j] = fmin3(lmin[i][j], p[i][2], p[i][3]);
                         } else {
-                            vmax[i][j] = fmax3(fmax3(vmax[i][j], p0, p1), p2, p3);
-                            vmin[i][j] = fmin3(fmin3(vmin[i][j], p0, p1), p2, p3);
+                            vmax[i][j] = fmax3(fmax3(vmax[i][j], p[i][0], p[i][1]), p[i][2], p[i][3]);
+                            vmin[i][j] = fmin3(fmin3(vmin[i][j], p[i][0], p[i][1]), p[i][2], p[i][3]);
                         }
                     }
                 }
             };
 
-            if (kc + 1 < nk || tail_quads == FWD_BK / 4) {
-                quad(0, true);
-#pragma unroll
-                for (int q = 1; q < FWD_BK / 4; ++q) quad(q, false);
-            } else {
-                quad(0, true);
-                for (int q = 1; q < tail_quads; ++q) quad(q, false);
-            }
+            // one code path for full and ragged chunks: the first group is peeled (it initialises
+            // the chunk-local extremes), the rest run in a loop unrolled UQ groups at a time so
+            // that the body stays inside the instruction cache
+            const int nq = (kc + 1 < nk) ? FWD_BK / 4 : tail_quads;
+            quad(0, true);
+#pragma unroll(Cfg::UQ)
+            for (int q = 1; q < nq; ++q) quad(q, false);
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty_bar[stage]);
             if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -266,6 +276,218 @@ mam_fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                 }
             }
         }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Index resolution, tiled: chunk ids -> exact lowest-k indices.
+//
+// Every output carries two tasks (its max chunk and its min chunk); a task rescans one 32-wide
+// chunk of one a-row against one W-row.  A CTA owns an RM x RN tile of outputs.  It counting-sorts
+// the tile's 2*RM*RN tasks by chunk in shared memory (integer shared-memory atomics), then
+// streams the tile's operand chunks through a TMA ring like the main kernel's, and for chunk c
+// its threads split the tasks of bucket c between them.
+//
+// Shared-memory bandwidth is the floor here (every task reads its own 2 x 128 bytes), so the
+// stage is NOT swizzled: lane L reads the eight 16-byte groups of its rows in the rotated order
+// (q + L) & 7, which puts the eight lanes of every quarter-warp on eight different bank groups
+// whatever rows they hold.  Group extremes therefore sit in rotated registers; the pick below
+// recovers the lowest true group index among those equal to the chunk extreme.
+// A min task negates its a-values (exact) and then runs the same max search as a max task.
+struct ResolveCfg {
+    static constexpr int RM = 64, RN = 128, STAGES = 2, THREADS = 256, WARPS = 8;
+    static constexpr int NK_MAX = 2048;  // K <= 65536
+    static constexpr int A_BYTES = RM * FWD_BK * 4, W_BYTES = RN * FWD_BK * 4;
+    static constexpr int STAGE_BYTES = A_BYTES + W_BYTES;
+    static constexpr int TASKS = 2 * RM * RN;
+    static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + 2 * STAGES * 8 + 64 + TASKS * 2 +
+                                      (2 * NK_MAX + 8) * 4;
+    static constexpr int LOOKAHEAD = STAGES - 1;
+};
+
+__global__ void __launch_bounds__(ResolveCfg::THREADS, 2)
+mam_resolve_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW,
+                         int* __restrict__ argmax, int* __restrict__ argmin,
+                         long long M, long long K, long long N, int* error) {
+    using C = ResolveCfg;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>(
+        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
+    uint64_t* empty_bar = full_bar + C::STAGES;
+    unsigned short* tasks = reinterpret_cast<unsigned short*>(smem + C::STAGES * C::STAGE_BYTES + 2 * C::STAGES * 8 + 64);
+    int* cursor = reinterpret_cast<int*>(tasks + C::TASKS);  // [nk]   running insert position
+    int* start = cursor + C::NK_MAX + 4;                      // [nk+1] bucket boundaries
+    __shared__ int warp_sums[C::WARPS];
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int nk = (int)((K + FWD_BK - 1) / FWD_BK);
+    const int tail_quads = (int)((K - (long long)(nk - 1) * FWD_BK) / 4);
+    const int ntn = (int)((N + C::RN - 1) / C::RN);
+    const long long m0 = (long long)(blockIdx.x / ntn) * C::RM, n0 = (long long)(blockIdx.x % ntn) * C::RN;
+
+    if (tid == 0) {
+        for (int s = 0; s < C::STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], C::WARPS);
+        }
+        mbar_fence_init();
+    }
+    for (int i = tid; i < nk; i += C::THREADS) cursor[i] = 0;
+    __syncthreads();
+
+    // producer state (thread 0)
+    int p_kc = 0, p_stage = 0;
+    uint32_t p_phase = 0;
+    auto produce_one = [&]() -> bool {
+        if (p_kc >= nk) return true;
+        if (!mbar_wait_bounded(&empty_bar[p_stage], p_phase ^ 1u)) return false;
+        mbar_expect_tx(&full_bar[p_stage], C::STAGE_BYTES);
+        unsigned char* sa = smem + p_stage * C::STAGE_BYTES;
+        tma_load_2d(sa, &tmA, &full_bar[p_stage], p_kc * FWD_BK, (int)m0);
+        tma_load_2d(sa + C::A_BYTES, &tmW, &full_bar[p_stage], p_kc * FWD_BK, (int)n0);
+        if (++p_stage == C::STAGES) { p_stage = 0; p_phase ^= 1u; }
+        ++p_kc;
+        return true;
+    };
+    if (tid == 0) {
+        tma_prefetch_desc(&tmA);
+        tma_prefetch_desc(&tmW);
+        for (int i = 0; i < C::LOOKAHEAD; ++i) produce_one();
+    }
+
+    // ---- pass A: count tasks per chunk
+    constexpr int PER_THREAD = C::RM * C::RN / C::THREADS;
+    for (int i = 0; i < PER_THREAD; ++i) {
+        const int o = i * C::THREADS + tid;
+        const long long m = m0 + o / C::RN, n = n0 + o % C::RN;
+        const bool in = m < M && n < N;
+        int c1 = 0, c2 = 0;
+        if (in) {
+            c1 = min(max(argmax[m * N + n], 0), nk - 1);
+            c2 = min(max(argmin[m * N + n], 0), nk - 1);
+        }
+        if (in) {
+            atomicAdd(&cursor[c1], 1);
+            atomicAdd(&cursor[c2], 1);
+        }
+    }
+    __syncthreads();
+    // ---- exclusive scan of the nk counts (nk <= NK_MAX = 8 * THREADS)
+    {
+        constexpr int PER = C::NK_MAX / C::THREADS;
+        int v[PER], sum = 0;
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            const int idx = tid * PER + i;
+            v[i] = idx < nk ? cursor[idx] : 0;
+            sum += v[i];
+        }
+        int incl = sum;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int t = __shfl_up_sync(0xffffffffu, incl, d);
+            if (lane >= d) incl += t;
+        }
+        if (lane == 31) warp_sums[warp] = incl;
+        __syncthreads();
+        int base = 0;
+        for (int w2 = 0; w2 < warp; ++w2) base += warp_sums[w2];
+        int run = base + incl - sum;
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            const int idx = tid * PER + i;
+            if (idx < nk) {
+                start[idx] = run;
+                cursor[idx] = run;
+            }
+            run += v[i];
+        }
+        if (tid == C::THREADS - 1) start[nk] = run;
+    }
+    __syncthreads();
+    // ---- pass B: scatter task codes into chunk order
+    for (int i = 0; i < PER_THREAD; ++i) {
+        const int o = i * C::THREADS + tid;
+        const long long m = m0 + o / C::RN, n = n0 + o % C::RN;
+        const bool in = m < M && n < N;
+        int c1 = 0, c2 = 0;
+        if (in) {
+            c1 = min(max(argmax[m * N + n], 0), nk - 1);
+            c2 = min(max(argmin[m * N + n], 0), nk - 1);
+        }
+        if (in) {
+            tasks[atomicAdd(&cursor[c1], 1)] = (unsigned short)(o << 1);
+            tasks[atomicAdd(&cursor[c2], 1)] = (unsigned short)((o << 1) | 1);
+        }
+    }
+    __syncthreads();
+
+    // ---- pass C: stream the chunks, resolve the tasks of each
+    int stage = 0;
+    uint32_t phase = 0;
+    for (int kc = 0; kc < nk; ++kc) {
+        if (tid == 0 && !produce_one()) atomicExch(error, 1);
+        if (!mbar_wait_bounded(&full_bar[stage], phase)) {
+            atomicExch(error, 1);
+            return;
+        }
+        const unsigned char* As = smem + stage * C::STAGE_BYTES;
+        const unsigned char* Ws = As + C::A_BYTES;
+        const int nq = (kc + 1 < nk) ? FWD_BK / 4 : tail_quads;
+        const int t_end = start[kc + 1];
+        for (int t = start[kc] + tid; t < t_end; t += C::THREADS) {
+            const unsigned code = tasks[t];
+            const int o = (int)(code >> 1);
+            const int ra = o / C::RN, rw = o % C::RN;
+            const float sgn = (code & 1u) ? -1.0f : 1.0f;
+            const f32x2_t sgn2 = pack2(sgn, sgn);
+            const unsigned char* ap = As + ra * 128;
+            const unsigned char* wp = Ws + rw * 128;
+            // rotated pass over the eight groups: register r holds true group (r + lane) & 7
+            float qm[FWD_BK / 4];
+#pragma unroll
+            for (int r = 0; r < FWD_BK / 4; ++r) {
+                const uint32_t off = (uint32_t)((r + lane) & 7) << 4;
+                const ulonglong2 av = lds128(ap + off);
+                const ulonglong2 wv = lds128(wp + off);
+                float p0, p1, p2, p3;
+                unpack2(mul2(mul2(av.x, sgn2), wv.x), p0, p1);
+                unpack2(mul2(mul2(av.y, sgn2), wv.y), p2, p3);
+                qm[r] = fmaxf(fmax3(p0, p1, p2), p3);
+            }
+            // groups at or beyond nq (ragged last chunk) hold zero fill: exclude them
+            float best = -INFINITY;
+#pragma unroll
+            for (int r = 0; r < FWD_BK / 4; ++r) {
+                const int gq = (r + lane) & 7;
+                if (gq >= nq) qm[r] = -INFINITY;
+                best = fmaxf(best, qm[r]);
+            }
+            int bq = FWD_BK / 4;
+#pragma unroll
+            for (int r = 0; r < FWD_BK / 4; ++r) {
+                const int gq = (r + lane) & 7;
+                if (qm[r] == best) bq = min(bq, gq);
+            }
+            bq = min(bq, nq - 1);  // only reachable when every product is NaN
+            // first element of group bq equal to the extreme
+            const ulonglong2 av = lds128(ap + ((uint32_t)bq << 4));
+            const ulonglong2 wv = lds128(wp + ((uint32_t)bq << 4));
+            float p0, p1, p2, p3;
+            unpack2(mul2(mul2(av.x, sgn2), wv.x), p0, p1);
+            unpack2(mul2(mul2(av.y, sgn2), wv.y), p2, p3);
+            int e = 3;
+            if (p2 == best) e = 2;
+            if (p1 == best) e = 1;
+            if (p0 == best) e = 0;
+            const int kbest = kc * FWD_BK + bq * 4 + e;
+            const long long m = m0 + ra, n = n0 + rw;
+            if (code & 1u) argmin[m * N + n] = kbest; else argmax[m * N + n] = kbest;
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty_bar[stage]);
+        if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
     }
 }
 
