@@ -269,7 +269,7 @@ def main():
     peaks = fp32_peaks(sms, max_mhz)
     achieved = flops_per_launch / (kavg * 1e-3) / 1e12
     roofline = {"bound": "fp32_cuda_core", "kernel": "mam_fwd_tiled_kernel (index-tracking variant "
-                + L.mam_fwd_variant_name(1, max(args.fwd_variant, 0)).decode() + ")",
+                + L.mam_fwd_variant_name(1, args.fwd_variant if args.fwd_variant >= 0 else 1).decode() + ")",
                 "achieved": achieved, "peak": peaks["fma_counted_tflops"], "unit": "TFLOP/s",
                 "frac": achieved / peaks["fma_counted_tflops"],
                 "peak_source": f"{sms} SMs x 128 lanes x 2 x {max_mhz:.0f} MHz (FMA counted as 2; no fp32 entry in "

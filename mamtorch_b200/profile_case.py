@@ -1,0 +1,58 @@
+"""Runs one MAM operation on a given shape a few times: the small, bounded command that `ncu`
+captures are taken on.
+
+    python -m mamtorch_b200.profile_case --shape 4096x1024x2048 --op fwd_idx --reps 3
+
+ops: fwd_idx (forward with indices: tiled kernel + index resolver), fwd_val (values only),
+bwd (selected-pair backward), selcount, step (forward + backward + selection count of one layer
+through the nn module).  Inputs are seeded N(0,1) activations and N(0,1/K) weights in [N,K] layout.
+"""
+import argparse
+
+import torch
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--shape", default="4096x1024x2048", help="MxKxN")
+    ap.add_argument("--op", default="fwd_idx", choices=["fwd_idx", "fwd_val", "bwd", "selcount", "step"])
+    ap.add_argument("--reps", type=int, default=3)
+    ap.add_argument("--variant", type=int, default=-1, help="tile configuration of the tiled forward (-1 auto)")
+    args = ap.parse_args()
+    M, K, N = (int(v) for v in args.shape.lower().split("x"))
+
+    import mamtorch_b200 as mamtorch
+    from mamtorch_b200 import _lib
+    from mamtorch_b200.nn import functional as MF
+
+    dev = torch.device("cuda:0")
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(M, K, generator=g).to(dev)
+    w = (torch.randn(N, K, generator=g) * K ** -0.5).to(dev)
+    gy = torch.randn(M, N, generator=g).to(dev)
+    if args.variant >= 0:
+        _lib.check(_lib.lib().mam_set_fwd_variant(1, args.variant), "variant")
+        _lib.check(_lib.lib().mam_set_fwd_variant(0, args.variant), "variant")
+    ops = torch.ops.mamtorch_b200
+    y, imax, imin = ops.linear_forward(x, w, None, None, 1.0, 0.0, True)
+    for _ in range(args.reps):
+        if args.op == "fwd_idx":
+            y, imax, imin = ops.linear_forward(x, w, None, None, 1.0, 0.0, True)
+        elif args.op == "fwd_val":
+            y, = ops.linear_forward(x, w, None, None, 1.0, 0.0, False)
+        elif args.op == "bwd":
+            ops.linear_backward(x, w, gy, imax, imin, 1.0)
+        elif args.op == "selcount":
+            MF.selection_hits(imax, imin, K)
+        else:
+            layer = mamtorch.nn.FullyConnected(K, N, store_args=True).to(dev)
+            out = layer(x.clone().requires_grad_())
+            out.backward(gy)
+            layer.update_selection_count()
+    torch.cuda.synchronize()
+    _lib.check(_lib.lib().mam_check_device_flag(), "device wait flag")
+    print(f"ok {args.op} {M}x{K}x{N} checksum {float(y.double().sum()):.6e}")
+
+
+if __name__ == "__main__":
+    main()
