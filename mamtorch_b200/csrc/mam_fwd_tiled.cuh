@@ -356,20 +356,25 @@ mam_resolve_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         for (int i = 0; i < C::LOOKAHEAD; ++i) produce_one();
     }
 
-    // ---- pass A: count tasks per chunk
+    // ---- pass A: read this thread's chunk ids once (all loads in flight together), count per chunk
     constexpr int PER_THREAD = C::RM * C::RN / C::THREADS;
+    unsigned ids[PER_THREAD];  // (max chunk) | (min chunk) << 16; 0xffffffff = outside the matrix
+#pragma unroll
     for (int i = 0; i < PER_THREAD; ++i) {
         const int o = i * C::THREADS + tid;
         const long long m = m0 + o / C::RN, n = n0 + o % C::RN;
-        const bool in = m < M && n < N;
-        int c1 = 0, c2 = 0;
-        if (in) {
-            c1 = min(max(argmax[m * N + n], 0), nk - 1);
-            c2 = min(max(argmin[m * N + n], 0), nk - 1);
+        ids[i] = 0xffffffffu;
+        if (m < M && n < N) {
+            const int c1 = min(max(argmax[m * N + n], 0), nk - 1);
+            const int c2 = min(max(argmin[m * N + n], 0), nk - 1);
+            ids[i] = (unsigned)c1 | ((unsigned)c2 << 16);
         }
-        if (in) {
-            atomicAdd(&cursor[c1], 1);
-            atomicAdd(&cursor[c2], 1);
+    }
+#pragma unroll
+    for (int i = 0; i < PER_THREAD; ++i) {
+        if (ids[i] != 0xffffffffu) {
+            atomicAdd(&cursor[ids[i] & 0xffffu], 1);
+            atomicAdd(&cursor[ids[i] >> 16], 1);
         }
     }
     __syncthreads();
@@ -407,18 +412,12 @@ mam_resolve_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     }
     __syncthreads();
     // ---- pass B: scatter task codes into chunk order
+#pragma unroll
     for (int i = 0; i < PER_THREAD; ++i) {
         const int o = i * C::THREADS + tid;
-        const long long m = m0 + o / C::RN, n = n0 + o % C::RN;
-        const bool in = m < M && n < N;
-        int c1 = 0, c2 = 0;
-        if (in) {
-            c1 = min(max(argmax[m * N + n], 0), nk - 1);
-            c2 = min(max(argmin[m * N + n], 0), nk - 1);
-        }
-        if (in) {
-            tasks[atomicAdd(&cursor[c1], 1)] = (unsigned short)(o << 1);
-            tasks[atomicAdd(&cursor[c2], 1)] = (unsigned short)((o << 1) | 1);
+        if (ids[i] != 0xffffffffu) {
+            tasks[atomicAdd(&cursor[ids[i] & 0xffffu], 1)] = (unsigned short)(o << 1);
+            tasks[atomicAdd(&cursor[ids[i] >> 16], 1)] = (unsigned short)((o << 1) | 1);
         }
     }
     __syncthreads();
