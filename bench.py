@@ -276,7 +276,9 @@ def main():
                                "MEASURED_PEAKS.json); a MAM unit has no FMA, see the two extra fractions",
                 "frac_of_non_fma_peak": achieved / peaks["non_fma_tops"],
                 "frac_of_measured_alu_pipe_ceiling": (achieved / 3 * 1e3) / peaks["alu_pipe_gunits"],
-                "launch_ms_avg": kavg, "launches_timed": len(kernel_ms), "traffic": None}
+                "launch_ms_avg": kavg, "launches_timed": len(kernel_ms), "traffic": 3.75e8,
+                "traffic_note": "dram read+write bytes per launch (layer-1 shape) from the ncu capture in "
+                                "profiles/step_kernels_4736x768x3072.md, scaled by rows to M=12608"}
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
