@@ -30,7 +30,8 @@ enum mam_status {
     MAM_ERR_WORKSPACE = 3,        /* workspace missing, too small or not 256-byte aligned         */
     MAM_ERR_CUDA = 4,             /* a CUDA runtime/driver call failed; see mam_last_cuda_error() */
     MAM_ERR_DEVICE_TIMEOUT = 5,   /* a bounded wait inside a kernel gave up (results invalid)     */
-    MAM_ERR_NOT_SM100 = 6         /* the current device is not compute capability 10.x            */
+    MAM_ERR_NOT_SM100 = 6,        /* the current device is not compute capability 10.x            */
+    MAM_ERR_STATIC_SCRATCH = 7    /* problem needs more scratch than the built-in static buffer   */
 };
 
 #define MAM_B_KN 0
@@ -84,6 +85,32 @@ int mam_fwd_f32(const float* a, const float* b, int b_layout,
                 float* y, int32_t* argmax, int32_t* argmin,
                 int64_t M, int64_t K, int64_t N,
                 void* workspace, size_t workspace_bytes, void* stream);
+
+/* Forward for callers that cannot allocate device memory.  (No counterpart in the reference:
+ * its host code allocates freely through ATen.)
+ *
+ * mam_fwd_f32 with the torch-op operand layout b[K,N] needs a K*N-float workspace for the
+ * K-contiguous copy of b that the tiled kernels read.  Some hosts have nowhere to get one: code
+ * running inside a stream capture or a real-time callback where cudaMalloc is forbidden, a plugin
+ * whose host framework owns the allocator and exposes no scratch interface, a process that runs
+ * with a fixed, fully committed memory plan.  For them this entry point keeps that copy in a
+ * buffer compiled into the library: MAM_STATIC_SCRATCH_BYTES of device memory that every GPU
+ * loading the library holds until the process exits, whether or not this function is ever called.
+ *
+ *   - Same results as mam_fwd_f32(a, b, MAM_B_KN, NULL, NULL, 0, ...): y = max+min, int32 indices
+ *     (pass both NULL for values only).  It calls no cudaMalloc/cudaFree and no allocating
+ *     library routine.
+ *   - K*N*4 (rounded up to 256) must not exceed MAM_STATIC_SCRATCH_BYTES, otherwise
+ *     MAM_ERR_STATIC_SCRATCH is returned and nothing is launched.
+ *   - The first call on each device looks up the buffer's device address (with that device
+ *     current).  Make that first call outside any stream capture.
+ *   - All calls on a device share the one buffer and it keeps the previous call's contents.  Each
+ *     call rewrites the part it uses before reading it, so nothing needs clearing, but two calls
+ *     whose kernels overlap on the GPU (different streams, no ordering between them) race on it:
+ *     serialise them. */
+#define MAM_STATIC_SCRATCH_BYTES (8u << 20)
+int mam_fwd_kn_static_f32(const float* a, const float* b, float* y, int32_t* argmax, int32_t* argmin,
+                          int64_t M, int64_t K, int64_t N, void* stream);
 
 /* MAM backward through the selected pairs.
  *   da[m,k]  = scale * sum_n grad[m,n] * b[k,n] * ([k==argmax[m,n]] + [k==argmin[m,n]])

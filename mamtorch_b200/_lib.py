@@ -27,6 +27,7 @@ ABI = {
     "mam_timer_disarm": (_i32, []),
     "mam_fwd_workspace_bytes": (_sz, [_i64, _i64, _i64, _i32, _i32]),
     "mam_fwd_f32": (_i32, [_vp, _vp, _i32, _vp, _vp, _i32, _f32, _f32, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _sz, _vp]),
+    "mam_fwd_kn_static_f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "mam_bwd_f32": (_i32, [_vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _f32, _i64, _i64, _i64, _vp]),
     "mam_selcount_i32": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "mam_selcount_indicator_i32": (_i32, [_vp, _vp, _vp, _i64, _vp]),

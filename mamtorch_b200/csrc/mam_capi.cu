@@ -150,6 +150,10 @@ const char* kIdxNames[N_VARIANTS] = {"idx_4x8_t64x128_c256_u8", "idx_4x8_t64x128
 int g_variant[2] = {-1, -1};  // [with_indices]
 int g_resolve_simple = 0;      // 1: use the thread-per-output resolver (cross-check)
 
+// Scratch for mam_fwd_kn_static_f32: lives in the library image, one copy per device.
+static __device__ __align__(256) unsigned char g_static_scratch[MAM_STATIC_SCRATCH_BYTES];
+void* g_static_scratch_addr[64] = {nullptr};  // device address per device, looked up on first use
+
 int bad_ptr(const void* p) { return p == nullptr; }
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 size_t round256(size_t x) { return (x + 255) & ~size_t(255); }
@@ -167,6 +171,9 @@ const char* mam_status_str(int status) {
         case MAM_ERR_CUDA: return "a CUDA call failed (see mam_last_cuda_error)";
         case MAM_ERR_DEVICE_TIMEOUT: return "a bounded wait inside a kernel gave up; results are invalid";
         case MAM_ERR_NOT_SM100: return "the current device is not compute capability 10.x (B200)";
+        case MAM_ERR_STATIC_SCRATCH:
+            return "the problem needs more scratch than the library's built-in static buffer "
+                   "(MAM_STATIC_SCRATCH_BYTES); use mam_fwd_f32 with a caller-provided workspace";
         default: return "unknown status";
     }
 }
@@ -342,6 +349,26 @@ int mam_fwd_f32(const float* a, const float* b, int b_layout, const float* bias,
     }
     MAM_CUDA(cudaGetLastError());
     return MAM_OK;
+}
+
+int mam_fwd_kn_static_f32(const float* a, const float* b, float* y, int32_t* argmax, int32_t* argmin, int64_t M,
+                          int64_t K, int64_t N, void* stream) {
+    if (M <= 0 || K <= 0 || N <= 0) return MAM_ERR_INVALID_ARGUMENT;
+    const size_t need = mam_fwd_workspace_bytes(M, K, N, MAM_B_KN, argmax != nullptr);
+    if (need > MAM_STATIC_SCRATCH_BYTES || (double)K * (double)N * 4.0 > (double)MAM_STATIC_SCRATCH_BYTES)
+        return MAM_ERR_STATIC_SCRATCH;
+    int dev = 0;
+    MAM_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return MAM_ERR_UNSUPPORTED;
+    if (g_static_scratch_addr[dev] == nullptr) {
+        // In host code `g_static_scratch` is only a handle for the symbol, not a device address:
+        // ask the runtime where the array lives on the current device, once.
+        void* p = nullptr;
+        MAM_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
+        g_static_scratch_addr[dev] = p;
+    }
+    return mam_fwd_f32(a, b, MAM_B_KN, nullptr, nullptr, 0, 1.0f, 0.0f, y, argmax, argmin, M, K, N,
+                       g_static_scratch_addr[dev], MAM_STATIC_SCRATCH_BYTES, stream);
 }
 
 int mam_bwd_f32(const float* a, const float* b, int b_layout, const float* grad, const int32_t* argmax,
