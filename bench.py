@@ -152,6 +152,7 @@ def main():
 
     import mamtorch_b200 as mamtorch
     from mamtorch_b200 import _lib
+    from mamtorch_b200.dist import allreduce_gradients
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -196,8 +197,7 @@ def main():
         fc1.update_selection_count()
         fc2.update_selection_count()
         if world > 1:
-            dist.all_reduce(fc1.weight.grad)
-            dist.all_reduce(fc2.weight.grad)
+            allreduce_gradients(params)
         return y
 
     def step_from_host():
