@@ -135,6 +135,21 @@ int mam_selcount_i32(const int32_t* argmax, const int32_t* argmin,
 int mam_selcount_indicator_i32(const int32_t* hit_max, const int32_t* hit_min,
                                int32_t* count, int64_t n_elems, void* stream);
 
+/* MAM forward on a pruned weight stored as CSR rows of W[N,K] (crow[N+1], col[nnz] ascending within
+ * a row, val[nnz]; 64-bit indices as torch.Tensor.to_sparse_csr() produces).  Result = the dense
+ * forward on W with zeros at the positions that are not stored: a missing position contributes a
+ * product of 0 at its k (lowest-k tie rule included).  bias, argmax, argmin may be NULL.
+ * The reference has no sparse MAM kernel; it runs the dense kernels on zeroed weights
+ * (examples/vitb16_imagenet1k/pruning_utils.py:105-116).  Limit: K <= 50000. */
+int mam_csr_fwd_f32(const float* a, const int64_t* crow, const int64_t* col, const float* val,
+                    const float* bias, float* y, int32_t* argmax, int32_t* argmin,
+                    int64_t M, int64_t K, int64_t N, void* stream);
+
+/* c[N,Mc] = A_csr[N,K] . b[K,Mc], ordinary sum.  Stands in for cusparsemm_csr / cusparsemm_coo
+ * (mamtorch/sparse/kernel/v1/csrc/cuda/cusparsemm_csr.cu:19-77, cusparsemm_coo.cu:19-76). */
+int mam_spmm_csr_f32(const int64_t* crow, const int64_t* col, const float* val, const float* b,
+                     float* c, int64_t N, int64_t K, int64_t Mc, void* stream);
+
 /* out[C,R] = transpose(in[R,C]); replaces the .T.contiguous() copies of the reference's glue
  * (mamtorch/nn/v4/fullyconnected.py:141, mamtorch/kernel/v4/csrc/cuda/fullyconnected.cu:66). */
 int mam_transpose_f32(const float* in, float* out, int64_t R, int64_t C, void* stream);

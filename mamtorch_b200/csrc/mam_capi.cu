@@ -7,6 +7,7 @@
 
 #include "../../include/mam_b200.h"
 #include "mam_bwd.cuh"
+#include "mam_csr.cuh"
 #include "mam_fwd_generic.cuh"
 #include "mam_fwd_tiled.cuh"
 
@@ -157,6 +158,20 @@ void* g_static_scratch_addr[64] = {nullptr};  // device address per device, look
 int bad_ptr(const void* p) { return p == nullptr; }
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 size_t round256(size_t x) { return (x + 255) & ~size_t(255); }
+
+template <int R>
+int launch_csr(const float* a, const int64_t* crow, const int64_t* col, const float* val, const float* bias,
+                      float* y, int32_t* argmax, int32_t* argmin, int64_t M, int64_t K, int64_t N, cudaStream_t cs) {
+    const size_t smem = ((size_t)R * (size_t)K + (size_t)CSR_WARPS * 3 * R * 32) * 4;
+    MAM_CUDA(cudaFuncSetAttribute(mam_csr_fwd_kernel<R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const long long grid = (M + R - 1) / R;
+    if (grid > 2147483647LL) return MAM_ERR_UNSUPPORTED;
+    mam_csr_fwd_kernel<R><<<(unsigned)grid, CSR_WARPS * 32, smem, cs>>>(
+        a, reinterpret_cast<const long long*>(crow), reinterpret_cast<const long long*>(col), val, bias, y, argmax,
+        argmin, M, K, N);
+    MAM_CUDA(cudaGetLastError());
+    return MAM_OK;
+}
 
 }  // namespace
 
@@ -424,6 +439,47 @@ int mam_selcount_i32(const int32_t* argmax, const int32_t* argmin, int32_t* hit_
         TimedLaunch t(MAM_KERNEL_SELCOUNT, (cudaStream_t)stream);
         mam_selcount_kernel<<<(unsigned)grid, 256, smem, (cudaStream_t)stream>>>(argmax, argmin, hit_max, hit_min, M,
                                                                                  K, N, cols);
+    }
+    MAM_CUDA(cudaGetLastError());
+    return MAM_OK;
+}
+
+int mam_csr_fwd_f32(const float* a, const int64_t* crow, const int64_t* col, const float* val, const float* bias,
+                    float* y, int32_t* argmax, int32_t* argmin, int64_t M, int64_t K, int64_t N, void* stream) {
+    if (bad_ptr(a) || bad_ptr(crow) || bad_ptr(y) || M <= 0 || K <= 0 || N <= 0) return MAM_ERR_INVALID_ARGUMENT;
+    if ((argmax == nullptr) != (argmin == nullptr)) return MAM_ERR_INVALID_ARGUMENT;
+    if (K >= (1LL << 31)) return MAM_ERR_UNSUPPORTED;
+    const DevInfo* d = nullptr;
+    int st = device_info(&d);
+    if (st != MAM_OK) return st;
+    cudaStream_t cs = (cudaStream_t)stream;
+    const long long budget = ((long long)d->max_smem - 1024) / 4;  // floats
+    auto fits = [&](int R) { return (long long)R * K + (long long)CSR_WARPS * 3 * R * 32 <= budget; };
+    // rows parked per CTA: as many as shared memory holds (each CTA streams the whole CSR once)
+    if (fits(8) && M >= 8) return launch_csr<8>(a, crow, col, val, bias, y, argmax, argmin, M, K, N, cs);
+    if (fits(4) && M >= 4) return launch_csr<4>(a, crow, col, val, bias, y, argmax, argmin, M, K, N, cs);
+    if (fits(2) && M >= 2) return launch_csr<2>(a, crow, col, val, bias, y, argmax, argmin, M, K, N, cs);
+    if (fits(1)) return launch_csr<1>(a, crow, col, val, bias, y, argmax, argmin, M, K, N, cs);
+    return MAM_ERR_UNSUPPORTED;
+}
+
+int mam_spmm_csr_f32(const int64_t* crow, const int64_t* col, const float* val, const float* b, float* c, int64_t N,
+                     int64_t K, int64_t Mc, void* stream) {
+    if (bad_ptr(crow) || bad_ptr(b) || bad_ptr(c) || N <= 0 || K <= 0 || Mc <= 0) return MAM_ERR_INVALID_ARGUMENT;
+    if (N > 65535) {
+        // grid.y limit: process row blocks
+        for (int64_t n0 = 0; n0 < N; n0 += 65535) {
+            const int64_t nn = N - n0 < 65535 ? N - n0 : 65535;
+            dim3 grid((unsigned)((Mc + 127) / 128), (unsigned)nn);
+            mam_spmm_csr_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(
+                reinterpret_cast<const long long*>(crow) + n0, reinterpret_cast<const long long*>(col), val, b,
+                c + n0 * Mc, nn, Mc);
+        }
+    } else {
+        dim3 grid((unsigned)((Mc + 127) / 128), (unsigned)N);
+        mam_spmm_csr_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(reinterpret_cast<const long long*>(crow),
+                                                                    reinterpret_cast<const long long*>(col), val, b, c,
+                                                                    N, Mc);
     }
     MAM_CUDA(cudaGetLastError());
     return MAM_OK;

@@ -5,6 +5,7 @@
 //   mamtorch/kernel/v2/csrc/register_functions.cpp:28-32
 //   mamtorch/kernel/v3/csrc/register_functions.cpp:30-34
 //   mamtorch/kernel/v4/csrc/register_functions.cpp:10-14
+//   mamtorch/sparse/kernel/v1/csrc/cuda/register_functions.cu:18-28
 // so torch.ops.mamtorch_kernel_v{1,2,3,4}.* keep their names, argument order and return types,
 // plus a `mamtorch_b200` namespace with the weight-as-stored ([N,K]) forms the nn modules use to
 // skip the reference's per-call transposes.  Only CUDA implementations are registered: a CPU
@@ -204,7 +205,73 @@ at::Tensor selection_count_update_(at::Tensor count, const at::Tensor& hit_max, 
     return count;
 }
 
+// ------------------------------------------------------------------ pruned weights (CSR)
+// y (and indices) of the dense layer on W with zeros at the positions that are not stored
+std::vector<at::Tensor> csr_linear_forward(const at::Tensor& x, const at::Tensor& crow, const at::Tensor& col,
+                                           const at::Tensor& val, const c10::optional<at::Tensor>& bias,
+                                           bool want_idx) {
+    check_matrix(x, "x");
+    TORCH_CHECK(crow.is_cuda() && col.is_cuda() && val.is_cuda(), "CSR components must be CUDA tensors");
+    TORCH_CHECK(crow.scalar_type() == at::kLong && col.scalar_type() == at::kLong, "CSR indices must be int64");
+    TORCH_CHECK(val.scalar_type() == at::kFloat, "CSR values must be float32");
+    TORCH_CHECK(crow.dim() == 1 && crow.numel() >= 1 && col.numel() == val.numel(), "malformed CSR components");
+    const int64_t M = x.size(0), K = x.size(1), N = crow.numel() - 1;
+    c10::cuda::CUDAGuard guard(x.device());
+    auto y = at::empty({M, N}, x.options());
+    at::Tensor amax, amin;
+    if (want_idx) {
+        amax = at::empty({M, N}, x.options().dtype(at::kInt));
+        amin = at::empty({M, N}, x.options().dtype(at::kInt));
+    }
+    if (M > 0 && N > 0) {
+        TORCH_CHECK(K > 0, "the reduction dimension must not be empty");
+        auto crow_c = crow.contiguous(), col_c = col.contiguous(), val_c = val.contiguous();
+        const float* bias_p = nullptr;
+        at::Tensor bias_c;
+        if (bias.has_value() && bias->defined()) {
+            TORCH_CHECK(bias->numel() == N && bias->scalar_type() == at::kFloat && bias->is_cuda(), "bias");
+            bias_c = bias->contiguous();
+            bias_p = bias_c.data_ptr<float>();
+        }
+        // col may be empty (everything pruned): pass a valid dummy pointer, it is never dereferenced
+        const int64_t* col_p = col_c.numel() ? col_c.data_ptr<int64_t>() : crow_c.data_ptr<int64_t>();
+        const float* val_p = val_c.numel() ? val_c.data_ptr<float>() : x.data_ptr<float>();
+        auto stream = at::cuda::getCurrentCUDAStream();
+        check_status(mam_csr_fwd_f32(x.data_ptr<float>(), crow_c.data_ptr<int64_t>(), col_p, val_p, bias_p,
+                                     y.data_ptr<float>(), want_idx ? amax.data_ptr<int32_t>() : nullptr,
+                                     want_idx ? amin.data_ptr<int32_t>() : nullptr, M, K, N, stream.stream()),
+                     "mam_csr_fwd_f32");
+    }
+    if (!want_idx) return {y};
+    return {y, amax, amin};
+}
+
+// cusparsemm(a_sparse[N,K], b[K,M]) -> dense [N,M]
+at::Tensor spmm_csr(const at::Tensor& a, const at::Tensor& b) {
+    TORCH_CHECK(b.is_cuda() && b.dim() == 2 && b.scalar_type() == at::kFloat, "b must be a 2-D float CUDA tensor");
+    TORCH_CHECK(a.dim() == 2 && a.size(1) == b.size(0), "inner dimensions differ");
+    c10::cuda::CUDAGuard guard(b.device());
+    const int64_t N = a.size(0), K = a.size(1), Mc = b.size(1);
+    auto c = at::zeros({N, Mc}, b.options());
+    if (N == 0 || Mc == 0 || K == 0) return c;
+    auto crow = a.crow_indices().to(at::kLong).contiguous();
+    auto col = a.col_indices().to(at::kLong).contiguous();
+    auto val = a.values().to(at::kFloat).contiguous();
+    if (val.numel() == 0) return c;
+    auto bc = b.contiguous();
+    auto stream = at::cuda::getCurrentCUDAStream();
+    check_status(mam_spmm_csr_f32(crow.data_ptr<int64_t>(), col.data_ptr<int64_t>(), val.data_ptr<float>(),
+                                  bc.data_ptr<float>(), c.data_ptr<float>(), N, K, Mc, stream.stream()),
+                 "mam_spmm_csr_f32");
+    return c;
+}
+at::Tensor spmm_coo(const at::Tensor& a, const at::Tensor& b) { return spmm_csr(a.to_sparse_csr(), b); }
+
 }  // namespace
+
+TORCH_LIBRARY(mamtorch_kernel_sparsev1, m) { m.def("cusparsemm(Tensor a, Tensor b) -> Tensor"); }
+TORCH_LIBRARY_IMPL(mamtorch_kernel_sparsev1, SparseCUDA, m) { m.impl("cusparsemm", &spmm_coo); }
+TORCH_LIBRARY_IMPL(mamtorch_kernel_sparsev1, SparseCsrCUDA, m) { m.impl("cusparsemm", &spmm_csr); }
 
 TORCH_LIBRARY(mamtorch_kernel_v1, m) {
     m.def("fullyconnected(Tensor a, Tensor b) -> Tensor[]");
@@ -253,10 +320,12 @@ TORCH_LIBRARY(mamtorch_b200, m) {
     m.def("linear_backward(Tensor x, Tensor weight, Tensor grad, Tensor argmax, Tensor argmin, float scale) -> Tensor[]");
     m.def("selection_hits(Tensor argmax, Tensor argmin, int K) -> Tensor[]");
     m.def("selection_count_update_(Tensor(a!) count, Tensor hit_max, Tensor hit_min) -> Tensor(a!)");
+    m.def("csr_linear_forward(Tensor x, Tensor crow, Tensor col, Tensor val, Tensor? bias, bool want_idx) -> Tensor[]");
 }
 TORCH_LIBRARY_IMPL(mamtorch_b200, CUDA, m) {
     m.impl("linear_forward", &linear_forward);
     m.impl("linear_backward", &linear_backward);
     m.impl("selection_hits", &selection_hits);
     m.impl("selection_count_update_", &selection_count_update_);
+    m.impl("csr_linear_forward", &csr_linear_forward);
 }

@@ -1,0 +1,76 @@
+"""Pruned-weight (CSR) kernels against the dense oracle on the zero-filled weight, and the
+cusparsemm operator against a dense product (the check of the reference's test/test_sparse.py:33-44)."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import assert_grad_close
+from oracle import c_oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def _pruned(N, K, keep, seed):
+    g = torch.Generator().manual_seed(seed)
+    w = torch.randn(N, K, generator=g) * K ** -0.5
+    mask = (torch.rand(N, K, generator=g) >= 1 - keep).float()   # Bernoulli keep, as test/test_sparse.py:13-16
+    return w, mask, g
+
+
+@pytest.mark.parametrize("shape,keep", [((70, 96, 45), 0.1), ((33, 257, 64), 0.5), ((9, 40, 20), 0.0),
+                                        ((16, 64, 31), 1.0), ((300, 1024, 130), 0.1), ((5, 4096, 37), 0.02)])
+def test_csr_forward_equals_dense_on_zero_filled_weight(shape, keep, cuda):
+    import mamtorch_b200 as mamtorch
+
+    M, K, N = shape
+    w, mask, g = _pruned(N, K, keep, M + K + N)
+    x = torch.randn(M, K, generator=g)
+    if keep == 0.1:
+        x = torch.relu(x)                # zero activations: explicit zero products tie with pruned ones
+        w[3] = -w[3].abs()               # a row whose stored products are all <= 0 against x >= 0
+    wz = w * mask
+    y_ref, imax_ref, imin_ref = c_oracle.forward(x.numpy(), wz.numpy(), b_is_nk=True)
+    w_csr = mamtorch.sparse.kernel.v1.prune_to_csr(w.to(cuda), mask.to(cuda))
+    y, imax, imin = mamtorch.sparse.kernel.v1.mam_linear_csr(x.to(cuda), w_csr)
+    assert torch.equal(imax.cpu().long(), torch.from_numpy(imax_ref))
+    assert torch.equal(imin.cpu().long(), torch.from_numpy(imin_ref))
+    assert torch.equal(y.cpu(), torch.from_numpy(y_ref))
+    yv, _, _ = mamtorch.sparse.kernel.v1.mam_linear_csr(x.to(cuda), w_csr, need_indices=False)
+    assert torch.equal(yv, y)
+
+
+def test_csr_layer_backward_gives_dense_weight_gradient(cuda):
+    import mamtorch_b200 as mamtorch
+
+    M, K, N = 64, 128, 48
+    w, mask, g = _pruned(N, K, 0.1, 7)
+    x = torch.randn(M, K, generator=g)
+    gy = torch.randn(M, N, generator=g)
+    bias = torch.randn(N, generator=g)
+    wz = (w * mask)
+    y_ref, imax_ref, imin_ref = c_oracle.forward(x.numpy(), wz.numpy(), b_is_nk=True, bias=bias.numpy())
+    da_ref, dw_ref = c_oracle.backward(x.numpy(), wz.numpy(), gy.numpy(), imax_ref, imin_ref, b_is_nk=True)
+    xd = x.to(cuda).requires_grad_()
+    wd = wz.to(cuda).requires_grad_()
+    bd = bias.to(cuda).requires_grad_()
+    y, _, _ = mamtorch.sparse.kernel.v1.mam_linear_csr(xd, wd.detach().to_sparse_csr(), bd, dense_weight=wd)
+    assert torch.equal(y.detach().cpu(), torch.from_numpy(y_ref))
+    y.backward(gy.to(cuda))
+    assert_grad_close(xd.grad.cpu().numpy(), da_ref)
+    assert_grad_close(wd.grad.cpu().numpy(), dw_ref)   # dense: selected pruned positions get gradient too
+    assert (wd.grad.cpu()[mask == 0] != 0).any()
+    assert_grad_close(bd.grad.cpu().numpy(), gy.sum(0).numpy())
+
+
+@pytest.mark.parametrize("layout", ["csr", "coo"])
+def test_cusparsemm_matches_dense_product(layout, cuda):
+    import mamtorch_b200 as mamtorch
+
+    g = torch.Generator().manual_seed(0)
+    N, K, Mc = 130, 257, 200
+    a = torch.randn(N, K, generator=g) * (torch.rand(N, K, generator=g) > 0.9)
+    b = torch.randn(K, Mc, generator=g)
+    a_sp = a.to(cuda).to_sparse_csr() if layout == "csr" else a.to(cuda).to_sparse()
+    c = mamtorch.sparse.kernel.v1.cusparsemm(a_sp, b.to(cuda))
+    ref = a.double() @ b.double()
+    np.testing.assert_allclose(c.cpu().numpy(), ref.numpy(), rtol=1e-5, atol=1e-5)
