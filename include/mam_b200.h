@@ -62,6 +62,7 @@ const char* mam_fwd_variant_name(int with_indices, int variant);
 #define MAM_KERNEL_FWD_GENERIC 2 /* any-shape forward                                    */
 #define MAM_KERNEL_BWD 3         /* selected-pair scatter                                */
 #define MAM_KERNEL_SELCOUNT 4    /* selection hits                                       */
+#define MAM_KERNEL_DENSE_TF32 5  /* tcgen05 TF32 product of the beta term                */
 int mam_timer_arm(void** starts, void** stops, int capacity, int kernel_id);
 int mam_timer_disarm(void);
 
@@ -134,6 +135,14 @@ int mam_selcount_i32(const int32_t* argmax, const int32_t* argmin,
  * the reference adds to max_selection_count (mamtorch/nn/v4/fullyconnected.py:125-129). */
 int mam_selcount_indicator_i32(const int32_t* hit_max, const int32_t* hit_min,
                                int32_t* count, int64_t n_elems, void* stream);
+
+/* Dense product on the tcgen05 tensor cores: out[M,N] = c_out*out + c_acc*(a[M,K] . w[N,K]^T), TF32
+ * inputs (10-bit mantissa), fp32 accumulation: the beta term of the blended layer.  Stands in for the
+ * cuBLAS products in mamtorch/kernel/v3/csrc/cuda/fullyconnected.cu:153-160 and for dense_cuda
+ * (mamtorch/kernel/v2/csrc/cuda/dense.cu:146-260).  Needs K % 4 == 0 and 16-byte aligned a, w
+ * (otherwise MAM_ERR_UNSUPPORTED).  Agreement with an fp32 product: 1e-3 relative. */
+int mam_dense_tf32(const float* a, const float* w, float* out, float c_acc, float c_out,
+                   int64_t M, int64_t K, int64_t N, void* stream);
 
 /* MAM forward on a pruned weight stored as CSR rows of W[N,K] (crow[N+1], col[nnz] ascending within
  * a row, val[nnz]; 64-bit indices as torch.Tensor.to_sparse_csr() produces).  Result = the dense

@@ -31,6 +31,7 @@ ABI = {
     "mam_bwd_f32": (_i32, [_vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _f32, _i64, _i64, _i64, _vp]),
     "mam_selcount_i32": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "mam_selcount_indicator_i32": (_i32, [_vp, _vp, _vp, _i64, _vp]),
+    "mam_dense_tf32": (_i32, [_vp, _vp, _vp, _f32, _f32, _i64, _i64, _i64, _vp]),
     "mam_csr_fwd_f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "mam_spmm_csr_f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "mam_transpose_f32": (_i32, [_vp, _vp, _i64, _i64, _vp]),

@@ -8,6 +8,7 @@
 #include "../../include/mam_b200.h"
 #include "mam_bwd.cuh"
 #include "mam_csr.cuh"
+#include "mam_dense_tf32.cuh"
 #include "mam_fwd_generic.cuh"
 #include "mam_fwd_tiled.cuh"
 
@@ -439,6 +440,32 @@ int mam_selcount_i32(const int32_t* argmax, const int32_t* argmin, int32_t* hit_
         TimedLaunch t(MAM_KERNEL_SELCOUNT, (cudaStream_t)stream);
         mam_selcount_kernel<<<(unsigned)grid, 256, smem, (cudaStream_t)stream>>>(argmax, argmin, hit_max, hit_min, M,
                                                                                  K, N, cols);
+    }
+    MAM_CUDA(cudaGetLastError());
+    return MAM_OK;
+}
+
+int mam_dense_tf32(const float* a, const float* w, float* out, float c_acc, float c_out, int64_t M, int64_t K,
+                   int64_t N, void* stream) {
+    if (bad_ptr(a) || bad_ptr(w) || bad_ptr(out) || M <= 0 || K <= 0 || N <= 0) return MAM_ERR_INVALID_ARGUMENT;
+    if (K % 4 != 0 || !aligned16(a) || !aligned16(w)) return MAM_ERR_UNSUPPORTED;
+    const DevInfo* d = nullptr;
+    int st = device_info(&d);
+    if (st != MAM_OK) return st;
+    CUtensorMap tmA, tmW;
+    st = encode_rows_k(&tmA, a, M, K, DG_BM);
+    if (st != MAM_OK) return st;
+    st = encode_rows_k(&tmW, w, N, K, DG_BN);
+    if (st != MAM_OK) return st;
+    const long long tiles = ((M + DG_BM - 1) / DG_BM) * ((N + DG_BN - 1) / DG_BN);
+    if (tiles > 2147483647LL) return MAM_ERR_UNSUPPORTED;
+    int* flag = nullptr;
+    MAM_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&flag), g_wait_gave_up));
+    MAM_CUDA(cudaFuncSetAttribute(mam_dense_tf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DG_SMEM_BYTES));
+    {
+        TimedLaunch t(MAM_KERNEL_DENSE_TF32, (cudaStream_t)stream);
+        mam_dense_tf32_kernel<<<(unsigned)tiles, DG_THREADS, DG_SMEM_BYTES, (cudaStream_t)stream>>>(
+            tmA, tmW, out, M, K, N, c_acc, c_out, flag);
     }
     MAM_CUDA(cudaGetLastError());
     return MAM_OK;

@@ -121,6 +121,32 @@ std::vector<at::Tensor> backward_impl(const at::Tensor& a, const at::Tensor& w, 
     return {da, dw};
 }
 
+// ------------------------------------------------------------------ dense (sum-of-products) term
+// 1: tcgen05 TF32 kernel of this library (default); 0: torch/cuBLAS in full fp32.
+int g_dense_backend = 1;
+
+void set_dense_backend(int64_t backend) { g_dense_backend = backend ? 1 : 0; }
+int64_t get_dense_backend() { return g_dense_backend; }
+
+// a[M,K] . w[N,K]^T -> [M,N]
+at::Tensor dense_nt(const at::Tensor& a, const at::Tensor& w) {
+    check_matrix(a, "a");
+    check_matrix(w, "w");
+    TORCH_CHECK(a.size(1) == w.size(1), "inner dimensions differ");
+    c10::cuda::CUDAGuard guard(a.device());
+    const int64_t M = a.size(0), K = a.size(1), N = w.size(0);
+    const bool tf32_ok = g_dense_backend == 1 && M > 0 && N > 0 && K > 0 && K % 4 == 0 &&
+                         reinterpret_cast<uintptr_t>(a.data_ptr()) % 16 == 0 &&
+                         reinterpret_cast<uintptr_t>(w.data_ptr()) % 16 == 0;
+    if (!tf32_ok) return at::matmul(a, w.t());
+    auto out = at::empty({M, N}, a.options());
+    auto stream = at::cuda::getCurrentCUDAStream();
+    check_status(mam_dense_tf32(a.data_ptr<float>(), w.data_ptr<float>(), out.data_ptr<float>(), 1.0f, 0.0f, M, K, N,
+                                stream.stream()),
+                 "mam_dense_tf32");
+    return out;
+}
+
 // ------------------------------------------------------------------ reference-named operators
 std::vector<at::Tensor> fullyconnected(const at::Tensor& a, const at::Tensor& b) {
     auto r = forward_impl(a, b, MAM_B_KN, c10::nullopt, c10::nullopt, false, 1.0, 0.0, true);
@@ -138,27 +164,52 @@ std::vector<at::Tensor> fullyconnected_backward(const at::Tensor& a, const at::T
 at::Tensor dense(const at::Tensor& a, const at::Tensor& b) {
     check_matrix(a, "a");
     check_matrix(b, "b");
-    return at::matmul(a, b);
+    TORCH_CHECK(a.size(1) == b.size(0), "inner dimensions differ");
+    if (g_dense_backend == 0) return at::matmul(a, b);
+    return dense_nt(a, b.t().contiguous());
+}
+// The K-contiguous copy of b serves both the tensor-core product and the MAM kernels, so the
+// blended operators transpose once instead of once per kernel.
+Fwd blended_impl(const at::Tensor& a, const at::Tensor& b, const at::Tensor& bias, double beta, bool want_idx) {
+    check_matrix(a, "a");
+    check_matrix(b, "b");
+    TORCH_CHECK(a.size(1) == b.size(0), "inner dimensions of a and b differ");
+    if (beta == 0.0) return forward_impl(a, b, MAM_B_KN, bias, c10::nullopt, true, 1.0, 0.0, want_idx);
+    auto bt = b.t().contiguous();  // W[N,K]
+    c10::optional<at::Tensor> d = dense_nt(a, bt);
+    return forward_impl(a, bt, MAM_B_NK, bias, d, true, 1.0 - beta, beta, want_idx);
 }
 std::vector<at::Tensor> fullyconnected_beta(const at::Tensor& a, const at::Tensor& b, const at::Tensor& bias,
                                             double beta) {
-    c10::optional<at::Tensor> d;
-    if (beta != 0.0) d = dense(a, b);
-    auto r = forward_impl(a, b, MAM_B_KN, bias, d, true, 1.0 - beta, beta, true);
+    auto r = blended_impl(a, b, bias, beta, true);
     return {r.y, r.argmax, r.argmin};
 }
 at::Tensor fullyconnected_fast_beta(const at::Tensor& a, const at::Tensor& b, const at::Tensor& bias, double beta) {
-    c10::optional<at::Tensor> d;
-    if (beta != 0.0) d = dense(a, b);
-    return forward_impl(a, b, MAM_B_KN, bias, d, true, 1.0 - beta, beta, false).y;
+    return blended_impl(a, b, bias, beta, false).y;
 }
 // (mamtorch/kernel/v3/csrc/cuda/fullyconnected_backward.cu:138-145)
 std::vector<at::Tensor> fullyconnected_backward_beta(const at::Tensor& a, const at::Tensor& b, const at::Tensor& grad,
                                                      const at::Tensor& argmax, const at::Tensor& argmin, double beta) {
     auto r = backward_impl(a, b, MAM_B_KN, grad, argmax, argmin, 1.0 - beta);
     if (beta != 0.0) {
-        r[0].addmm_(grad, b.t(), 1.0, beta);
-        r[1].addmm_(a.t(), grad, 1.0, beta);
+        const int64_t M = a.size(0), K = a.size(1), N = b.size(1);
+        const bool tf32_ok = g_dense_backend == 1 && M % 4 == 0 && N % 4 == 0 && K % 4 == 0 && M > 0 && N > 0 && K > 0;
+        if (tf32_ok) {
+            // da[M,K] += beta * grad[M,N] . b[K,N]^T      (reduction over N: both operands N-contiguous)
+            // db[K,N] += beta * a^T[K,M] . grad^T[N,M]^T  (reduction over M: transposed copies)
+            auto stream = at::cuda::getCurrentCUDAStream();
+            check_status(mam_dense_tf32(grad.data_ptr<float>(), b.data_ptr<float>(), r[0].data_ptr<float>(),
+                                        (float)beta, 1.0f, M, N, K, stream.stream()),
+                         "mam_dense_tf32");
+            auto at_ = a.t().contiguous();
+            auto gt = grad.t().contiguous();
+            check_status(mam_dense_tf32(at_.data_ptr<float>(), gt.data_ptr<float>(), r[1].data_ptr<float>(),
+                                        (float)beta, 1.0f, K, M, N, stream.stream()),
+                         "mam_dense_tf32");
+        } else {
+            r[0].addmm_(grad, b.t(), 1.0, beta);
+            r[1].addmm_(a.t(), grad, 1.0, beta);
+        }
     }
     return r;
 }
@@ -320,6 +371,9 @@ TORCH_LIBRARY(mamtorch_b200, m) {
     m.def("linear_backward(Tensor x, Tensor weight, Tensor grad, Tensor argmax, Tensor argmin, float scale) -> Tensor[]");
     m.def("selection_hits(Tensor argmax, Tensor argmin, int K) -> Tensor[]");
     m.def("selection_count_update_(Tensor(a!) count, Tensor hit_max, Tensor hit_min) -> Tensor(a!)");
+    m.def("dense_nt(Tensor a, Tensor w) -> Tensor");
+    m.def("set_dense_backend(int backend) -> ()");
+    m.def("get_dense_backend() -> int");
     m.def("csr_linear_forward(Tensor x, Tensor crow, Tensor col, Tensor val, Tensor? bias, bool want_idx) -> Tensor[]");
 }
 TORCH_LIBRARY_IMPL(mamtorch_b200, CUDA, m) {
@@ -328,4 +382,9 @@ TORCH_LIBRARY_IMPL(mamtorch_b200, CUDA, m) {
     m.impl("selection_hits", &selection_hits);
     m.impl("selection_count_update_", &selection_count_update_);
     m.impl("csr_linear_forward", &csr_linear_forward);
+    m.impl("dense_nt", &dense_nt);
+}
+TORCH_LIBRARY_IMPL(mamtorch_b200, CompositeExplicitAutograd, m) {
+    m.impl("set_dense_backend", &set_dense_backend);
+    m.impl("get_dense_backend", &get_dense_backend);
 }

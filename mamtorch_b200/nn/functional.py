@@ -34,6 +34,50 @@ def _(argmax, argmin, K):
     return [argmax.new_empty(shape), argmax.new_empty(shape)]
 
 
+@torch.library.register_fake("mamtorch_b200::dense_nt")
+def _(a, w):
+    torch._check(a.dim() == 2 and w.dim() == 2 and a.size(1) == w.size(1))
+    return a.new_empty((a.size(0), w.size(0)))
+
+
+def set_dense_backend(name: str) -> None:
+    """Backend of the dense (sum-of-products) beta term: "tf32" = this library's tcgen05 kernel
+    (TF32 inputs, fp32 accumulation, 1e-3 relative to fp32; the default), "fp32" = torch/cuBLAS in
+    full fp32, bit-compatible with the reference's `F.linear` / `at::linalg_matmul`."""
+    if name not in ("tf32", "fp32"):
+        raise ValueError("dense backend must be 'tf32' or 'fp32'")
+    _ops.set_dense_backend(1 if name == "tf32" else 0)
+
+
+def get_dense_backend() -> str:
+    return "tf32" if _ops.get_dense_backend() else "fp32"
+
+
+class _DenseLinear(torch.autograd.Function):
+    """x[M,K] . W[N,K]^T on the tensor cores, with the two gradient products on them as well."""
+
+    @staticmethod
+    def forward(ctx, x, weight):
+        ctx.save_for_backward(x, weight)
+        return _ops.dense_nt(x, weight)
+
+    @staticmethod
+    def backward(ctx, g):
+        x, weight = ctx.saved_tensors
+        g = g.contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = _ops.dense_nt(g, weight.t().contiguous())          # [M,N] . [K,N]^T
+        if ctx.needs_input_grad[1]:
+            dw = _ops.dense_nt(g.t().contiguous(), x.t().contiguous())  # [N,M] . [K,M]^T
+        return dx, dw
+
+
+def dense_linear(x: Tensor, weight: Tensor) -> Tensor:
+    """The MAC term of a blended layer: x @ weight.T (no bias)."""
+    return _DenseLinear.apply(x.contiguous(), weight.contiguous())
+
+
 class _MamLinear(torch.autograd.Function):
     """y = alpha*(max_k x*w + min_k x*w) + beta*dense + bias, gradient through the selected pairs."""
 

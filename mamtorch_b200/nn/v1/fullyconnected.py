@@ -31,7 +31,7 @@ class _SelectionCountMixin:
         """(1-beta)*mam + beta*linear + bias with the indices kept on the module."""
         x = input.reshape(-1, input.size(-1))
         blend = self.beta > beta_floor
-        dense = F.linear(x, self.weight) if blend else None
+        dense = MF.dense_linear(x, self.weight) if blend else None
         y, self.argmax, self.argmin = MF.mam_linear(x, self.weight, self.bias, dense,
                                                     1 - self.beta if blend else 1.0,
                                                     self.beta if blend else 0.0)

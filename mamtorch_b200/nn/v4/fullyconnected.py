@@ -126,7 +126,7 @@ class FullyConnected(Module):
 
         dense = None
         if self.beta > 0:
-            dense = F.linear(x, self.weight.detach() if self.train_mam_only else self.weight)
+            dense = MF.dense_linear(x, self.weight.detach() if self.train_mam_only else self.weight)
         need_idx = self.training or (self.store_args and self.splits <= 1)
 
         if self.beta >= 1:

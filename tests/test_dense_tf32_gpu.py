@@ -1,0 +1,71 @@
+"""tcgen05 TF32 product (the dense beta term) against an fp64 product: 1e-3 relative, the
+tolerance the blended-training configuration states for this term."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from mamtorch_b200 import _lib
+
+pytestmark = pytest.mark.gpu
+
+TF32_RTOL = 1e-3
+
+
+def _dense(a, w, out=None, c_acc=1.0, c_out=0.0):
+    M, K = a.shape
+    N = w.shape[0]
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float32, device=a.device)
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    st = _lib.lib().mam_dense_tf32(p(a), p(w), p(out), c_acc, c_out, M, K, N,
+                                   ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    _lib.check(st, "mam_dense_tf32")
+    return out
+
+
+def _close(got, ref):
+    scale = float(ref.abs().max())
+    np.testing.assert_allclose(got.cpu().double().numpy(), ref.cpu().numpy(), rtol=TF32_RTOL, atol=TF32_RTOL * scale)
+
+
+@pytest.mark.parametrize("shape", [(128, 32, 128), (128, 256, 128), (256, 64, 384), (300, 100, 200),
+                                   (1, 8, 1), (129, 36, 257), (1000, 768, 520), (4096, 4096, 512)])
+def test_tf32_product_matches_fp64(shape, cuda):
+    M, K, N = shape
+    g = torch.Generator().manual_seed(M + K + N)
+    a = torch.randn(M, K, generator=g).to(cuda)
+    w = (torch.randn(N, K, generator=g) * K ** -0.5).to(cuda)
+    out = _dense(a, w)
+    torch.cuda.synchronize()
+    assert _lib.lib().mam_check_device_flag() == 0
+    _close(out, a.double() @ w.double().T)
+
+
+def test_tf32_product_exact_on_small_integers(cuda):
+    """Integers up to 2^10 are exact in TF32, sums stay exact in fp32: the result must be exact,
+    which pins the operand layout (any mis-addressed row or k-slice shows up as a wrong integer)."""
+    g = torch.Generator().manual_seed(1)
+    M, K, N = 256, 160, 384
+    a = torch.randint(-8, 9, (M, K), generator=g).float().to(cuda)
+    w = torch.randint(-8, 9, (N, K), generator=g).float().to(cuda)
+    out = _dense(a, w)
+    assert torch.equal(out, a @ w.T)
+
+
+def test_tf32_product_accumulates_into_output(cuda):
+    g = torch.Generator().manual_seed(2)
+    a = torch.randn(200, 64, generator=g).to(cuda)
+    w = torch.randn(130, 64, generator=g).to(cuda)
+    base = torch.randn(200, 130, generator=g).to(cuda)
+    out = _dense(a, w, out=base.clone(), c_acc=0.25, c_out=0.5)
+    _close(out, 0.5 * base.double() + 0.25 * (a.double() @ w.double().T))
+
+
+def test_unsupported_shapes_are_reported(cuda):
+    a = torch.zeros(4, 6, device=cuda)
+    w = torch.zeros(5, 6, device=cuda)
+    out = torch.zeros(4, 5, device=cuda)
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    assert _lib.lib().mam_dense_tf32(p(a), p(w), p(out), 1.0, 0.0, 4, 6, 5, None) == 2

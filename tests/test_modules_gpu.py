@@ -29,10 +29,16 @@ def test_opcheck_plain_ops(ns, cuda):
     torch.library.opcheck(ops.fullyconnected_backward, (a.detach(), b.detach(), torch.ones_like(c), imax, imin))
 
 
+@pytest.mark.parametrize("backend", ["fp32", "tf32"])
 @pytest.mark.parametrize("ns", ["mamtorch_kernel_v2", "mamtorch_kernel_v3"])
-def test_blended_ops_match_reference_formula(ns, cuda):
-    import mamtorch_b200  # noqa: F401
+def test_blended_ops_match_reference_formula(ns, backend, cuda):
+    """The MAM term (indices) is exact with either backend of the dense term; the blended value is
+    held to 1e-5 with the fp32 backend and to 1e-3 (TF32 inputs) with the tensor-core backend."""
+    import mamtorch_b200
+    from mamtorch_b200.nn import functional as MF
 
+    tol = 1e-5 if backend == "fp32" else 1e-3
+    MF.set_dense_backend(backend)
     g = load_golden("blend_40x64x48")
     a, b, bias, grad = (torch.from_numpy(g[k]).to(cuda) for k in ("a", "b", "bias", "g"))
     beta = float(g["beta"])
@@ -47,10 +53,11 @@ def test_blended_ops_match_reference_formula(ns, cuda):
             assert torch.equal(cf, c)
     finally:
         torch.backends.cuda.matmul.allow_tf32 = prev
+        MF.set_dense_backend("tf32")
     assert np.array_equal(imax.cpu().numpy(), g["argmax"]) and np.array_equal(imin.cpu().numpy(), g["argmin"])
-    np.testing.assert_allclose(c.cpu().numpy(), g["y"], rtol=1e-5, atol=1e-5)
-    assert_grad_close(da.cpu().numpy(), g["agrad"])
-    assert_grad_close(db.cpu().numpy(), g["bgrad"])
+    np.testing.assert_allclose(c.cpu().numpy(), g["y"], rtol=tol, atol=tol * float(np.abs(g["y"]).max()))
+    assert_grad_close(da.cpu().numpy(), g["agrad"], rtol=tol)
+    assert_grad_close(db.cpu().numpy(), g["bgrad"], rtol=tol)
 
 
 def test_autograd_through_v4_wrapper(cuda):
@@ -110,7 +117,7 @@ def test_module_beta_blend_splits_and_relu(cuda):
     y = layer(x)
     xr = torch.relu(x).cpu()
     y_ref, _, _ = mam_oracle.mam_forward(xr, layer.weight.detach().T.contiguous().cpu(), layer.bias.detach().cpu(), 0.75)
-    np.testing.assert_allclose(y.detach().cpu().numpy(), y_ref.numpy(), rtol=1e-4, atol=1e-5)
+    np.testing.assert_allclose(y.detach().cpu().numpy(), y_ref.numpy(), rtol=1e-3, atol=1e-3 * float(y_ref.abs().max()))
     y.sum().backward()
     assert layer.weight.grad is not None and torch.isfinite(layer.weight.grad).all()
     # K cut into 3 slices: the sum of the three per-slice (max+min) terms
@@ -182,3 +189,37 @@ def test_conv1d(cuda):
         p = (xp[b_, :, t:t + 3] * w[f]).reshape(-1)
         assert y[b_, f, t].item() == (p.max() + p.min()).item()
         assert conv.argmax[b_, f, t].item() == int(p.argmax())
+
+
+def test_beta_blended_training_step(cuda):
+    """The blended-training configuration at reduced size (M=N=K=1024, beta=0.5, x and W with
+    variance K^-0.5): the MAM term is bit-exact (checked through a beta=0 call on the same inputs
+    and through the indices of the beta=0.5 call), the blended output and the gradients are within
+    1e-3 relative of the fp32 oracle because the dense term runs in TF32 on the tensor cores."""
+    import mamtorch_b200 as mamtorch
+    from oracle import c_oracle
+
+    M = N = K = 1024
+    beta = 0.5
+    g = torch.Generator().manual_seed(0)
+    std = K ** -0.25
+    x = torch.randn(M, K, generator=g) * std
+    w = torch.randn(N, K, generator=g) * std
+    gy = torch.randn(M, N, generator=g)
+    b = w.T.contiguous()
+    s_ref, imax_ref, imin_ref = c_oracle.forward(x.numpy(), w.numpy(), b_is_nk=True)
+    zero_bias = torch.zeros(N, device=cuda)
+    xd, bd = x.to(cuda), b.to(cuda)
+    c0, imax0, imin0 = mamtorch.kernel.v3.fullyconnected(xd, bd, zero_bias, 0.0)
+    assert torch.equal(c0.cpu(), torch.from_numpy(s_ref))
+    c, imax, imin = mamtorch.kernel.v3.fullyconnected(xd, bd, zero_bias, beta)
+    for got, ref in ((imax0, imax_ref), (imin0, imin_ref), (imax, imax_ref), (imin, imin_ref)):
+        assert torch.equal(got.cpu().long(), torch.from_numpy(ref))
+    y_ref = beta * (x.double() @ b.double()) + (1 - beta) * torch.from_numpy(s_ref).double()
+    np.testing.assert_allclose(c.cpu().double().numpy(), y_ref.numpy(), rtol=1e-3, atol=1e-3 * float(y_ref.abs().max()))
+    da, db = torch.ops.mamtorch_kernel_v3.fullyconnected_backward(xd, bd, gy.to(cuda), imax, imin, beta)
+    da_m, dw_m = c_oracle.backward(x.numpy(), w.numpy(), gy.numpy(), imax_ref, imin_ref, b_is_nk=True)
+    da_ref = beta * (gy.double() @ w.double()) + (1 - beta) * torch.from_numpy(da_m).double()
+    db_ref = beta * (x.double().T @ gy.double()) + (1 - beta) * torch.from_numpy(dw_m).double().T
+    assert_grad_close(da.cpu().numpy(), da_ref.numpy(), rtol=1e-3)
+    assert_grad_close(db.cpu().numpy(), db_ref.numpy(), rtol=1e-3)
