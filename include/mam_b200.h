@@ -125,6 +125,14 @@ int mam_bwd_f32(const float* a, const float* b, int b_layout, const float* grad,
                 float* da, float* db, float scale,
                 int64_t M, int64_t K, int64_t N, void* stream);
 
+/* The same backward with the selection hits of this pass accumulated on the way: hit_max[n,k] +=
+ * #rows with argmax[m,n]==k, hit_min likewise ([N,K] int32, added into; pass both NULL for no
+ * counting).  One sweep over grad / argmax / argmin serves dW and the counts. */
+int mam_bwd_count_f32(const float* a, const float* b, int b_layout, const float* grad,
+                      const int32_t* argmax, const int32_t* argmin,
+                      float* da, float* db, int32_t* hit_max, int32_t* hit_min, float scale,
+                      int64_t M, int64_t K, int64_t N, void* stream);
+
 /* Selection hits: hit_max[n,k] += #rows m with argmax[m,n]==k, hit_min likewise ([N,K] int32,
  * accumulated into, so zero them first for per-call counts).  The device-side form of the
  * bookkeeping in FullyConnected.update_selection_count (mamtorch/nn/v4/fullyconnected.py:114-131). */

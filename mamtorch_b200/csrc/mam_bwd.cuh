@@ -52,6 +52,89 @@ mam_bwd_kernel(const float* __restrict__ a, const float* __restrict__ w, const f
     for (long long i = threadIdx.x; i < (long long)rows * K; i += BWD_THREADS) da[m0 * K + i] = da_s[i];
 }
 
+// ---------------------------------------------------------------------------------------------
+// Two-kernel form of the backward used when both operands fit the shared-memory budgets.
+//
+// fp32 atomics are the cost of this pass (shared memory ~1.7 lane-ops/clk/SM, L2 reductions ~0.8),
+// so neither gradient goes through global atomics here:
+//   mam_bwd_dx_kernel : a CTA owns rows of a, accumulates their da in shared memory (as above,
+//                       without the dW reductions);
+//   mam_bwd_dw_kernel : a CTA owns `cols` consecutive outputs n, keeps their dW rows [cols][K] --
+//                       and, when asked, their max/min hit counters -- in shared memory, sweeps
+//                       all M rows, then writes each dW row once.  The selection count rides
+//                       along for free (integer shared-memory atomics are ~7x faster than fp32).
+// grad and the indices are read twice (once per kernel); both reads are streaming.
+template <bool B_NK>
+__global__ void __launch_bounds__(BWD_THREADS)
+mam_bwd_dx_kernel(const float* __restrict__ w, const float* __restrict__ g,
+                  const int* __restrict__ argmax, const int* __restrict__ argmin,
+                  float* __restrict__ da, long long M, long long K, long long N, int rows_per_cta, float scale) {
+    extern __shared__ float da_s[];  // [rows_per_cta][K]
+    const long long m0 = (long long)blockIdx.x * rows_per_cta;
+    const int rows = (int)min((long long)rows_per_cta, M - m0);
+    for (long long i = threadIdx.x; i < (long long)rows * K; i += BWD_THREADS) da_s[i] = 0.f;
+    __syncthreads();
+    for (int r = 0; r < rows; ++r) {
+        const long long m = m0 + r;
+        float* dar = da_s + (long long)r * K;
+        for (long long n = threadIdx.x; n < N; n += BWD_THREADS) {
+            const float gv = __fmul_rn(g[m * N + n], scale);
+            const int k1 = argmax[m * N + n], k2 = argmin[m * N + n];
+            if ((unsigned)k1 < (unsigned long long)K)
+                atomicAdd(&dar[k1], __fmul_rn(w[B_NK ? n * K + k1 : (long long)k1 * N + n], gv));
+            if ((unsigned)k2 < (unsigned long long)K)
+                atomicAdd(&dar[k2], __fmul_rn(w[B_NK ? n * K + k2 : (long long)k2 * N + n], gv));
+        }
+    }
+    __syncthreads();
+    for (long long i = threadIdx.x; i < (long long)rows * K; i += BWD_THREADS) da[m0 * K + i] = da_s[i];
+}
+
+// COUNT: also accumulate hit_max / hit_min ([N,K] int32, added to the caller's matrices).
+template <bool B_NK, bool COUNT>
+__global__ void __launch_bounds__(BWD_THREADS)
+mam_bwd_dw_kernel(const float* __restrict__ a, const float* __restrict__ g,
+                  const int* __restrict__ argmax, const int* __restrict__ argmin,
+                  float* __restrict__ dw, int* __restrict__ hit_max, int* __restrict__ hit_min,
+                  long long M, long long K, long long N, int cols, float scale) {
+    extern __shared__ float dw_s[];                                  // [cols][K] fp32
+    int* cmax_s = reinterpret_cast<int*>(dw_s + (size_t)cols * K);   // [cols][K] (COUNT only)
+    int* cmin_s = cmax_s + (size_t)cols * K;
+    const long long n0 = (long long)blockIdx.x * cols;
+    const int nc = (int)min((long long)cols, N - n0);
+    const long long tot = (long long)cols * K * (COUNT ? 3 : 1);
+    for (long long i = threadIdx.x; i < tot; i += BWD_THREADS) reinterpret_cast<int*>(dw_s)[i] = 0;
+    __syncthreads();
+    const long long work = M * nc;  // c = t % nc fastest: the nc values of a row are read together
+    for (long long t = threadIdx.x; t < work; t += BWD_THREADS) {
+        const long long m = t / nc;
+        const int c = (int)(t - m * nc);
+        const long long o = m * N + n0 + c;
+        const float gv = __fmul_rn(g[o], scale);
+        const int k1 = argmax[o], k2 = argmin[o];
+        const float* arow = a + m * K;
+        if ((unsigned)k1 < (unsigned long long)K) {
+            atomicAdd(&dw_s[(long long)c * K + k1], __fmul_rn(arow[k1], gv));
+            if (COUNT) atomicAdd(&cmax_s[(long long)c * K + k1], 1);
+        }
+        if ((unsigned)k2 < (unsigned long long)K) {
+            atomicAdd(&dw_s[(long long)c * K + k2], __fmul_rn(arow[k2], gv));
+            if (COUNT) atomicAdd(&cmin_s[(long long)c * K + k2], 1);
+        }
+    }
+    __syncthreads();
+    for (long long i = threadIdx.x; i < (long long)nc * K; i += BWD_THREADS) {
+        const long long c = i / K, k = i - c * K;
+        const long long n = n0 + c;
+        if (B_NK) dw[n * K + k] = dw_s[i]; else dw[k * N + n] = dw_s[i];
+        if (COUNT) {
+            const int vmax = cmax_s[i], vmin = cmin_s[i];
+            if (vmax) hit_max[n * K + k] += vmax;
+            if (vmin) hit_min[n * K + k] += vmin;
+        }
+    }
+}
+
 // True selection counts: cnt_max[n,k] += #rows with argmax[m,n]==k, same for min.  A CTA owns
 // `cols` consecutive outputs n and keeps their [cols][K] int32 counters for max and for min in
 // shared memory (integer shared-memory atomics are an order of magnitude faster than fp32 ones),

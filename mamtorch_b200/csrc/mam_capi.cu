@@ -125,30 +125,32 @@ int launch_tiled(const float* a, const float* w, const FwdParams& prm, const Dev
     return MAM_OK;
 }
 
-//                         TM TN WM WN ST track UQ batch
-using ValCfg0 = FwdCfg<8, 8, 4, 2, 4, false, 8, false>;  // 128x128 tile, 256 threads
+//                         TM TN WM WN ST track UQ batch mul2
+using ValCfg0 = FwdCfg<8, 8, 4, 2, 4, false, 1, false, false>;  // 128x128 tile, 256 threads, scalar multiplies
 using ValCfg1 = FwdCfg<8, 8, 4, 2, 4, false, 2, false>;
 using ValCfg2 = FwdCfg<8, 8, 4, 2, 4, false, 1, false>;
-using ValCfg3 = FwdCfg<8, 8, 4, 2, 4, false, 2, true>;
-using ValCfg4 = FwdCfg<4, 8, 4, 2, 4, false, 8, false>;  // 64x128 tile, 256 threads
-using ValCfg5 = FwdCfg<4, 8, 4, 2, 4, false, 2, false>;
-using ValCfg6 = FwdCfg<4, 8, 4, 2, 4, false, 2, true>;
-using ValCfg7 = FwdCfg<8, 4, 2, 4, 4, false, 2, true>;   // 64x128 tile, 256 threads, A-heavy
-using IdxCfg0 = FwdCfg<4, 8, 4, 2, 4, true, 8, false>;   // 64x128 tile, 256 threads
-using IdxCfg1 = FwdCfg<4, 8, 4, 2, 4, true, 2, false>;
+using ValCfg3 = FwdCfg<4, 8, 6, 2, 4, false, 2, false>;         // 96x128 tile, 384 threads
+using ValCfg4 = FwdCfg<4, 8, 4, 3, 4, false, 2, false>;         // 64x192 tile, 384 threads
+using ValCfg5 = FwdCfg<4, 8, 4, 2, 4, false, 2, false, false>;  // 64x128 tile, 256 threads, scalar multiplies
+using ValCfg6 = FwdCfg<4, 8, 4, 2, 4, false, 2, true>;          // 64x128 tile, 256 threads
+using ValCfg7 = FwdCfg<4, 4, 8, 2, 6, false, 4, false>;         // 128x64 tile, 512 threads
+using IdxCfg0 = FwdCfg<4, 8, 4, 2, 4, true, 2, false, false>;   // 64x128 tile, 256 threads, scalar multiplies
+using IdxCfg1 = FwdCfg<4, 8, 4, 2, 4, true, 2, false>;          // 64x128 tile, 256 threads
 using IdxCfg2 = FwdCfg<4, 8, 4, 2, 4, true, 1, false>;
-using IdxCfg3 = FwdCfg<4, 8, 4, 2, 4, true, 2, true>;
-using IdxCfg4 = FwdCfg<8, 4, 2, 4, 4, true, 8, false>;   // 64x128 tile, 256 threads, A-heavy
-using IdxCfg5 = FwdCfg<8, 4, 2, 4, 4, true, 2, false>;
-using IdxCfg6 = FwdCfg<4, 4, 4, 4, 4, true, 4, false>;   // 64x128 tile, 512 threads
-using IdxCfg7 = FwdCfg<4, 4, 4, 4, 4, true, 2, true>;
+using IdxCfg3 = FwdCfg<4, 8, 4, 2, 4, true, 4, false>;
+using IdxCfg4 = FwdCfg<8, 4, 2, 4, 4, true, 2, false, false>;   // A-heavy, scalar multiplies
+using IdxCfg5 = FwdCfg<8, 4, 2, 4, 4, true, 2, false>;          // 64x128 tile, 256 threads, A-heavy
+using IdxCfg6 = FwdCfg<4, 4, 4, 4, 4, true, 4, false>;          // 64x128 tile, 512 threads
+using IdxCfg7 = FwdCfg<4, 4, 6, 2, 4, true, 4, false>;          // 96x64 tile, 384 threads
 constexpr int N_VARIANTS = 8;
-const char* kValNames[N_VARIANTS] = {"val_8x8_t128x128_c256_u8", "val_8x8_t128x128_c256_u2", "val_8x8_t128x128_c256_u1",
-                                     "val_8x8_t128x128_c256_u2b", "val_4x8_t64x128_c256_u8", "val_4x8_t64x128_c256_u2",
-                                     "val_4x8_t64x128_c256_u2b", "val_8x4_t64x128_c256_u2b"};
-const char* kIdxNames[N_VARIANTS] = {"idx_4x8_t64x128_c256_u8", "idx_4x8_t64x128_c256_u2", "idx_4x8_t64x128_c256_u1",
-                                     "idx_4x8_t64x128_c256_u2b", "idx_8x4_t64x128_c256_u8", "idx_8x4_t64x128_c256_u2",
-                                     "idx_4x4_t64x128_c512_u4", "idx_4x4_t64x128_c512_u2b"};
+const char* kValNames[N_VARIANTS] = {"val_8x8_t128x128_c256_u1_scalar", "val_8x8_t128x128_c256_u2",
+                                     "val_8x8_t128x128_c256_u1", "val_4x8_t96x128_c384_u2", "val_4x8_t64x192_c384_u2",
+                                     "val_4x8_t64x128_c256_u2_scalar", "val_4x8_t64x128_c256_u2b",
+                                     "val_4x4_t128x64_c512_u4"};
+const char* kIdxNames[N_VARIANTS] = {"idx_4x8_t64x128_c256_u2_scalar", "idx_4x8_t64x128_c256_u2",
+                                     "idx_4x8_t64x128_c256_u1", "idx_4x8_t64x128_c256_u4",
+                                     "idx_8x4_t64x128_c256_u2_scalar", "idx_8x4_t64x128_c256_u2",
+                                     "idx_4x4_t64x128_c512_u4", "idx_4x4_t96x64_c384_u4"};
 int g_variant[2] = {-1, -1};  // [with_indices]
 int g_resolve_simple = 0;      // 1: use the thread-per-output resolver (cross-check)
 
@@ -174,6 +176,38 @@ int launch_csr(const float* a, const int64_t* crow, const int64_t* col, const fl
     return MAM_OK;
 }
 
+int g_bwd_mode = 0;  // 0 auto, 1 force the single-kernel form, 2 force the two-kernel form
+
+template <bool NK>
+int launch_bwd_split(const float* a, const float* b, const float* grad, const int32_t* argmax, const int32_t* argmin,
+                     float* da, float* db, int32_t* hit_max, int32_t* hit_min, float scale, int64_t M, int64_t K,
+                     int64_t N, int rows, int cols, cudaStream_t cs) {
+    const size_t smem_dx = (size_t)rows * (size_t)K * 4;
+    MAM_CUDA(cudaFuncSetAttribute(mam_bwd_dx_kernel<NK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dx));
+    {
+        TimedLaunch t(MAM_KERNEL_BWD, cs);
+        mam_bwd_dx_kernel<NK><<<(unsigned)((M + rows - 1) / rows), BWD_THREADS, smem_dx, cs>>>(
+            b, grad, argmax, argmin, da, M, K, N, rows, scale);
+    }
+    MAM_CUDA(cudaGetLastError());
+    const bool count = hit_max != nullptr;
+    const size_t smem_dw = (size_t)cols * (size_t)K * 4 * (count ? 3 : 1);
+    const unsigned grid = (unsigned)((N + cols - 1) / cols);
+    TimedLaunch t(MAM_KERNEL_BWD, cs);
+    if (count) {
+        MAM_CUDA(cudaFuncSetAttribute(mam_bwd_dw_kernel<NK, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      (int)smem_dw));
+        mam_bwd_dw_kernel<NK, true><<<grid, BWD_THREADS, smem_dw, cs>>>(a, grad, argmax, argmin, db, hit_max, hit_min,
+                                                                        M, K, N, cols, scale);
+    } else {
+        MAM_CUDA(cudaFuncSetAttribute(mam_bwd_dw_kernel<NK, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      (int)smem_dw));
+        mam_bwd_dw_kernel<NK, false><<<grid, BWD_THREADS, smem_dw, cs>>>(a, grad, argmax, argmin, db, nullptr, nullptr,
+                                                                         M, K, N, cols, scale);
+    }
+    MAM_CUDA(cudaGetLastError());
+    return MAM_OK;
+}
 }  // namespace
 
 extern "C" {
@@ -227,6 +261,11 @@ int mam_timer_disarm(void) {
 }
 
 int mam_set_fwd_variant(int with_indices, int variant) {
+    if (with_indices == 3) {  // selects the backward form: 0 auto, 1 single kernel, 2 two kernels
+        if (variant < 0 || variant > 2) return MAM_ERR_INVALID_ARGUMENT;
+        g_bwd_mode = variant;
+        return MAM_OK;
+    }
     if (with_indices == 2) {  // selects the index resolver: 0 tiled (default), 1 thread-per-output
         g_resolve_simple = variant ? 1 : 0;
         return MAM_OK;
@@ -387,13 +426,14 @@ int mam_fwd_kn_static_f32(const float* a, const float* b, float* y, int32_t* arg
                        g_static_scratch_addr[dev], MAM_STATIC_SCRATCH_BYTES, stream);
 }
 
-int mam_bwd_f32(const float* a, const float* b, int b_layout, const float* grad, const int32_t* argmax,
-                const int32_t* argmin, float* da, float* db, float scale, int64_t M, int64_t K, int64_t N,
-                void* stream) {
+int mam_bwd_count_f32(const float* a, const float* b, int b_layout, const float* grad, const int32_t* argmax,
+                      const int32_t* argmin, float* da, float* db, int32_t* hit_max, int32_t* hit_min, float scale,
+                      int64_t M, int64_t K, int64_t N, void* stream) {
     if (bad_ptr(a) || bad_ptr(b) || bad_ptr(grad) || bad_ptr(argmax) || bad_ptr(argmin) || bad_ptr(da) ||
         bad_ptr(db) || M <= 0 || K <= 0 || N <= 0)
         return MAM_ERR_INVALID_ARGUMENT;
     if (b_layout != MAM_B_KN && b_layout != MAM_B_NK) return MAM_ERR_INVALID_ARGUMENT;
+    if ((hit_max == nullptr) != (hit_min == nullptr)) return MAM_ERR_INVALID_ARGUMENT;
     const DevInfo* d = nullptr;
     int st = device_info(&d);
     if (st != MAM_OK) return st;
@@ -402,22 +442,48 @@ int mam_bwd_f32(const float* a, const float* b, int b_layout, const float* grad,
     int rows = (int)((32 * 1024) / (K * 4));
     if (rows < 1) rows = 1;
     if (rows > 8) rows = 8;
+    const bool count = hit_max != nullptr;
+    // columns owned per CTA in the two-kernel form: at most 8, shared memory permitting, and enough
+    // CTAs to cover the SMs twice
+    const long long per_col = K * 4 * (count ? 3 : 1);
+    int cols = (int)(((long long)d->max_smem - 1024) / per_col);
+    if (cols > 8) cols = 8;
+    while (cols > 1 && (N + cols - 1) / cols < 2LL * d->sms) cols >>= 1;
+    // Measured on B200 the single-kernel form is faster at every benchmarked shape (0.87 vs 1.32 ms at
+    // 12608x768x3072): the column-owned sweep is latency-bound.  The two-kernel form stays selectable.
+    const bool split = g_bwd_mode == 2;
+    if (split && cols >= 1) {
+        if (b_layout == MAM_B_NK)
+            return launch_bwd_split<true>(a, b, grad, argmax, argmin, da, db, hit_max, hit_min, scale, M, K, N, rows,
+                                          cols, cs);
+        return launch_bwd_split<false>(a, b, grad, argmax, argmin, da, db, hit_max, hit_min, scale, M, K, N, rows, cols,
+                                       cs);
+    }
     const size_t smem = (size_t)rows * (size_t)K * 4;
     const long long grid = (M + rows - 1) / rows;
     if (grid > 2147483647LL) return MAM_ERR_UNSUPPORTED;
     MAM_CUDA(cudaMemsetAsync(db, 0, (size_t)K * (size_t)N * 4, cs));
-    TimedLaunch t(MAM_KERNEL_BWD, cs);
-    if (b_layout == MAM_B_NK) {
-        MAM_CUDA(cudaFuncSetAttribute(mam_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        mam_bwd_kernel<true><<<(unsigned)grid, BWD_THREADS, smem, cs>>>(a, b, grad, argmax, argmin, da, db, M, K, N,
-                                                                        rows, scale);
-    } else {
-        MAM_CUDA(cudaFuncSetAttribute(mam_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        mam_bwd_kernel<false><<<(unsigned)grid, BWD_THREADS, smem, cs>>>(a, b, grad, argmax, argmin, da, db, M, K,
-                                                                         N, rows, scale);
+    {
+        TimedLaunch t(MAM_KERNEL_BWD, cs);
+        if (b_layout == MAM_B_NK) {
+            MAM_CUDA(cudaFuncSetAttribute(mam_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            mam_bwd_kernel<true><<<(unsigned)grid, BWD_THREADS, smem, cs>>>(a, b, grad, argmax, argmin, da, db, M, K, N,
+                                                                            rows, scale);
+        } else {
+            MAM_CUDA(cudaFuncSetAttribute(mam_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            mam_bwd_kernel<false><<<(unsigned)grid, BWD_THREADS, smem, cs>>>(a, b, grad, argmax, argmin, da, db, M, K,
+                                                                             N, rows, scale);
+        }
     }
     MAM_CUDA(cudaGetLastError());
+    if (count) return mam_selcount_i32(argmax, argmin, hit_max, hit_min, M, K, N, stream);
     return MAM_OK;
+}
+
+int mam_bwd_f32(const float* a, const float* b, int b_layout, const float* grad, const int32_t* argmax,
+                const int32_t* argmin, float* da, float* db, float scale, int64_t M, int64_t K, int64_t N,
+                void* stream) {
+    return mam_bwd_count_f32(a, b, b_layout, grad, argmax, argmin, da, db, nullptr, nullptr, scale, M, K, N, stream);
 }
 
 int mam_selcount_i32(const int32_t* argmax, const int32_t* argmin, int32_t* hit_max, int32_t* hit_min, int64_t M,

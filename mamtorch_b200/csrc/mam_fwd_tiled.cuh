@@ -24,14 +24,17 @@
 //    the exact lowest-k index -- the tie rule of the reference -- without per-k index tracking.
 #pragma once
 #include <cuda.h>
+#include <type_traits>
 #include "mam_fwd_generic.cuh"
 
 namespace mamb200 {
 
 constexpr int FWD_BK = 32;  // floats per row per stage = one 128-byte swizzle span
 
-template <int TM_, int TN_, int WM_, int WN_, int STAGES_, bool TRACK_, int UQ_ = 8, bool BATCH_ = false>
+template <int TM_, int TN_, int WM_, int WN_, int STAGES_, bool TRACK_, int UQ_ = 8, bool BATCH_ = false,
+          bool MUL2_ = true>
 struct FwdCfg {
+    static constexpr bool MUL2 = MUL2_;     // packed mul.rn.f32x2 (true) or four scalar multiplies
     static constexpr int UQ = UQ_;          // 16-byte k groups per unrolled loop body
     static constexpr bool BATCH = BATCH_;   // form all products of a W row before any max/min
     static constexpr int TM = TM_, TN = TN_, WM = WM_, WN = WN_, STAGES = STAGES_;
@@ -64,6 +67,15 @@ struct FwdParams {
     float one;     // 1.0f kept opaque to the compiler (see merge below)
     int* error;    // set to 1 when a bounded wait gave up
 };
+
+// compile-time loop: f receives std::integral_constant<int, I>, so I can feed "n" asm operands
+template <int I, int N, class F>
+__device__ __forceinline__ void static_for(F&& f) {
+    if constexpr (I < N) {
+        f(std::integral_constant<int, I>{});
+        static_for<I + 1, N>(f);
+    }
+}
 
 __device__ __forceinline__ ulonglong2 lds128(const unsigned char* p) {
     return *reinterpret_cast<const ulonglong2*>(p);
@@ -179,19 +191,29 @@ mam_fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                 for (int j = 0; j < TN; ++j) {
                     const ulonglong2 wv = lds128(wp + xw + j * 1024);
                     float p[TM][4];
-                    if constexpr (Cfg::BATCH) {
-#pragma unroll
-                        for (int i = 0; i < TM; ++i) {
+                    auto products = [&](int i) {
+                        if constexpr (Cfg::MUL2) {
                             unpack2(mul2(av[i].x, wv.x), p[i][0], p[i][1]);
                             unpack2(mul2(av[i].y, wv.y), p[i][2], p[i][3]);
+                        } else {
+                            float a0, a1, a2, a3, w0, w1, w2, w3;
+                            unpack2(av[i].x, a0, a1);
+                            unpack2(av[i].y, a2, a3);
+                            unpack2(wv.x, w0, w1);
+                            unpack2(wv.y, w2, w3);
+                            p[i][0] = __fmul_rn(a0, w0);
+                            p[i][1] = __fmul_rn(a1, w1);
+                            p[i][2] = __fmul_rn(a2, w2);
+                            p[i][3] = __fmul_rn(a3, w3);
                         }
+                    };
+                    if constexpr (Cfg::BATCH) {
+#pragma unroll
+                        for (int i = 0; i < TM; ++i) products(i);
                     }
 #pragma unroll
                     for (int i = 0; i < TM; ++i) {
-                        if constexpr (!Cfg::BATCH) {
-                            unpack2(mul2(av[i].x, wv.x), p[i][0], p[i][1]);
-                            unpack2(mul2(av[i].y, wv.y), p[i][2], p[i][3]);
-                        }
+                        if constexpr (!Cfg::BATCH) products(i);
                         if constexpr (TRACK) {
                             if (first) {
                                 lmax[i][j] = fmaxf(p[i][0], p[i][1]);
@@ -226,29 +248,27 @@ mam_fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                 // The value move is a multiply by an opaque 1.0 (exact for every input, keeps the
                 // sign of zero) so that it issues on the FMA pipe rather than the saturated ALU pipe.
                 const unsigned short kid = (unsigned short)kc;
-#pragma unroll
-                for (int i = 0; i < TM; ++i)
-#pragma unroll
-                    for (int j = 0; j < TN; ++j) {
-                        const uint32_t amax = id_addr + (uint32_t)(((i * TN + j) * 2 + 0) * Cfg::CONSUMERS * 2);
-                        const uint32_t amin = id_addr + (uint32_t)(((i * TN + j) * 2 + 1) * Cfg::CONSUMERS * 2);
-                        asm volatile(
-                            "{\n\t.reg .pred p;\n\t"
-                            "setp.gt.f32 p, %1, %0;\n\t"
-                            "@p mul.rn.f32 %0, %1, %2;\n\t"
-                            "@p st.shared.u16 [%3], %4;\n\t}"
-                            : "+f"(vmax[i][j])
-                            : "f"(lmax[i][j]), "f"(prm.one), "r"(amax), "h"(kid)
-                            : "memory");
-                        asm volatile(
-                            "{\n\t.reg .pred p;\n\t"
-                            "setp.lt.f32 p, %1, %0;\n\t"
-                            "@p mul.rn.f32 %0, %1, %2;\n\t"
-                            "@p st.shared.u16 [%3], %4;\n\t}"
-                            : "+f"(vmin[i][j])
-                            : "f"(lmin[i][j]), "f"(prm.one), "r"(amin), "h"(kid)
-                            : "memory");
-                    }
+                static_for<0, TM * TN>([&](auto slot) {
+                    constexpr int S = decltype(slot)::value;
+                    constexpr int i = S / TN, j = S % TN;
+                    // slot addresses are id_addr + compile-time offsets: no address arithmetic
+                    asm volatile(
+                        "{\n\t.reg .pred p;\n\t"
+                        "setp.gt.f32 p, %1, %0;\n\t"
+                        "@p mul.rn.f32 %0, %1, %2;\n\t"
+                        "@p st.shared.u16 [%3+%5], %4;\n\t}"
+                        : "+f"(vmax[i][j])
+                        : "f"(lmax[i][j]), "f"(prm.one), "r"(id_addr), "h"(kid), "n"((S * 2 + 0) * Cfg::CONSUMERS * 2)
+                        : "memory");
+                    asm volatile(
+                        "{\n\t.reg .pred p;\n\t"
+                        "setp.lt.f32 p, %1, %0;\n\t"
+                        "@p mul.rn.f32 %0, %1, %2;\n\t"
+                        "@p st.shared.u16 [%3+%5], %4;\n\t}"
+                        : "+f"(vmin[i][j])
+                        : "f"(lmin[i][j]), "f"(prm.one), "r"(id_addr), "h"(kid), "n"((S * 2 + 1) * Cfg::CONSUMERS * 2)
+                        : "memory");
+                });
             }
         }
         if (!ok) break;

@@ -94,7 +94,8 @@ Fwd forward_impl(const at::Tensor& a, const at::Tensor& w, int b_layout, const c
 }
 
 std::vector<at::Tensor> backward_impl(const at::Tensor& a, const at::Tensor& w, int b_layout, const at::Tensor& grad,
-                                      const at::Tensor& argmax, const at::Tensor& argmin, double scale) {
+                                      const at::Tensor& argmax, const at::Tensor& argmin, double scale,
+                                      bool count = false) {
     check_matrix(a, "a");
     check_matrix(w, "b");
     check_matrix(grad, "grad");
@@ -108,16 +109,24 @@ std::vector<at::Tensor> backward_impl(const at::Tensor& a, const at::Tensor& w, 
     c10::cuda::CUDAGuard guard(a.device());
     auto da = at::empty_like(a);
     auto dw = at::empty_like(w);
+    at::Tensor hmax, hmin;
+    if (count) {
+        hmax = at::zeros({N, K}, argmax.options());
+        hmin = at::zeros({N, K}, argmax.options());
+    }
     if (M == 0 || N == 0 || K == 0) {
         da.zero_();
         dw.zero_();
-        return {da, dw};
+    } else {
+        auto stream = at::cuda::getCurrentCUDAStream();
+        const int st = mam_bwd_count_f32(a.data_ptr<float>(), w.data_ptr<float>(), b_layout, grad.data_ptr<float>(),
+                                         argmax.data_ptr<int32_t>(), argmin.data_ptr<int32_t>(), da.data_ptr<float>(),
+                                         dw.data_ptr<float>(), count ? hmax.data_ptr<int32_t>() : nullptr,
+                                         count ? hmin.data_ptr<int32_t>() : nullptr, (float)scale, M, K, N,
+                                         stream.stream());
+        check_status(st, "mam_bwd_count_f32");
     }
-    auto stream = at::cuda::getCurrentCUDAStream();
-    const int st = mam_bwd_f32(a.data_ptr<float>(), w.data_ptr<float>(), b_layout, grad.data_ptr<float>(),
-                               argmax.data_ptr<int32_t>(), argmin.data_ptr<int32_t>(), da.data_ptr<float>(),
-                               dw.data_ptr<float>(), (float)scale, M, K, N, stream.stream());
-    check_status(st, "mam_bwd_f32");
+    if (count) return {da, dw, hmax, hmin};
     return {da, dw};
 }
 
@@ -226,6 +235,11 @@ std::vector<at::Tensor> linear_forward(const at::Tensor& x, const at::Tensor& we
 std::vector<at::Tensor> linear_backward(const at::Tensor& x, const at::Tensor& weight, const at::Tensor& grad,
                                         const at::Tensor& argmax, const at::Tensor& argmin, double scale) {
     return backward_impl(x, weight, MAM_B_NK, grad, argmax, argmin, scale);
+}
+// {dx, dw, hit_max[N,K], hit_min[N,K]}: the backward with this pass's selection hits counted on the way
+std::vector<at::Tensor> linear_backward_count(const at::Tensor& x, const at::Tensor& weight, const at::Tensor& grad,
+                                              const at::Tensor& argmax, const at::Tensor& argmin, double scale) {
+    return backward_impl(x, weight, MAM_B_NK, grad, argmax, argmin, scale, true);
 }
 // hits[0] = hit_max[N,K], hits[1] = hit_min[N,K]: how many rows selected each weight
 std::vector<at::Tensor> selection_hits(const at::Tensor& argmax, const at::Tensor& argmin, int64_t K) {
@@ -369,6 +383,7 @@ TORCH_LIBRARY_IMPL(mamtorch_kernel_v4, CUDA, m) {
 TORCH_LIBRARY(mamtorch_b200, m) {
     m.def("linear_forward(Tensor x, Tensor weight, Tensor? bias, Tensor? dense, float alpha, float beta, bool want_idx) -> Tensor[]");
     m.def("linear_backward(Tensor x, Tensor weight, Tensor grad, Tensor argmax, Tensor argmin, float scale) -> Tensor[]");
+    m.def("linear_backward_count(Tensor x, Tensor weight, Tensor grad, Tensor argmax, Tensor argmin, float scale) -> Tensor[]");
     m.def("selection_hits(Tensor argmax, Tensor argmin, int K) -> Tensor[]");
     m.def("selection_count_update_(Tensor(a!) count, Tensor hit_max, Tensor hit_min) -> Tensor(a!)");
     m.def("dense_nt(Tensor a, Tensor w) -> Tensor");
@@ -379,6 +394,7 @@ TORCH_LIBRARY(mamtorch_b200, m) {
 TORCH_LIBRARY_IMPL(mamtorch_b200, CUDA, m) {
     m.impl("linear_forward", &linear_forward);
     m.impl("linear_backward", &linear_backward);
+    m.impl("linear_backward_count", &linear_backward_count);
     m.impl("selection_hits", &selection_hits);
     m.impl("selection_count_update_", &selection_count_update_);
     m.impl("csr_linear_forward", &csr_linear_forward);

@@ -28,6 +28,29 @@ def _(x, weight, grad, argmax, argmin, scale):
     return [torch.empty_like(x), torch.empty_like(weight)]
 
 
+@torch.library.register_fake("mamtorch_b200::linear_backward_count")
+def _(x, weight, grad, argmax, argmin, scale):
+    shape = (weight.size(0), weight.size(1))
+    return [torch.empty_like(x), torch.empty_like(weight), argmax.new_empty(shape), argmax.new_empty(shape)]
+
+
+class HitSink:
+    """Receives the selection hits a backward pass counted on its way, tagged with the index
+    tensor they belong to, so that a later `update_selection_count()` need not sweep the indices
+    again."""
+
+    def __init__(self):
+        self.argmax = None
+        self.hits = None
+
+    def take(self, argmax):
+        """The hits recorded for exactly this index tensor, or None."""
+        if self.hits is not None and self.argmax is argmax:
+            hits, self.hits, self.argmax = self.hits, None, None
+            return hits
+        return None
+
+
 @torch.library.register_fake("mamtorch_b200::selection_hits")
 def _(argmax, argmin, K):
     shape = (argmax.size(1), K)
@@ -82,10 +105,10 @@ class _MamLinear(torch.autograd.Function):
     """y = alpha*(max_k x*w + min_k x*w) + beta*dense + bias, gradient through the selected pairs."""
 
     @staticmethod
-    def forward(ctx, x, weight, bias, dense, alpha, beta):
+    def forward(ctx, x, weight, bias, dense, alpha, beta, hit_sink=None):
         y, argmax, argmin = _ops.linear_forward(x, weight, bias, dense, alpha, beta, True)
         ctx.save_for_backward(x, weight, argmax, argmin)
-        ctx.alpha, ctx.beta = alpha, beta
+        ctx.alpha, ctx.beta, ctx.hit_sink = alpha, beta, hit_sink
         ctx.has_bias, ctx.has_dense = bias is not None, dense is not None
         ctx.mark_non_differentiable(argmax, argmin)
         return y, argmax, argmin
@@ -96,16 +119,20 @@ class _MamLinear(torch.autograd.Function):
         gy = gy.contiguous()
         dx = dw = dbias = ddense = None
         if ctx.needs_input_grad[0] or ctx.needs_input_grad[1]:
-            dx, dw = _ops.linear_backward(x, weight, gy, argmax, argmin, ctx.alpha)
+            if ctx.hit_sink is not None:
+                dx, dw, hmax, hmin = _ops.linear_backward_count(x, weight, gy, argmax, argmin, ctx.alpha)
+                ctx.hit_sink.argmax, ctx.hit_sink.hits = argmax, (hmax, hmin)
+            else:
+                dx, dw = _ops.linear_backward(x, weight, gy, argmax, argmin, ctx.alpha)
         if ctx.has_bias and ctx.needs_input_grad[2]:
             dbias = gy.sum(0)
         if ctx.has_dense and ctx.needs_input_grad[3]:
             ddense = gy * ctx.beta
-        return dx, dw, dbias, ddense, None, None
+        return dx, dw, dbias, ddense, None, None, None
 
 
 def mam_linear(x: Tensor, weight: Tensor, bias: Tensor | None = None, dense: Tensor | None = None,
-               alpha: float = 1.0, beta: float = 0.0, need_indices: bool = True):
+               alpha: float = 1.0, beta: float = 0.0, need_indices: bool = True, hit_sink: "HitSink | None" = None):
     """x[M,K], weight[N,K] -> (y[M,N], argmax, argmin) or (y, None, None).
 
     With `need_indices=False` the values-only kernel runs (no autograd: use it for inference)."""
@@ -118,7 +145,7 @@ def mam_linear(x: Tensor, weight: Tensor, bias: Tensor | None = None, dense: Ten
         y, _, _ = _MamLinear.apply(x, weight, bias, dense, float(alpha), float(beta))
         return y, None, None
     if need_indices:
-        return _MamLinear.apply(x, weight, bias, dense, float(alpha), float(beta))
+        return _MamLinear.apply(x, weight, bias, dense, float(alpha), float(beta), hit_sink)
     y, = _ops.linear_forward(x, weight, bias, dense, float(alpha), float(beta), False)
     return y, None, None
 
@@ -128,9 +155,9 @@ def selection_hits(argmax: Tensor, argmin: Tensor, in_features: int):
     return _ops.selection_hits(argmax.contiguous(), argmin.contiguous(), int(in_features))
 
 
-def selection_count_update_(count: Tensor, argmax: Tensor, argmin: Tensor) -> Tensor:
+def selection_count_update_(count: Tensor, argmax: Tensor, argmin: Tensor, hits=None) -> Tensor:
     """In-place equivalent of one `update_selection_count()` of the reference module
     (`mamtorch/nn/v4/fullyconnected.py:114-131`): +1 for every weight any row selected as max and
     +1 for every weight any row selected as min, both added to the same matrix."""
-    hmax, hmin = selection_hits(argmax, argmin, count.size(1))
+    hmax, hmin = hits if hits is not None else selection_hits(argmax, argmin, count.size(1))
     return _ops.selection_count_update_(count, hmax, hmin)

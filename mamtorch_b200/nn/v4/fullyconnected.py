@@ -56,6 +56,7 @@ class FullyConnected(Module):
         self.min_selection_count = None
         self.argmax = None
         self.argmin = None
+        self._hit_sink = MF.HitSink() if store_args else None
         self.reset_parameters()
 
     # -- initialisation: the same distributions as torch.nn.Linear, as in the reference (:76-84)
@@ -103,7 +104,9 @@ class FullyConnected(Module):
             self.reset_selection_count()
         # Both updates land in max_selection_count and each distinct (n,k) counts once per call:
         # that is what the reference's two `t[idx] += 1` statements do (:125-129).
-        MF.selection_count_update_(self.max_selection_count, self.argmax, self.argmin)
+        # if a backward pass already ran on these indices it counted the hits on its way
+        hits = self._hit_sink.take(self.argmax) if self._hit_sink is not None else None
+        MF.selection_count_update_(self.max_selection_count, self.argmax, self.argmin, hits)
 
     def selection_hits(self):
         """True per-weight hit counts (hit_max, hit_min) of the last stored forward: an extension,
@@ -150,7 +153,8 @@ class FullyConnected(Module):
                 y = y + self.bias
         else:
             y, argmax, argmin = MF.mam_linear(x, w, self.bias, dense, self.alpha, self.beta if dense is not None else 0.0,
-                                              need_indices=need_idx)
+                                              need_indices=need_idx,
+                                              hit_sink=self._hit_sink if (self.store_args and self.training) else None)
             if self.store_args:
                 self.argmax, self.argmin = argmax, argmin
 

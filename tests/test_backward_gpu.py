@@ -38,8 +38,11 @@ def test_blend_scale(cuda):
     assert_grad_close(db.cpu().numpy(), g["bgrad"])
 
 
+@pytest.mark.parametrize("mode", [1, 2])
 @pytest.mark.parametrize("shape", [(700, 768, 520), (33, 3000, 40), (2048, 64, 96)])
-def test_random_backward_against_c_oracle(shape, cuda):
+def test_random_backward_against_c_oracle(shape, mode, cuda):
+    """mode 1 = single kernel (da in shared memory, dW by L2 reductions); mode 2 = two kernels
+    (row-owned da, column-owned dW), the form used for large M."""
     M, K, N = shape
     gen = torch.Generator().manual_seed(M + K + N)
     a = torch.randn(M, K, generator=gen)
@@ -49,11 +52,46 @@ def test_random_backward_against_c_oracle(shape, cuda):
     # a few coincident selections: the pair must then be counted twice
     imin[0, :] = imax[0, :]
     da_ref, dw_ref = c_oracle.backward(a.numpy(), w.numpy(), grad.numpy(), imax, imin, b_is_nk=True)
-    da, dw = capi.backward(a.to(cuda), w.to(cuda), grad.to(cuda),
-                           torch.from_numpy(imax).to(torch.int32).to(cuda),
-                           torch.from_numpy(imin).to(torch.int32).to(cuda), capi.NK)
+    from mamtorch_b200 import _lib
+    _lib.check(_lib.lib().mam_set_fwd_variant(3, mode), "backward form")
+    try:
+        da, dw = capi.backward(a.to(cuda), w.to(cuda), grad.to(cuda),
+                               torch.from_numpy(imax).to(torch.int32).to(cuda),
+                               torch.from_numpy(imin).to(torch.int32).to(cuda), capi.NK)
+        dak, dbk = capi.backward(a.to(cuda), w.T.contiguous().to(cuda), grad.to(cuda),
+                                 torch.from_numpy(imax).to(torch.int32).to(cuda),
+                                 torch.from_numpy(imin).to(torch.int32).to(cuda), capi.KN)
+    finally:
+        _lib.lib().mam_set_fwd_variant(3, 0)
     assert_grad_close(da.cpu().numpy(), da_ref)
     assert_grad_close(dw.cpu().numpy(), dw_ref)
+    assert_grad_close(dak.cpu().numpy(), da_ref)
+    assert_grad_close(dbk.T.cpu().numpy(), dw_ref)
+
+
+def test_backward_counts_hits_on_the_way(cuda):
+    import ctypes
+    from mamtorch_b200 import _lib
+
+    M, K, N = 3000, 768, 200
+    gen = torch.Generator().manual_seed(9)
+    a = torch.randn(M, K, generator=gen).to(cuda)
+    w = (torch.randn(N, K, generator=gen) * K ** -0.5).to(cuda)
+    grad = torch.randn(M, N, generator=gen).to(cuda)
+    _, imax, imin = capi.forward(a, w, capi.NK)
+    da_ref, dw_ref = capi.backward(a, w, grad, imax, imin, capi.NK)
+    hmax_ref, hmin_ref = capi.selcount(imax, imin, K)
+    da, dw = torch.empty_like(a), torch.empty_like(w)
+    hmax = torch.zeros((N, K), dtype=torch.int32, device=cuda)
+    hmin = torch.zeros((N, K), dtype=torch.int32, device=cuda)
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    for _ in range(2):  # counts accumulate, gradients are overwritten
+        st = _lib.lib().mam_bwd_count_f32(p(a), p(w), capi.NK, p(grad), p(imax), p(imin), p(da), p(dw), p(hmax), p(hmin),
+                                          1.0, M, K, N, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+        _lib.check(st, "mam_bwd_count_f32")
+    assert torch.equal(hmax, 2 * hmax_ref) and torch.equal(hmin, 2 * hmin_ref)
+    assert_grad_close(da.cpu().numpy(), da_ref.cpu().numpy())
+    assert_grad_close(dw.cpu().numpy(), dw_ref.cpu().numpy())
 
 
 @pytest.mark.parametrize("name", ["relu_pruned_64x96x64", "edge_128x160x128"])

@@ -11,8 +11,7 @@ from oracle import c_oracle
 
 pytestmark = pytest.mark.gpu
 
-IDX_VARIANTS = [-2, 0, 1, 2, 3]   # -2 = any-shape kernel, 0.. = tiled TMA configurations
-VAL_VARIANTS = [-2, 0, 1, 2, 3]
+IDX_VARIANTS = [-2, 0, 1, 2, 3, 4, 5, 6, 7]   # -2 = any-shape kernel, 0.. = tiled TMA configurations
 
 
 def _check_forward(a_np, b_np, y_ref, imax_ref, imin_ref, dev, variant, layout, bias_np=None):

@@ -223,3 +223,35 @@ def test_beta_blended_training_step(cuda):
     db_ref = beta * (x.double().T @ gy.double()) + (1 - beta) * torch.from_numpy(dw_m).double().T
     assert_grad_close(da.cpu().numpy(), da_ref.numpy(), rtol=1e-3)
     assert_grad_close(db.cpu().numpy(), db_ref.numpy(), rtol=1e-3)
+
+
+def test_conv_benchmark_shape_properties(cuda):
+    """The convolution configuration at full size (input [128,64,56,56], 3x3, 64->128 channels,
+    stride 1, pad 1: GEMM M=401408, K=576, N=128).  Too large for the CPU oracle, so check what holds
+    at any size: the output equals the sum of the two selected products bit for bit, indices are in
+    range, and a sample of pixels agrees with a direct evaluation of their patches."""
+    import mamtorch_b200 as mamtorch
+
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(128, 64, 56, 56, generator=g).to(cuda)
+    conv = mamtorch.nn.MAMConv2d(64, 128, 3, padding=1, bias=False).to(cuda)
+    with torch.no_grad():
+        conv.weight.copy_(torch.randn(128, 64, 3, 3, generator=g) * 576 ** -0.5)
+        y = conv(x)
+    assert y.shape == (128, 128, 56, 56)
+    assert int(conv.argmax.min()) >= 0 and int(conv.argmax.max()) < 576
+    xp = torch.nn.functional.pad(x, (1, 1, 1, 1))
+    w = conv.weight.detach()
+    for (b_, f, i, j) in [(0, 0, 0, 0), (127, 127, 55, 55), (64, 3, 17, 40), (5, 99, 55, 0)]:
+        p = (xp[b_, :, i:i + 3, j:j + 3] * w[f]).reshape(-1)
+        assert y[b_, f, i, j].item() == (p.max() + p.min()).item()
+        assert conv.argmax[b_, f, i, j].item() == int(p.argmax()) and conv.argmin[b_, f, i, j].item() == int(p.argmin())
+    # every output is the sum of the products its two indices point at
+    rows = torch.nn.functional.unfold(x[:8], 3, padding=1).transpose(1, 2).reshape(-1, 576)
+    wf = w.reshape(128, -1)
+    im = conv.argmax[:8].permute(0, 2, 3, 1).reshape(-1, 128).long()
+    imn = conv.argmin[:8].permute(0, 2, 3, 1).reshape(-1, 128).long()
+    r = torch.arange(rows.shape[0], device=cuda)[:, None].expand_as(im)
+    c = torch.arange(128, device=cuda)[None, :].expand_as(im)
+    want = rows[r, im] * wf[c, im] + rows[r, imn] * wf[c, imn]
+    assert torch.equal(y[:8].permute(0, 2, 3, 1).reshape(-1, 128), want)

@@ -74,3 +74,20 @@ def test_cusparsemm_matches_dense_product(layout, cuda):
     c = mamtorch.sparse.kernel.v1.cusparsemm(a_sp, b.to(cuda))
     ref = a.double() @ b.double()
     np.testing.assert_allclose(c.cpu().numpy(), ref.numpy(), rtol=1e-5, atol=1e-5)
+
+
+def test_sharded_pruned_layer_shape_equals_dense_kernels(cuda):
+    """One rank's share of the large sharded configuration (M=65536 rows over 8 ranks = 8192, K=N=4096,
+    90 % of W pruned): the CSR kernel must reproduce, bit for bit, what the dense kernels give on the
+    zero-filled weight (which the oracle-pinned tests cover at small sizes)."""
+    import mamtorch_b200 as mamtorch
+
+    M, K, N = 8192, 4096, 4096
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(M, K, generator=g).to(cuda)
+    w = (torch.randn(N, K, generator=g) * K ** -0.5).to(cuda)
+    mask = (torch.rand(N, K, generator=g) >= 0.9).float().to(cuda)
+    wz = w * mask
+    y, imax, imin = mamtorch.sparse.kernel.v1.mam_linear_csr(x, wz.to_sparse_csr())
+    yd, imaxd, imind = torch.ops.mamtorch_b200.linear_forward(x, wz, None, None, 1.0, 0.0, True)
+    assert torch.equal(y, yd) and torch.equal(imax, imaxd) and torch.equal(imin, imind)
