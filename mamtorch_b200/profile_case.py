@@ -5,7 +5,8 @@ captures are taken on.
 
 ops: fwd_idx (forward with indices: tiled kernel + index resolver), fwd_val (values only),
 bwd (selected-pair backward), selcount, step (forward + backward + selection count of one layer
-through the nn module).  Inputs are seeded N(0,1) activations and N(0,1/K) weights in [N,K] layout.
+through the nn module), dense_tf32 (tcgen05 product of the beta term), csr_fwd (forward on a weight
+pruned to 90 % sparsity, CSR).  Inputs are seeded N(0,1) activations and N(0,1/K) weights in [N,K] layout.
 """
 import argparse
 
@@ -15,7 +16,7 @@ import torch
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--shape", default="4096x1024x2048", help="MxKxN")
-    ap.add_argument("--op", default="fwd_idx", choices=["fwd_idx", "fwd_val", "bwd", "selcount", "step"])
+    ap.add_argument("--op", default="fwd_idx", choices=["fwd_idx", "fwd_val", "bwd", "selcount", "step", "dense_tf32", "csr_fwd"])
     ap.add_argument("--reps", type=int, default=3)
     ap.add_argument("--variant", type=int, default=-1, help="tile configuration of the tiled forward (-1 auto)")
     args = ap.parse_args()
@@ -44,6 +45,13 @@ def main():
             ops.linear_backward(x, w, gy, imax, imin, 1.0)
         elif args.op == "selcount":
             MF.selection_hits(imax, imin, K)
+        elif args.op == "dense_tf32":
+            y = ops.dense_nt(x, w)
+        elif args.op == "csr_fwd":
+            if "w_csr" not in locals():
+                keep = (torch.rand(N, K, generator=g) >= 0.9).float().to(dev)
+                w_csr = (w * keep).to_sparse_csr()
+            y, imax, imin = mamtorch.sparse.kernel.v1.mam_linear_csr(x, w_csr)
         else:
             layer = mamtorch.nn.FullyConnected(K, N, store_args=True).to(dev)
             out = layer(x.clone().requires_grad_())
