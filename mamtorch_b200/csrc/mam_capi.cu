@@ -320,14 +320,21 @@ int mam_fwd_f32(const float* a, const float* b, int b_layout, const float* bias,
         } else if (want_idx) {
             variant = 1;  // 4x8 outputs per thread, 64x128 tile
         } else {
-            // 8x8 per thread on 128x128 tiles is ~10% faster per unit than 4x8 on 64x128 tiles, but its
-            // last wave of tiles can leave most SMs idle: weigh both by their wave efficiency
-            auto eff = [&](long long bm, long long bn) {
-                const long long tiles = ((M + bm - 1) / bm) * ((N + bn - 1) / bn);
+            // Candidates differ in speed per unit (measured, units/clk/SM) and in how well their tile
+            // count fills whole waves of SMs; pick the best product of the two.
+            struct Cand { int variant; long long bm, bn; double rate; };
+            const Cand cands[3] = {{2, 128, 128, 42.9}, {3, 96, 128, 40.0}, {6, 64, 128, 39.3}};
+            double best = -1.0;
+            for (const Cand& c : cands) {
+                const long long tiles = ((M + c.bm - 1) / c.bm) * ((N + c.bn - 1) / c.bn);
                 const long long waves = (tiles + d->sms - 1) / d->sms;
-                return (double)tiles / (double)(waves * d->sms);
-            };
-            variant = (eff(128, 128) * 1.10 >= eff(64, 128)) ? 2 : 6;
+                // work actually executed includes the padding of edge tiles
+                const double useful = (double)M * (double)N / ((double)waves * d->sms * c.bm * c.bn);
+                if (useful * c.rate > best) {
+                    best = useful * c.rate;
+                    variant = c.variant;
+                }
+            }
         }
     }
     if (variant >= 0 && !tma_ok) variant = -2;

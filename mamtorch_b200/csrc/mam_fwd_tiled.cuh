@@ -80,6 +80,15 @@ __device__ __forceinline__ void static_for(F&& f) {
 __device__ __forceinline__ ulonglong2 lds128(const unsigned char* p) {
     return *reinterpret_cast<const ulonglong2*>(p);
 }
+// LDS.128 from a 32-bit shared-window address plus a compile-time byte offset.  Going through a
+// generic pointer instead costs two integer adds per load on the ALU pipe -- the pipe the max/min
+// instructions saturate.
+template <int OFF>
+__device__ __forceinline__ ulonglong2 lds128_at(uint32_t addr) {
+    ulonglong2 v;
+    asm volatile("ld.shared.v2.u64 {%0, %1}, [%2+%3];" : "=l"(v.x), "=l"(v.y) : "r"(addr), "n"(OFF));
+    return v;
+}
 
 template <class Cfg>
 __global__ void __launch_bounds__(Cfg::THREADS, 1)
@@ -175,21 +184,25 @@ mam_fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                 ok = false;
                 break;
             }
-            const unsigned char* sbase = smem + stage * Cfg::STAGE_BYTES;
-            const unsigned char* ap = sbase + a_row0;
-            const unsigned char* wp = sbase + w_row0;
+            const uint32_t sbase = smem_u32(smem) + (uint32_t)(stage * Cfg::STAGE_BYTES);
+            const uint32_t ap = sbase + a_row0;
+            const uint32_t wp = sbase + w_row0;
             float lmax[TRACK ? TM : 1][TRACK ? TN : 1], lmin[TRACK ? TM : 1][TRACK ? TN : 1];
 
             auto quad = [&](const int q, const bool first) {
-                const uint32_t xa0 = ((uint32_t)q << 4) ^ a_key;
+                // ap and wp are 128-byte aligned and the swizzled group offset is < 128, so OR is ADD
+                // and each address is one three-input logic op
+                const uint32_t xa0 = ap | (((uint32_t)q << 4) ^ a_key);
                 const uint32_t xa1 = xa0 ^ 64u;
-                const uint32_t xw = ((uint32_t)q << 4) ^ w_key;
+                const uint32_t xw = wp | (((uint32_t)q << 4) ^ w_key);
                 ulonglong2 av[TM];
-#pragma unroll
-                for (int i = 0; i < TM; ++i) av[i] = lds128(ap + ((i & 1) ? xa1 : xa0) + i * 512);
-#pragma unroll
-                for (int j = 0; j < TN; ++j) {
-                    const ulonglong2 wv = lds128(wp + xw + j * 1024);
+                static_for<0, TM>([&](auto ic) {
+                    constexpr int i = decltype(ic)::value;
+                    av[i] = lds128_at<i * 512>((i & 1) ? xa1 : xa0);
+                });
+                static_for<0, TN>([&](auto jc) {
+                    constexpr int j = decltype(jc)::value;
+                    const ulonglong2 wv = lds128_at<j * 1024>(xw);
                     float p[TM][4];
                     auto products = [&](int i) {
                         if constexpr (Cfg::MUL2) {
@@ -229,7 +242,7 @@ mam_fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                             vmin[i][j] = fmin3(fmin3(vmin[i][j], p[i][0], p[i][1]), p[i][2], p[i][3]);
                         }
                     }
-                }
+                });
             };
 
             // one code path for full and ragged chunks: the first group is peeled (it initialises
