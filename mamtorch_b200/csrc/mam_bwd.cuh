@@ -136,35 +136,62 @@ mam_bwd_dw_kernel(const float* __restrict__ a, const float* __restrict__ g,
 }
 
 // True selection counts: cnt_max[n,k] += #rows with argmax[m,n]==k, same for min.  A CTA owns
-// `cols` consecutive outputs n and keeps their [cols][K] int32 counters for max and for min in
-// shared memory (integer shared-memory atomics are an order of magnitude faster than fp32 ones),
-// sweeps all M rows, then adds the counters to the caller's [N,K] matrices.
+// COLS consecutive outputs n (COLS*4 bytes = one 32-byte sector of each index row when COLS is 8)
+// and one slice of the rows; it keeps the [COLS][K] int32 counters for max and for min in shared
+// memory (integer shared-memory atomics run ~7x faster than fp32 ones), sweeps its rows with
+// SEL_UNROLL independent loads in flight per thread (the sweep is a pure stream: without them it
+// is bound by load latency, not by HBM), then adds its non-zero counters to the caller's [N,K]
+// matrices -- atomically, because the CTAs of the other row slices add into the same entries.
 // The module-level rule of the reference (mamtorch/nn/v4/fullyconnected.py:114-131) is derived
 // from these on the host side: +1 where cnt_max>0, +1 where cnt_min>0.
-__global__ void __launch_bounds__(256)
+constexpr int SEL_THREADS = 256;
+constexpr int SEL_UNROLL = 8;
+
+template <int COLS>
+__global__ void __launch_bounds__(SEL_THREADS)
 mam_selcount_kernel(const int* __restrict__ argmax, const int* __restrict__ argmin,
                     int* __restrict__ cnt_max, int* __restrict__ cnt_min,
-                    long long M, long long K, long long N, int cols) {
-    extern __shared__ int cnt_s[];  // [2][cols][K]
-    const long long n0 = (long long)blockIdx.x * cols;
-    const int nc = (int)min((long long)cols, N - n0);
-    const long long tot = 2LL * cols * K;
-    for (long long i = threadIdx.x; i < tot; i += 256) cnt_s[i] = 0;
+                    long long M, long long K, long long N, long long rows_per_slice) {
+    extern __shared__ int cnt_s[];  // [2][COLS][K]
+    const long long n0 = (long long)blockIdx.x * COLS;
+    const int nc = (int)min((long long)COLS, N - n0);
+    const long long m_begin = (long long)blockIdx.y * rows_per_slice;
+    const long long m_end = min(M, m_begin + rows_per_slice);
+    const long long tot = 2LL * COLS * K;
+    for (long long i = threadIdx.x; i < tot; i += SEL_THREADS) cnt_s[i] = 0;
     __syncthreads();
-    // threads: c = tid % nc fastest so that the nc consecutive ints of a row are read together
-    const long long work = M * nc;
-    for (long long t = threadIdx.x; t < work; t += 256) {
-        const long long m = t / nc;
-        const int c = (int)(t % nc);
-        const int k1 = argmax[m * N + n0 + c], k2 = argmin[m * N + n0 + c];
-        if ((unsigned)k1 < (unsigned long long)K) atomicAdd(&cnt_s[(long long)c * K + k1], 1);
-        if ((unsigned)k2 < (unsigned long long)K) atomicAdd(&cnt_s[((long long)cols + c) * K + k2], 1);
+    constexpr int ROWS_PER_PASS = SEL_THREADS / COLS;
+    const int c = threadIdx.x % COLS, r = threadIdx.x / COLS;
+    int* my_max = cnt_s + (long long)c * K;
+    int* my_min = cnt_s + ((long long)COLS + c) * K;
+    if (c < nc) {
+        const int* pmax = argmax + n0 + c;
+        const int* pmin = argmin + n0 + c;
+        for (long long m = m_begin + r; m < m_end; m += (long long)ROWS_PER_PASS * SEL_UNROLL) {
+            int k1[SEL_UNROLL], k2[SEL_UNROLL];
+#pragma unroll
+            for (int u = 0; u < SEL_UNROLL; ++u) {
+                const long long mm = m + (long long)u * ROWS_PER_PASS;
+                k1[u] = -1;
+                k2[u] = -1;
+                if (mm < m_end) {
+                    k1[u] = __ldg(pmax + mm * N);
+                    k2[u] = __ldg(pmin + mm * N);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < SEL_UNROLL; ++u) {
+                // an index outside [0,K) cannot come from the forward; skip it rather than fault
+                if ((unsigned)k1[u] < (unsigned long long)K) atomicAdd(&my_max[k1[u]], 1);
+                if ((unsigned)k2[u] < (unsigned long long)K) atomicAdd(&my_min[k2[u]], 1);
+            }
+        }
     }
     __syncthreads();
-    for (long long i = threadIdx.x; i < (long long)nc * K; i += 256) {
-        const int vmax = cnt_s[i], vmin = cnt_s[(long long)cols * K + i];
-        if (vmax) cnt_max[n0 * K + i] += vmax;
-        if (vmin) cnt_min[n0 * K + i] += vmin;
+    for (long long i = threadIdx.x; i < (long long)nc * K; i += SEL_THREADS) {
+        const int vmax = cnt_s[i], vmin = cnt_s[(long long)COLS * K + i];
+        if (vmax) atomicAdd(&cnt_max[n0 * K + i], vmax);
+        if (vmin) atomicAdd(&cnt_min[n0 * K + i], vmin);
     }
 }
 

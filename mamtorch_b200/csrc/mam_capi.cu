@@ -502,18 +502,39 @@ int mam_selcount_i32(const int32_t* argmax, const int32_t* argmin, int32_t* hit_
     if (st != MAM_OK) return st;
     const long long budget = (long long)d->max_smem - 1024;
     if (2 * K * 4 > budget) return MAM_ERR_UNSUPPORTED;
-    int cols = (int)(budget / (2 * K * 4));
-    if (cols > 8) cols = 8;
-    // keep at least ~2 CTAs per SM worth of blocks when N allows it
-    while (cols > 1 && (N + cols - 1) / cols < 2LL * d->sms) cols >>= 1;
+    // Columns per CTA: 8 ints = one 32-byte sector of every index row; fewer only when the
+    // counters of 8 columns would not leave room for two CTAs per SM (or would not fit at all).
+    int cols = 8;
+    while (cols > 1 && 2LL * cols * K * 4 > budget / 2) cols >>= 1;
     const size_t smem = 2ull * cols * (size_t)K * 4;
-    const long long grid = (N + cols - 1) / cols;
-    MAM_CUDA(cudaFuncSetAttribute(mam_selcount_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    {
-        TimedLaunch t(MAM_KERNEL_SELCOUNT, (cudaStream_t)stream);
-        mam_selcount_kernel<<<(unsigned)grid, 256, smem, (cudaStream_t)stream>>>(argmax, argmin, hit_max, hit_min, M,
-                                                                                 K, N, cols);
+    const long long col_blocks = (N + cols - 1) / cols;
+    if (col_blocks > 2147483647LL) return MAM_ERR_UNSUPPORTED;
+    // Row slices: enough CTAs for ~3 rounds over the SMs, each slice at least 512 rows.
+    long long ctas_per_sm = (long long)(budget / (long long)smem);
+    if (ctas_per_sm > 8) ctas_per_sm = 8;
+    if (ctas_per_sm < 1) ctas_per_sm = 1;
+    long long slices = (3LL * d->sms * ctas_per_sm + col_blocks - 1) / col_blocks;
+    const long long max_slices = (M + 511) / 512;
+    if (slices > max_slices) slices = max_slices;
+    if (slices < 1) slices = 1;
+    if (slices > 65535) slices = 65535;
+    const long long rows_per_slice = (M + slices - 1) / slices;
+    slices = (M + rows_per_slice - 1) / rows_per_slice;
+    const dim3 grid((unsigned)col_blocks, (unsigned)slices);
+    cudaStream_t cs = (cudaStream_t)stream;
+    auto launch = [&](auto kern) -> int {
+        MAM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        TimedLaunch t(MAM_KERNEL_SELCOUNT, cs);
+        kern<<<grid, SEL_THREADS, smem, cs>>>(argmax, argmin, hit_max, hit_min, M, K, N, rows_per_slice);
+        return MAM_OK;
+    };
+    switch (cols) {
+        case 8: st = launch(mam_selcount_kernel<8>); break;
+        case 4: st = launch(mam_selcount_kernel<4>); break;
+        case 2: st = launch(mam_selcount_kernel<2>); break;
+        default: st = launch(mam_selcount_kernel<1>); break;
     }
+    if (st != MAM_OK) return st;
     MAM_CUDA(cudaGetLastError());
     return MAM_OK;
 }
