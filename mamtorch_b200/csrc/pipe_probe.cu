@@ -307,6 +307,91 @@ static void run(int sms, float* d_out, long long* d_clk) {
     }
 }
 
+// ---------------------------------------------------------------- datapath-sharing probes
+// Register-only streams with NO dependency between the max/min instructions and the multiplies:
+// whatever slows the mix down here is the hardware's issue/datapath structure, not latency.
+//   0  max.f32 (3-input) alone, all three sources distinct registers
+//   1  2 max3 : 1 mul.rn.f32x2 with register operands      (the instruction mix of the MAM loop)
+//   2  2 max3 : 2 scalar mul.rn.f32 with register operands (same work, scalar multiplies)
+//   3  2 max3 : 1 scalar mul.rn.f32 by an immediate         (multiplies the compiler can keep scalar)
+// Reported: max3 instructions per clock per SM (64 = the ALU pipe saturated).
+template <int VAR>
+__global__ void __launch_bounds__(THREADS, 1)
+share_probe_kernel(float* out, int iters, long long* clk_out) {
+    float m[32];
+    f32x2_t s[16], f[16], g[16];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) m[i] = out[i] + threadIdx.x;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        s[i] = pack2(out[i + 32] + threadIdx.x, out[i + 33]);
+        f[i] = pack2(out[i + 48] * 0.f + 1.f, 1.0f + out[i + 49] * 0.f);
+        g[i] = pack2(1.f + out[i + 50] * 0.f, 1.f + out[i + 51] * 0.f);
+    }
+    long long t0 = clock64();
+    for (int it = 0; it < iters; ++it) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                float lo, hi;
+                unpack2(s[(i * 5 + r * 3) & 15], lo, hi);
+                asm volatile("max.f32 %0, %0, %1, %2;" : "+f"(m[i]) : "f"(lo), "f"(hi));
+                if ((i & 1) == 0) {
+                    const int fi = i >> 1, gi = ((i >> 1) * 3 + r) & 15;
+                    if constexpr (VAR == 1) {
+                        asm volatile("mul.rn.f32x2 %0, %0, %1;" : "+l"(f[fi]) : "l"(g[gi]));
+                    } else if constexpr (VAR == 2) {
+                        float a0, a1, b0, b1;
+                        unpack2(f[fi], a0, a1);
+                        unpack2(g[gi], b0, b1);
+                        asm volatile("mul.rn.f32 %0, %0, %1;" : "+f"(a0) : "f"(b0));
+                        asm volatile("mul.rn.f32 %0, %0, %1;" : "+f"(a1) : "f"(b1));
+                        f[fi] = pack2(a0, a1);
+                    } else if constexpr (VAR == 3) {
+                        float a0, a1;
+                        unpack2(f[fi], a0, a1);
+                        asm volatile("mul.rn.f32 %0, %0, 0f3F800001;" : "+f"(a0));
+                        f[fi] = pack2(a0, a1);
+                    }
+                }
+            }
+        }
+    }
+    long long t1 = clock64();
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) acc += m[i];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        float lo, hi;
+        unpack2(f[i], lo, hi);
+        acc += lo + hi;
+    }
+    out[blockIdx.x * THREADS + threadIdx.x + 64] = acc;
+    if (threadIdx.x == 0) clk_out[blockIdx.x] = t1 - t0;
+}
+
+template <int VAR>
+static void run_share(int sms, float* d_out, long long* d_clk) {
+    static const char* nm[4] = {"share_max3_only", "share_2max3_1fmul2_reg", "share_2max3_2fmul_reg",
+                                "share_2max3_1fmul_imm"};
+    const int iters = 2000;
+    share_probe_kernel<VAR><<<sms, THREADS>>>(d_out, 20, d_clk);
+    CK(cudaDeviceSynchronize());
+    share_probe_kernel<VAR><<<sms, THREADS>>>(d_out, iters, d_clk);
+    CK(cudaDeviceSynchronize());
+    std::vector<long long> clk(sms);
+    CK(cudaMemcpy(clk.data(), d_clk, sms * sizeof(long long), cudaMemcpyDeviceToHost));
+    double mean_clk = 0;
+    for (auto c : clk) mean_clk += (double)c;
+    mean_clk /= sms;
+    printf("{\"probe\": \"%s\", \"counted\": \"max3 instructions\", \"threads_per_sm\": %d, "
+           "\"per_clk_per_sm\": %.2f}\n",
+           nm[VAR], THREADS, (double)iters * 4 * 32 * THREADS / mean_clk);
+    fflush(stdout);
+}
+
 // ---------------------------------------------------------------- scatter-add probes
 // SPACE 0: fp32 atomic add into shared memory bins; 1: fp32 red.global.add into an L2-resident
 // matrix; 2: int32 atomic add into shared memory.  Addresses are pseudo-random with no
@@ -396,6 +481,10 @@ int main() {
     run<MIX_MUL2_MAX3>(sms, d_out, d_clk);
     run<MIX_NAIVE_INDEX>(sms, d_out, d_clk);
     run<MIX_BLOCKTRACK>(sms, d_out, d_clk);
+    run_share<0>(sms, d_out, d_clk);
+    run_share<1>(sms, d_out, d_clk);
+    run_share<2>(sms, d_out, d_clk);
+    run_share<3>(sms, d_out, d_clk);
     run_scatter<0>(sms, d_clk);
     run_scatter<1>(sms, d_clk);
     run_scatter<2>(sms, d_clk);
