@@ -558,7 +558,8 @@ int mam_dense_tf32(const float* a, const float* w, float* out, float c_acc, floa
     MAM_CUDA(cudaFuncSetAttribute(mam_dense_tf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DG_SMEM_BYTES));
     {
         TimedLaunch t(MAM_KERNEL_DENSE_TF32, (cudaStream_t)stream);
-        mam_dense_tf32_kernel<<<(unsigned)tiles, DG_THREADS, DG_SMEM_BYTES, (cudaStream_t)stream>>>(
+        const unsigned grid = (unsigned)(tiles < d->sms ? tiles : d->sms);  // persistent: one CTA per SM
+        mam_dense_tf32_kernel<<<grid, DG_THREADS, DG_SMEM_BYTES, (cudaStream_t)stream>>>(
             tmA, tmW, out, M, K, N, c_acc, c_out, flag);
     }
     MAM_CUDA(cudaGetLastError());

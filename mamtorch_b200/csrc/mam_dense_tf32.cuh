@@ -6,14 +6,20 @@
 // SIMT `dense_cuda_kernel` (mamtorch/kernel/v2/csrc/cuda/dense.cu:33-144).  The max/min semiring of
 // the MAM term cannot use tensor cores; this sum-of-products term can.
 //
-// One 128x128 output tile per CTA, 192 threads in three roles:
-//   warp 0, one lane : TMA producer -- [128 rows][32 floats] boxes of a and W (both K-contiguous, 128-byte
-//                      swizzle) into a STAGES-deep full/empty mbarrier ring;
-//   warp 1, one lane : issues tcgen05.mma.cta_group::1.kind::tf32 (M=128, N=128, K=8; four per stage,
-//                      stepping the shared-memory descriptors 32 bytes along K), accumulating in
-//                      128 columns of tensor memory that warp 1 allocates and frees; tcgen05.commit
-//                      hands each stage back to the producer and finally signals the epilogue;
-//   warps 2..5       : epilogue -- tcgen05.ld (32 lanes x 32 columns per instruction), scale/blend, store.
+// Persistent kernel, one CTA of 192 threads per SM walking 128x256 output tiles, three roles:
+//   warp 0, one lane : TMA producer -- [128][32 floats] of a and [256][32 floats] of W per stage (both
+//                      K-contiguous, 128-byte swizzle) into a 4-deep full/empty mbarrier ring that
+//                      runs straight across tile boundaries;
+//   warp 1, one lane : issues tcgen05.mma.cta_group::1.kind::tf32 (M=128, N=256, K=8; four per stage,
+//                      stepping the shared-memory descriptors 32 bytes along K).  The accumulator
+//                      alternates between the two 256-column halves of tensor memory, so the MMAs of
+//                      tile i+1 run while the epilogue drains tile i; tcgen05.commit hands each stage
+//                      back to the producer and each finished accumulator to the epilogue;
+//   warps 2..5       : epilogue -- tcgen05.ld (32 lanes x 32 columns per instruction), a turn through a
+//                      padded shared-memory block so that global accesses are whole 128-byte row
+//                      segments, scale/blend, store, then release of the accumulator half.
+// 128x256 rather than 128x128 because the product is fed from L2: a 128x128 tile needs 32 KB of
+// operands per 1.05 MFLOP, a 128x256 tile 48 KB per 2.1 MFLOP.
 // Rows and columns beyond M, N and the k tail are zero-filled by TMA (zeros are neutral for a sum)
 // and masked at the store.  Every mbarrier wait is bounded; on expiry the kernel raises the
 // device flag, still frees its tensor memory and returns.
@@ -23,12 +29,13 @@
 
 namespace mamb200 {
 
-constexpr int DG_BM = 128, DG_BN = 128, DG_BK = 32, DG_STAGES = 6;
+constexpr int DG_BM = 128, DG_BN = 256, DG_BK = 32, DG_STAGES = 4;
 constexpr int DG_THREADS = 192;
 constexpr int DG_A_BYTES = DG_BM * DG_BK * 4, DG_B_BYTES = DG_BN * DG_BK * 4;
 constexpr int DG_STAGE_BYTES = DG_A_BYTES + DG_B_BYTES;
-constexpr int DG_SMEM_BYTES = 1024 + DG_STAGES * DG_STAGE_BYTES + (2 * DG_STAGES + 1) * 8 + 16;
-constexpr int DG_TMEM_COLS = 128;
+constexpr int DG_EPI_BYTES = 4 * 32 * 33 * 4;  // one padded 32x32 fp32 block per epilogue warp
+constexpr int DG_SMEM_BYTES = 1024 + DG_STAGES * DG_STAGE_BYTES + (2 * DG_STAGES + 4) * 8 + 16 + DG_EPI_BYTES;
+constexpr int DG_TMEM_COLS = 2 * DG_BN;  // two accumulators of 256 fp32 columns: all of tensor memory
 
 // Instruction descriptor of tcgen05.mma kind::tf32: fp32 accumulator (bits 4-5 = 1), TF32 A and B
 // (bits 7-9 and 10-12 = 2), both operands K-major (bits 15, 16 = 0), N>>3 at bit 17, M>>4 at bit 24.
@@ -67,6 +74,18 @@ __device__ __forceinline__ void tc_commit(uint64_t* bar) {
                  : "memory");
 }
 
+// Tile order: bands of DG_BAND tile-rows, walked row-fastest inside a band, so that the CTAs running
+// at the same time share a few row-tiles of a and a run of adjacent column-tiles of W in L2.
+constexpr int DG_BAND = 8;
+__device__ __forceinline__ void dg_tile_coords(long long tile, int ntm, int ntn, int& tm, int& tn) {
+    const long long per_band = (long long)DG_BAND * ntn;
+    const int band = (int)(tile / per_band);
+    const int r = (int)(tile - (long long)band * per_band);
+    const int rows = min(DG_BAND, ntm - band * DG_BAND);
+    tm = band * DG_BAND + r % rows;
+    tn = r / rows;
+}
+
 __global__ void __launch_bounds__(DG_THREADS, 1)
 mam_dense_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW,
                       float* __restrict__ out, long long M, long long K, long long N, float c_acc, float c_out,
@@ -76,12 +95,14 @@ mam_dense_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         (reinterpret_cast<uintptr_t>(dg_smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + DG_STAGES * DG_STAGE_BYTES);
     uint64_t* empty_bar = full_bar + DG_STAGES;
-    uint64_t* accum_bar = empty_bar + DG_STAGES;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
+    uint64_t* acc_full = empty_bar + DG_STAGES;  // [2] accumulator half holds a finished tile
+    uint64_t* acc_empty = acc_full + 2;          // [2] accumulator half has been drained
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int ntn = (int)((N + DG_BN - 1) / DG_BN);
-    const int tm = blockIdx.x / ntn, tn = blockIdx.x % ntn;
+    const int ntm = (int)((M + DG_BM - 1) / DG_BM);
+    const long long ntiles = (long long)ntm * ntn;
     const int nk = (int)((K + DG_BK - 1) / DG_BK);
 
     if (threadIdx.x == 0) {
@@ -89,7 +110,10 @@ mam_dense_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], 1);
         }
-        mbar_init(accum_bar, 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], 4);  // one arrival per epilogue warp
+        }
         mbar_fence_init();
     }
     if (warp == 1) {
@@ -109,16 +133,22 @@ mam_dense_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             tma_prefetch_desc(&tmW);
             int stage = 0;
             uint32_t phase = 0;
-            for (int kc = 0; kc < nk; ++kc) {
-                if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u)) {
-                    atomicExch(error, 1);
-                    break;
+            bool ok = true;
+            for (long long tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+                int tm, tn;
+                dg_tile_coords(tile, ntm, ntn, tm, tn);
+                for (int kc = 0; kc < nk; ++kc) {
+                    if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u)) {
+                        atomicExch(error, 1);
+                        ok = false;
+                        break;
+                    }
+                    mbar_expect_tx(&full_bar[stage], DG_STAGE_BYTES);
+                    unsigned char* sa = smem + stage * DG_STAGE_BYTES;
+                    tma_load_2d(sa, &tmA, &full_bar[stage], kc * DG_BK, tm * DG_BM);
+                    tma_load_2d(sa + DG_A_BYTES, &tmW, &full_bar[stage], kc * DG_BK, tn * DG_BN);
+                    if (++stage == DG_STAGES) { stage = 0; phase ^= 1u; }
                 }
-                mbar_expect_tx(&full_bar[stage], DG_STAGE_BYTES);
-                unsigned char* sa = smem + stage * DG_STAGE_BYTES;
-                tma_load_2d(sa, &tmA, &full_bar[stage], kc * DG_BK, tm * DG_BM);
-                tma_load_2d(sa + DG_A_BYTES, &tmW, &full_bar[stage], kc * DG_BK, tn * DG_BN);
-                if (++stage == DG_STAGES) { stage = 0; phase ^= 1u; }
             }
         }
     } else if (warp == 1) {
@@ -126,39 +156,56 @@ mam_dense_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int kc = 0; kc < nk && ok; ++kc) {
-                if (!mbar_wait_bounded(&full_bar[stage], phase)) {
+            long long it = 0;  // tiles done by this CTA
+            for (long long tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++it) {
+                const int buf = (int)(it & 1);
+                // the half must have been drained by the epilogue of the tile two steps back
+                if (!mbar_wait_bounded(&acc_empty[buf], (uint32_t)((it >> 1) & 1) ^ 1u)) {
                     atomicExch(error, 1);
-                    ok = false;
                     break;
                 }
                 tc_fence_after();
-                const uint32_t a_addr = smem_u32(smem + stage * DG_STAGE_BYTES);
-                const uint32_t b_addr = a_addr + DG_A_BYTES;
+                const uint32_t tmem_d = tmem_base + (uint32_t)(buf * DG_BN);
+                for (int kc = 0; kc < nk; ++kc) {
+                    if (!mbar_wait_bounded(&full_bar[stage], phase)) {
+                        atomicExch(error, 1);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(smem + stage * DG_STAGE_BYTES);
+                    const uint32_t b_addr = a_addr + DG_A_BYTES;
 #pragma unroll
-                for (int k = 0; k < DG_BK / 8; ++k) {
-                    // 8 tf32 = 32 bytes along K inside the 128-byte swizzle span: +2 in the address field
-                    const uint64_t adesc = dg_smem_desc(a_addr + k * 32);
-                    const uint64_t bdesc = dg_smem_desc(b_addr + k * 32);
-                    tc_mma_tf32(tmem_base, adesc, bdesc, dg_idesc(), (kc | k) ? 1u : 0u);
+                    for (int k = 0; k < DG_BK / 8; ++k) {
+                        // 8 tf32 = 32 bytes along K inside the 128-byte swizzle span: +2 in the address field
+                        const uint64_t adesc = dg_smem_desc(a_addr + k * 32);
+                        const uint64_t bdesc = dg_smem_desc(b_addr + k * 32);
+                        tc_mma_tf32(tmem_d, adesc, bdesc, dg_idesc(), (kc | k) ? 1u : 0u);
+                    }
+                    tc_commit(&empty_bar[stage]);  // stage is free once these MMAs have read it
+                    if (++stage == DG_STAGES) { stage = 0; phase ^= 1u; }
                 }
-                tc_commit(&empty_bar[stage]);  // stage is free once these MMAs have read it
-                if (++stage == DG_STAGES) { stage = 0; phase ^= 1u; }
+                if (ok) tc_commit(&acc_full[buf]);  // arrives when every MMA of this tile has completed
             }
-            tc_commit(accum_bar);  // arrives when every MMA issued so far has completed
         }
     } else {
         // epilogue warps 2..5: TMEM lane quarter = warp % 4
         const int quarter = warp & 3;
-        const bool ready = mbar_wait_bounded(accum_bar, 0);
-        if (!ready) atomicExch(error, 1);
-        tc_fence_after();
-        const long long m = (long long)tm * DG_BM + quarter * 32 + lane;
-        if (ready) {
+        float* stage_s = reinterpret_cast<float*>(tmem_slot + 4) + (warp - 2) * (32 * 33);
+        long long it = 0;
+        for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++it) {
+            int tm, tn;
+            dg_tile_coords(tile, ntm, ntn, tm, tn);
+            const int buf = (int)(it & 1);
+            if (!mbar_wait_bounded(&acc_full[buf], (uint32_t)((it >> 1) & 1))) {
+                atomicExch(error, 1);
+                break;
+            }
+            tc_fence_after();
 #pragma unroll 1
             for (int cg = 0; cg < DG_BN / 32; ++cg) {
                 uint32_t r[32];
-                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(cg * 32);
+                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * DG_BN + cg * 32);
                 asm volatile(
                     "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
                     "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -171,19 +218,30 @@ mam_dense_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                     : "r"(taddr)
                     : "memory");
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (m < M) {
-                    const long long n0 = (long long)tn * DG_BN + cg * 32;
-                    float* o = out + m * N + n0;
+                // thread = row here; turn the 32x32 block through shared memory so that every global
+                // access of the warp is one 128-byte row segment
+                __syncwarp();
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        if (n0 + i < N) {
-                            float v = __uint_as_float(r[i]) * c_acc;
-                            if (c_out != 0.f) v = fmaf(c_out, o[i], v);
-                            o[i] = v;
+                for (int i = 0; i < 32; ++i) stage_s[lane * 33 + i] = __uint_as_float(r[i]) * c_acc;
+                __syncwarp();
+                const long long n = (long long)tn * DG_BN + cg * 32 + lane;
+                const long long mrow0 = (long long)tm * DG_BM + quarter * 32;
+                if (n < N) {
+#pragma unroll 8
+                    for (int rr = 0; rr < 32; ++rr) {
+                        if (mrow0 + rr < M) {
+                            float* o = out + (mrow0 + rr) * N + n;
+                            float v = stage_s[rr * 33 + lane];
+                            if (c_out != 0.f) v = fmaf(c_out, *o, v);
+                            *o = v;
                         }
                     }
                 }
             }
+            // every tcgen05.ld of this half has completed (wait::ld above): hand it back to the MMA warp
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
         }
     }
     tc_fence_before();
