@@ -34,6 +34,8 @@ ABI = {
     "mam_selcount_indicator_i32": (_i32, [_vp, _vp, _vp, _i64, _vp]),
     "mam_dense_tf32": (_i32, [_vp, _vp, _vp, _f32, _f32, _i64, _i64, _i64, _vp]),
     "mam_csr_fwd_f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
+    "mam_csr_fwd_workspace_bytes": (ctypes.c_size_t, [_i64, _i64, _i64, _i64]),
+    "mam_csr_fwd_ws_f32": (_i32, [_vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, ctypes.c_size_t, _vp]),
     "mam_spmm_csr_f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "mam_transpose_f32": (_i32, [_vp, _vp, _i64, _i64, _vp]),
 }
@@ -47,7 +49,7 @@ _shim_loaded = False
 def _missing(path: str) -> ImportError:
     return ImportError(
         f"mamtorch_b200: native library {path} is missing. Build it in-tree with "
-        f"`python -m mamtorch_b200._build` (needs nvcc and g++); there is no CPU fallback.")
+        f"`python mamtorch_b200/_build.py` (needs nvcc and g++); there is no CPU fallback.")
 
 
 def lib() -> ctypes.CDLL:

@@ -8,6 +8,7 @@
 #include "../../include/mam_b200.h"
 #include "mam_bwd.cuh"
 #include "mam_csr.cuh"
+#include "mam_csr_tiled.cuh"
 #include "mam_dense_tf32.cuh"
 #include "mam_fwd_generic.cuh"
 #include "mam_fwd_tiled.cuh"
@@ -100,6 +101,22 @@ int encode_rows_k(CUtensorMap* tm, const float* base, long long rows, long long 
     CUresult r = g_encode(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), gdim, gstr, box,
                           estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                           swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return cuda_fail(cudaErrorInvalidValue);
+    return MAM_OK;
+}
+
+// [outer][inner] fp32 matrix with a row pitch in bytes -> boxes of [box_outer][box_inner], no swizzle, zero fill.
+int encode_2d_plain(CUtensorMap* tm, const float* base, long long inner, long long outer, long long pitch_bytes,
+                    int box_inner, int box_outer) {
+    int st = get_encode();
+    if (st != MAM_OK) return st;
+    cuuint64_t gdim[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+    cuuint64_t gstr[1] = {(cuuint64_t)pitch_bytes};
+    cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = g_encode(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), gdim, gstr, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return cuda_fail(cudaErrorInvalidValue);
     return MAM_OK;
@@ -583,6 +600,122 @@ int mam_csr_fwd_f32(const float* a, const int64_t* crow, const int64_t* col, con
     if (fits(2) && M >= 2) return launch_csr<2>(a, crow, col, val, bias, y, argmax, argmin, M, K, N, cs);
     if (fits(1)) return launch_csr<1>(a, crow, col, val, bias, y, argmax, argmin, M, K, N, cs);
     return MAM_ERR_UNSUPPORTED;
+}
+
+namespace {
+struct CsrWs {
+    size_t at_off, counts_off, seg_off, k0_off, list_off, rlist_off, total;
+    long long pitch;  // floats per row of the transposed activations
+    int nks;
+};
+CsrWs csr_ws_layout(int64_t M, int64_t K, int64_t N, int64_t nnz) {
+    CsrWs w{};
+    w.nks = (int)((K + CT_KS - 1) / CT_KS);
+    w.pitch = (M + 3) & ~3LL;
+    const size_t segs = (size_t)w.nks * (size_t)N;
+    size_t off = 0;
+    w.at_off = off;     off += round256((size_t)K * (size_t)w.pitch * 4);
+    w.counts_off = off; off += round256(segs * 4);
+    w.seg_off = off;    off += round256((segs + 1) * 4);
+    w.k0_off = off;     off += round256((size_t)N * 4);
+    w.list_off = off;   off += round256(((size_t)nnz + segs) * sizeof(CsrEntry));
+    w.rlist_off = off;  off += round256(((size_t)nnz + segs) * sizeof(CsrColEntry));
+    w.total = off;
+    return w;
+}
+bool csr_tiled_applies(int64_t M, int64_t K, int64_t N, int64_t nnz) {
+    const long long nks = (K + CT_KS - 1) / CT_KS;
+    return M >= 32 && nks * N < (1LL << 30) && nnz + nks * N < (1LL << 30) && K < (1LL << 31) &&
+           (N + CT_BN - 1) / CT_BN < (1LL << 31) && (M + CT_BM - 1) / CT_BM <= 65535;
+}
+}  // namespace
+
+size_t mam_csr_fwd_workspace_bytes(int64_t M, int64_t K, int64_t N, int64_t nnz) {
+    if (M <= 0 || K <= 0 || N <= 0 || nnz < 0 || !csr_tiled_applies(M, K, N, nnz)) return 0;
+    return csr_ws_layout(M, K, N, nnz).total;
+}
+
+int mam_csr_fwd_ws_f32(const float* a, const int64_t* crow, const int64_t* col, const float* val, int64_t nnz,
+                       const float* bias, float* y, int32_t* argmax, int32_t* argmin, int64_t M, int64_t K,
+                       int64_t N, void* workspace, size_t workspace_bytes, void* stream) {
+    if (bad_ptr(a) || bad_ptr(crow) || bad_ptr(y) || M <= 0 || K <= 0 || N <= 0 || nnz < 0)
+        return MAM_ERR_INVALID_ARGUMENT;
+    if ((argmax == nullptr) != (argmin == nullptr)) return MAM_ERR_INVALID_ARGUMENT;
+    if (!csr_tiled_applies(M, K, N, nnz) || workspace == nullptr)
+        return mam_csr_fwd_f32(a, crow, col, val, bias, y, argmax, argmin, M, K, N, stream);
+    const CsrWs w = csr_ws_layout(M, K, N, nnz);
+    if (workspace_bytes < w.total || (reinterpret_cast<uintptr_t>(workspace) & 255u)) return MAM_ERR_WORKSPACE;
+    const DevInfo* d = nullptr;
+    int st = device_info(&d);
+    if (st != MAM_OK) return st;
+    if (CT_SMEM_BYTES > d->max_smem) return MAM_ERR_UNSUPPORTED;
+    cudaStream_t cs = (cudaStream_t)stream;
+    unsigned char* ws = static_cast<unsigned char*>(workspace);
+    float* at = reinterpret_cast<float*>(ws + w.at_off);
+    int* counts = reinterpret_cast<int*>(ws + w.counts_off);
+    int* seg = reinterpret_cast<int*>(ws + w.seg_off);
+    int* k0 = reinterpret_cast<int*>(ws + w.k0_off);
+    CsrEntry* list = reinterpret_cast<CsrEntry*>(ws + w.list_off);
+    CsrColEntry* rlist = reinterpret_cast<CsrColEntry*>(ws + w.rlist_off);
+    const long long segs = (long long)w.nks * N;
+
+    // activations transposed: aT[K][pitch]
+    {
+        const long long gx = (K + 31) / 32, gy = (M + 31) / 32;
+        if (gy > 65535) return MAM_ERR_UNSUPPORTED;
+        mam_transpose_pitch_kernel<<<dim3((unsigned)gx, (unsigned)gy), 256, 0, cs>>>(a, at, M, K, w.pitch);
+    }
+    // stored entries regrouped by stage
+    const unsigned seg_blocks = (unsigned)((segs + 255) / 256);
+    const long long* crow_ll = reinterpret_cast<const long long*>(crow);
+    const long long* col_ll = reinterpret_cast<const long long*>(col);
+    csr_tile_count_kernel<<<seg_blocks, 256, 0, cs>>>(crow_ll, col_ll, counts, k0, N, K, w.nks);
+    {
+        // counts -> seg (exclusive scan); the first words of the list area hold the per-block sums
+        // until the fill kernel overwrites them
+        int* block_sums = reinterpret_cast<int*>(list);
+        const long long nb = (segs + 1 + CSR_SCAN_BLOCK - 1) / CSR_SCAN_BLOCK;
+        csr_scan_block_sums_kernel<<<(unsigned)nb, 1024, 0, cs>>>(counts, block_sums, segs);
+        csr_scan_sums_kernel<<<1, 1024, 0, cs>>>(block_sums, nb);
+        csr_scan_apply_kernel<<<(unsigned)nb, 1024, 0, cs>>>(counts, block_sums, seg, segs);
+    }
+    csr_tile_fill_kernel<<<seg_blocks, 256, 0, cs>>>(crow_ll, col_ll, val, seg, list, rlist, N, w.nks);
+    MAM_CUDA(cudaGetLastError());
+
+    CUtensorMap tmAT;
+    st = encode_2d_plain(&tmAT, at, M, K, w.pitch * 4, CT_BM, CT_KS);
+    if (st != MAM_OK) return st;
+    int* flag = nullptr;
+    MAM_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&flag), g_wait_gave_up));
+    CsrTiledParams prm{seg, list, k0, bias, y, argmax, argmin, M, K, N, w.nks, 1.0f, flag};
+    const dim3 grid((unsigned)((N + CT_BN - 1) / CT_BN), (unsigned)((M + CT_BM - 1) / CT_BM));
+    if (argmax) {
+        MAM_CUDA(cudaFuncSetAttribute(mam_csr_tiled_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      CT_SMEM_BYTES));
+        mam_csr_tiled_kernel<true><<<grid, CT_THREADS, CT_SMEM_BYTES, cs>>>(tmAT, prm);
+    } else {
+        MAM_CUDA(cudaFuncSetAttribute(mam_csr_tiled_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      CT_SMEM_BYTES));
+        mam_csr_tiled_kernel<false><<<grid, CT_THREADS, CT_SMEM_BYTES, cs>>>(tmAT, prm);
+    }
+    MAM_CUDA(cudaGetLastError());
+    if (!argmax) return MAM_OK;
+    // recorded segments -> indices; rows parked per CTA so that three CTAs share an SM
+    auto launch_resolve = [&](auto kern, int R) -> int {
+        const size_t smem = (size_t)R * (size_t)K * 4;
+        MAM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        const long long g = (M + R - 1) / R;
+        if (g > 2147483647LL) return MAM_ERR_UNSUPPORTED;
+        kern<<<(unsigned)g, 512, smem, cs>>>(a, rlist, k0, argmax, argmin, M, K, N);
+        return MAM_OK;
+    };
+    const long long row_bytes = K * 4;
+    if (row_bytes > d->max_smem - 1024) return MAM_ERR_UNSUPPORTED;
+    if (2 * row_bytes <= 110 * 1024) st = launch_resolve(mam_csr_resolve_kernel<2>, 2);
+    else st = launch_resolve(mam_csr_resolve_kernel<1>, 1);
+    if (st != MAM_OK) return st;
+    MAM_CUDA(cudaGetLastError());
+    return MAM_OK;
 }
 
 int mam_spmm_csr_f32(const int64_t* crow, const int64_t* col, const float* val, const float* b, float* c, int64_t N,

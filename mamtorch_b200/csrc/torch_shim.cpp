@@ -302,10 +302,16 @@ std::vector<at::Tensor> csr_linear_forward(const at::Tensor& x, const at::Tensor
         const int64_t* col_p = col_c.numel() ? col_c.data_ptr<int64_t>() : crow_c.data_ptr<int64_t>();
         const float* val_p = val_c.numel() ? val_c.data_ptr<float>() : x.data_ptr<float>();
         auto stream = at::cuda::getCurrentCUDAStream();
-        check_status(mam_csr_fwd_f32(x.data_ptr<float>(), crow_c.data_ptr<int64_t>(), col_p, val_p, bias_p,
-                                     y.data_ptr<float>(), want_idx ? amax.data_ptr<int32_t>() : nullptr,
-                                     want_idx ? amin.data_ptr<int32_t>() : nullptr, M, K, N, stream.stream()),
-                     "mam_csr_fwd_f32");
+        // scratch for the tiled kernels (transposed activations + regrouped entries); 0 = not applicable
+        const int64_t nnz = val_c.numel();
+        const size_t wsb = mam_csr_fwd_workspace_bytes(M, K, N, nnz);
+        at::Tensor ws;
+        if (wsb) ws = at::empty({(int64_t)wsb}, x.options().dtype(at::kByte));
+        check_status(mam_csr_fwd_ws_f32(x.data_ptr<float>(), crow_c.data_ptr<int64_t>(), col_p, val_p, nnz, bias_p,
+                                        y.data_ptr<float>(), want_idx ? amax.data_ptr<int32_t>() : nullptr,
+                                        want_idx ? amin.data_ptr<int32_t>() : nullptr, M, K, N,
+                                        wsb ? ws.data_ptr() : nullptr, wsb, stream.stream()),
+                     "mam_csr_fwd_ws_f32");
     }
     if (!want_idx) return {y};
     return {y, amax, amin};

@@ -17,8 +17,13 @@ def _pruned(N, K, keep, seed):
     return w, mask, g
 
 
+# Shapes with fewer than 32 rows run the lane-per-entry kernel, the others the tiled kernels (rows of a
+# on the lanes): ragged last stage (K % 64 != 0), ragged row/column tiles, nothing stored, everything
+# stored (runs of 128 entry pairs per warp and stage, i.e. several staging batches), one stage only.
 @pytest.mark.parametrize("shape,keep", [((70, 96, 45), 0.1), ((33, 257, 64), 0.5), ((9, 40, 20), 0.0),
-                                        ((16, 64, 31), 1.0), ((300, 1024, 130), 0.1), ((5, 4096, 37), 0.02)])
+                                        ((16, 64, 31), 1.0), ((300, 1024, 130), 0.1), ((5, 4096, 37), 0.02),
+                                        ((64, 200, 70), 1.0), ((40, 130, 9), 0.0), ((129, 36, 65), 0.3),
+                                        ((32, 64, 4), 0.5), ((260, 708, 131), 0.05)])
 def test_csr_forward_equals_dense_on_zero_filled_weight(shape, keep, cuda):
     import mamtorch_b200 as mamtorch
 
@@ -37,6 +42,49 @@ def test_csr_forward_equals_dense_on_zero_filled_weight(shape, keep, cuda):
     assert torch.equal(y.cpu(), torch.from_numpy(y_ref))
     yv, _, _ = mamtorch.sparse.kernel.v1.mam_linear_csr(x.to(cuda), w_csr, need_indices=False)
     assert torch.equal(yv, y)
+
+
+@pytest.mark.parametrize("shape,keep", [((96, 512, 200), 0.1), ((45, 100, 33), 0.6), ((2048, 1024, 256), 0.1)])
+def test_tiled_and_lane_per_entry_kernels_agree(shape, keep, cuda):
+    """The two CSR forward entry points of the C ABI must give identical bits: with a workspace the
+    tiled kernels run, without one the lane-per-entry kernel."""
+    import ctypes
+
+    from mamtorch_b200 import _lib
+
+    L = _lib.lib()
+    M, K, N = shape
+    w, mask, g = _pruned(N, K, keep, 3 * M + K + N)
+    x = torch.randn(M, K, generator=g).to(cuda)
+    w_csr = (w * mask).to(cuda).to_sparse_csr()
+    crow, col, val = w_csr.crow_indices().contiguous(), w_csr.col_indices().contiguous(), w_csr.values().contiguous()
+    bias = torch.randn(N, generator=g).to(cuda)
+    nnz = val.numel()
+    p = lambda t: None if t is None else ctypes.c_void_p(t.data_ptr())
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    wsb = L.mam_csr_fwd_workspace_bytes(M, K, N, nnz)
+    assert wsb > 0
+    ws = torch.empty(wsb, dtype=torch.uint8, device=cuda)
+    out = []
+    for use_ws in (True, False):
+        y = torch.empty(M, N, device=cuda)
+        i1 = torch.empty(M, N, dtype=torch.int32, device=cuda)
+        i2 = torch.empty_like(i1)
+        _lib.check(L.mam_csr_fwd_ws_f32(p(x), p(crow), p(col), p(val), nnz, p(bias), p(y), p(i1), p(i2), M, K, N,
+                                        p(ws) if use_ws else None, wsb if use_ws else 0, st), "mam_csr_fwd_ws_f32")
+        yv = torch.empty(M, N, device=cuda)
+        _lib.check(L.mam_csr_fwd_ws_f32(p(x), p(crow), p(col), p(val), nnz, p(bias), p(yv), None, None, M, K, N,
+                                        p(ws) if use_ws else None, wsb if use_ws else 0, st), "mam_csr_fwd_ws_f32")
+        assert torch.equal(y, yv)
+        out.append((y, i1, i2))
+    assert L.mam_check_device_flag() == 0
+    for a, b in zip(*out):
+        assert torch.equal(a, b)
+    # a workspace that is too small or misaligned is refused, nothing is launched
+    assert L.mam_csr_fwd_ws_f32(p(x), p(crow), p(col), p(val), nnz, None, p(out[0][0]), None, None, M, K, N,
+                                p(ws), wsb - 1, st) == 3
+    assert L.mam_csr_fwd_ws_f32(p(x), p(crow), p(col), p(val), nnz, None, p(out[0][0]), None, None, M, K, N,
+                                ctypes.c_void_p(ws.data_ptr() + 8), wsb, st) == 3
 
 
 def test_csr_layer_backward_gives_dense_weight_gradient(cuda):
