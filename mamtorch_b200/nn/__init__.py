@@ -3,7 +3,8 @@ convolution modules the reference keeps only as text backups (`mamtorch/nn/backu
 from . import functional
 from . import v1
 from . import v4
+from . import vit
 from .conv import MAMConv1d, MAMConv2d
 from .v4.fullyconnected import FullyConnected
 
-__all__ = ["FullyConnected", "MAMConv1d", "MAMConv2d", "functional", "v1", "v4"]
+__all__ = ["FullyConnected", "MAMConv1d", "MAMConv2d", "functional", "v1", "v4", "vit"]
