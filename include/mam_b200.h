@@ -133,6 +133,29 @@ int mam_bwd_count_f32(const float* a, const float* b, int b_layout, const float*
                       float* da, float* db, int32_t* hit_max, int32_t* hit_min, float scale,
                       int64_t M, int64_t K, int64_t N, void* stream);
 
+/* The same with a choice of layout for da: MAM_DA_MK is da[m*K + k] (as above), MAM_DA_KM is the
+ * transpose da[k*M + m], which is what mam_col2im_f32 reads. */
+#define MAM_DA_MK 0
+#define MAM_DA_KM 1
+int mam_bwd_count_ex_f32(const float* a, const float* b, int b_layout, const float* grad,
+                         const int32_t* argmax, const int32_t* argmin,
+                         float* da, int da_layout, float* db, int32_t* hit_max, int32_t* hit_min, float scale,
+                         int64_t M, int64_t K, int64_t N, void* stream);
+
+/* Patch rows of a convolution input: rows[m][k] = x[b][c][ho*sh-ph+kh][wo*sw-pw+kw] (0 outside the image),
+ * m = (b*Ho+ho)*Wo+wo, k = (c*kH+kh)*kW+kw, Ho = (H+2*ph-kH)/sh+1, Wo likewise; x is [B,C,H,W], rows is
+ * [B*Ho*Wo, C*kH*kW].  Feeds mam_fwd_f32 (MAM_B_NK with weight.view(F, C*kH*kW)); one pass, no transposes.
+ * Stands in for the per-call permutes of the reference's (never compiled) convolution host code,
+ * mamtorch/kernel/backup/mamconv2d.txt:70-100, and the F.pad of mamtorch/nn/backup/mamconv2d.txt:133-139. */
+int mam_im2col_f32(const float* x, float* rows, int64_t B, int64_t C, int64_t H, int64_t W,
+                   int kH, int kW, int sh, int sw, int ph, int pw, void* stream);
+/* Input gradient of the convolution from the TRANSPOSED row gradients cols_t[K][M] that
+ * mam_bwd_count_ex_f32(..., MAM_DA_KM, ...) writes: dx[b][c][h][w] = sum of the (up to kH*kW) entries that
+ * patch element came from.  dx is overwritten; no atomics.  Counterpart of the input-gradient scatter in
+ * mamtorch/kernel/backup/mamconv2d_backward.txt:21-124. */
+int mam_col2im_f32(const float* cols_t, float* dx, int64_t B, int64_t C, int64_t H, int64_t W,
+                   int kH, int kW, int sh, int sw, int ph, int pw, void* stream);
+
 /* Selection hits: hit_max[n,k] += #rows m with argmax[m,n]==k, hit_min likewise ([N,K] int32,
  * accumulated into, so zero them first for per-call counts).  The device-side form of the
  * bookkeeping in FullyConnected.update_selection_count (mamtorch/nn/v4/fullyconnected.py:114-131). */

@@ -16,7 +16,9 @@ namespace mamb200 {
 constexpr int BWD_THREADS = 256;
 
 // B_NK: w is W[N,K] and dw has the same layout; otherwise b[K,N].
-template <bool B_NK>
+// DA_KM: da is written transposed, da[k*M + m] (what the convolution's fold kernel wants: unit stride
+// along the output pixels); a CTA's rows are consecutive, so every k still gets one whole sector.
+template <bool B_NK, bool DA_KM = false>
 __global__ void __launch_bounds__(BWD_THREADS)
 mam_bwd_kernel(const float* __restrict__ a, const float* __restrict__ w, const float* __restrict__ g,
                const int* __restrict__ argmax, const int* __restrict__ argmin,
@@ -49,7 +51,15 @@ mam_bwd_kernel(const float* __restrict__ a, const float* __restrict__ w, const f
         }
     }
     __syncthreads();
-    for (long long i = threadIdx.x; i < (long long)rows * K; i += BWD_THREADS) da[m0 * K + i] = da_s[i];
+    if constexpr (DA_KM) {
+        for (long long i = threadIdx.x; i < (long long)rows * K; i += BWD_THREADS) {
+            const long long k = i / rows;
+            const int r = (int)(i - k * rows);
+            da[k * M + m0 + r] = da_s[(long long)r * K + k];
+        }
+    } else {
+        for (long long i = threadIdx.x; i < (long long)rows * K; i += BWD_THREADS) da[m0 * K + i] = da_s[i];
+    }
 }
 
 // ---------------------------------------------------------------------------------------------

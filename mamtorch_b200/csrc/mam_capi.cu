@@ -7,6 +7,7 @@
 
 #include "../../include/mam_b200.h"
 #include "mam_bwd.cuh"
+#include "mam_conv.cuh"
 #include "mam_csr.cuh"
 #include "mam_csr_tiled.cuh"
 #include "mam_dense_tf32.cuh"
@@ -453,6 +454,14 @@ int mam_fwd_kn_static_f32(const float* a, const float* b, float* y, int32_t* arg
 int mam_bwd_count_f32(const float* a, const float* b, int b_layout, const float* grad, const int32_t* argmax,
                       const int32_t* argmin, float* da, float* db, int32_t* hit_max, int32_t* hit_min, float scale,
                       int64_t M, int64_t K, int64_t N, void* stream) {
+    return mam_bwd_count_ex_f32(a, b, b_layout, grad, argmax, argmin, da, MAM_DA_MK, db, hit_max, hit_min, scale, M, K,
+                                N, stream);
+}
+
+int mam_bwd_count_ex_f32(const float* a, const float* b, int b_layout, const float* grad, const int32_t* argmax,
+                         const int32_t* argmin, float* da, int da_layout, float* db, int32_t* hit_max,
+                         int32_t* hit_min, float scale, int64_t M, int64_t K, int64_t N, void* stream) {
+    if (da_layout != MAM_DA_MK && da_layout != MAM_DA_KM) return MAM_ERR_INVALID_ARGUMENT;
     if (bad_ptr(a) || bad_ptr(b) || bad_ptr(grad) || bad_ptr(argmax) || bad_ptr(argmin) || bad_ptr(da) ||
         bad_ptr(db) || M <= 0 || K <= 0 || N <= 0)
         return MAM_ERR_INVALID_ARGUMENT;
@@ -466,6 +475,9 @@ int mam_bwd_count_f32(const float* a, const float* b, int b_layout, const float*
     int rows = (int)((32 * 1024) / (K * 4));
     if (rows < 1) rows = 1;
     if (rows > 8) rows = 8;
+    // transposed da: every k receives `rows` consecutive floats from a CTA, so take more rows per CTA
+    // (16 = one 64-byte run) when their accumulators still leave room for several CTAs per SM
+    if (da_layout == MAM_DA_KM && 16 * K * 4 <= 48 * 1024) rows = 16;
     const bool count = hit_max != nullptr;
     // columns owned per CTA in the two-kernel form: at most 8, shared memory permitting, and enough
     // CTAs to cover the SMs twice
@@ -475,7 +487,7 @@ int mam_bwd_count_f32(const float* a, const float* b, int b_layout, const float*
     while (cols > 1 && (N + cols - 1) / cols < 2LL * d->sms) cols >>= 1;
     // Measured on B200 the single-kernel form is faster at every benchmarked shape (0.87 vs 1.32 ms at
     // 12608x768x3072): the column-owned sweep is latency-bound.  The two-kernel form stays selectable.
-    const bool split = g_bwd_mode == 2;
+    const bool split = g_bwd_mode == 2 && da_layout == MAM_DA_MK;
     if (split && cols >= 1) {
         if (b_layout == MAM_B_NK)
             return launch_bwd_split<true>(a, b, grad, argmax, argmin, da, db, hit_max, hit_min, scale, M, K, N, rows,
@@ -488,16 +500,16 @@ int mam_bwd_count_f32(const float* a, const float* b, int b_layout, const float*
     if (grid > 2147483647LL) return MAM_ERR_UNSUPPORTED;
     MAM_CUDA(cudaMemsetAsync(db, 0, (size_t)K * (size_t)N * 4, cs));
     {
-        TimedLaunch t(MAM_KERNEL_BWD, cs);
-        if (b_layout == MAM_B_NK) {
-            MAM_CUDA(cudaFuncSetAttribute(mam_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            mam_bwd_kernel<true><<<(unsigned)grid, BWD_THREADS, smem, cs>>>(a, b, grad, argmax, argmin, da, db, M, K, N,
-                                                                            rows, scale);
-        } else {
-            MAM_CUDA(cudaFuncSetAttribute(mam_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            mam_bwd_kernel<false><<<(unsigned)grid, BWD_THREADS, smem, cs>>>(a, b, grad, argmax, argmin, da, db, M, K,
-                                                                             N, rows, scale);
-        }
+        auto launch = [&](auto kern) -> int {
+            MAM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            TimedLaunch t(MAM_KERNEL_BWD, cs);
+            kern<<<(unsigned)grid, BWD_THREADS, smem, cs>>>(a, b, grad, argmax, argmin, da, db, M, K, N, rows, scale);
+            return MAM_OK;
+        };
+        const bool nk = b_layout == MAM_B_NK, km = da_layout == MAM_DA_KM;
+        st = nk ? (km ? launch(mam_bwd_kernel<true, true>) : launch(mam_bwd_kernel<true, false>))
+                : (km ? launch(mam_bwd_kernel<false, true>) : launch(mam_bwd_kernel<false, false>));
+        if (st != MAM_OK) return st;
     }
     MAM_CUDA(cudaGetLastError());
     if (count) return mam_selcount_i32(argmax, argmin, hit_max, hit_min, M, K, N, stream);
@@ -508,6 +520,56 @@ int mam_bwd_f32(const float* a, const float* b, int b_layout, const float* grad,
                 const int32_t* argmin, float* da, float* db, float scale, int64_t M, int64_t K, int64_t N,
                 void* stream) {
     return mam_bwd_count_f32(a, b, b_layout, grad, argmax, argmin, da, db, nullptr, nullptr, scale, M, K, N, stream);
+}
+
+namespace {
+int conv_geom(ConvGeom* g, int64_t B, int64_t C, int64_t H, int64_t W, int kH, int kW, int sh, int sw, int ph, int pw) {
+    if (B <= 0 || C <= 0 || H <= 0 || W <= 0 || kH <= 0 || kW <= 0 || sh <= 0 || sw <= 0 || ph < 0 || pw < 0)
+        return MAM_ERR_INVALID_ARGUMENT;
+    if (H + 2LL * ph < kH || W + 2LL * pw < kW) return MAM_ERR_INVALID_ARGUMENT;
+    const long long Ho = (H + 2LL * ph - kH) / sh + 1, Wo = (W + 2LL * pw - kW) / sw + 1;
+    if (B >= (1LL << 31) || C * (long long)kH * kW >= (1LL << 31) || H >= (1LL << 30) || W >= (1LL << 30))
+        return MAM_ERR_UNSUPPORTED;
+    *g = ConvGeom{(int)B, (int)C, (int)H, (int)W, kH, kW, sh, sw, ph, pw, (int)Ho, (int)Wo};
+    return MAM_OK;
+}
+}  // namespace
+
+int mam_im2col_f32(const float* x, float* rows, int64_t B, int64_t C, int64_t H, int64_t W, int kH, int kW, int sh,
+                   int sw, int ph, int pw, void* stream) {
+    if (bad_ptr(x) || bad_ptr(rows)) return MAM_ERR_INVALID_ARGUMENT;
+    ConvGeom g;
+    int st = conv_geom(&g, B, C, H, W, kH, kW, sh, sw, ph, pw);
+    if (st != MAM_OK) return st;
+    if ((long long)g.C * g.H * g.W >= (1LL << 31)) return MAM_ERR_UNSUPPORTED;   // per-image offsets are 32-bit
+    const long long blocks = (long long)g.B * g.Ho;
+    if (blocks > 2147483647LL) return MAM_ERR_UNSUPPORTED;
+    mam_im2col_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(x, rows, g);
+    MAM_CUDA(cudaGetLastError());
+    return MAM_OK;
+}
+
+int mam_col2im_f32(const float* cols_t, float* dx, int64_t B, int64_t C, int64_t H, int64_t W, int kH, int kW, int sh,
+                   int sw, int ph, int pw, void* stream) {
+    if (bad_ptr(cols_t) || bad_ptr(dx)) return MAM_ERR_INVALID_ARGUMENT;
+    ConvGeom g;
+    int st = conv_geom(&g, B, C, H, W, kH, kW, sh, sw, ph, pw);
+    if (st != MAM_OK) return st;
+    const long long M = (long long)g.B * g.Ho * g.Wo;
+    // input rows per CTA: whole planes when that still gives a few CTAs per SM, else split the height
+    const DevInfo* d = nullptr;
+    st = device_info(&d);
+    if (st != MAM_OK) return st;
+    int hrows = g.H;
+    while (hrows > 4 && (long long)g.B * g.C * ((g.H + hrows - 1) / hrows) < 4LL * d->sms) hrows = (hrows + 1) / 2;
+    const long long blocks = (long long)g.B * g.C * ((g.H + hrows - 1) / hrows);
+    if (blocks > 2147483647LL) return MAM_ERR_UNSUPPORTED;
+    if (g.sh == 1 && g.sw == 1)
+        mam_col2im_kernel<true><<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(cols_t, dx, g, M, hrows);
+    else
+        mam_col2im_kernel<false><<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(cols_t, dx, g, M, hrows);
+    MAM_CUDA(cudaGetLastError());
+    return MAM_OK;
 }
 
 int mam_selcount_i32(const int32_t* argmax, const int32_t* argmin, int32_t* hit_max, int32_t* hit_min, int64_t M,

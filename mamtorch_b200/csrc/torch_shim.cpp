@@ -95,7 +95,7 @@ Fwd forward_impl(const at::Tensor& a, const at::Tensor& w, int b_layout, const c
 
 std::vector<at::Tensor> backward_impl(const at::Tensor& a, const at::Tensor& w, int b_layout, const at::Tensor& grad,
                                       const at::Tensor& argmax, const at::Tensor& argmin, double scale,
-                                      bool count = false) {
+                                      bool count = false, bool da_km = false) {
     check_matrix(a, "a");
     check_matrix(w, "b");
     check_matrix(grad, "grad");
@@ -107,7 +107,7 @@ std::vector<at::Tensor> backward_impl(const at::Tensor& a, const at::Tensor& w, 
     TORCH_CHECK(grad.size(0) == M && grad.size(1) == N, "grad must be [M,N]");
     TORCH_CHECK(argmax.sizes() == grad.sizes() && argmin.sizes() == grad.sizes(), "index shapes must match grad");
     c10::cuda::CUDAGuard guard(a.device());
-    auto da = at::empty_like(a);
+    auto da = da_km ? at::empty({K, M}, a.options()) : at::empty_like(a);   // da_km: gradient of a, transposed
     auto dw = at::empty_like(w);
     at::Tensor hmax, hmin;
     if (count) {
@@ -119,12 +119,13 @@ std::vector<at::Tensor> backward_impl(const at::Tensor& a, const at::Tensor& w, 
         dw.zero_();
     } else {
         auto stream = at::cuda::getCurrentCUDAStream();
-        const int st = mam_bwd_count_f32(a.data_ptr<float>(), w.data_ptr<float>(), b_layout, grad.data_ptr<float>(),
-                                         argmax.data_ptr<int32_t>(), argmin.data_ptr<int32_t>(), da.data_ptr<float>(),
-                                         dw.data_ptr<float>(), count ? hmax.data_ptr<int32_t>() : nullptr,
-                                         count ? hmin.data_ptr<int32_t>() : nullptr, (float)scale, M, K, N,
-                                         stream.stream());
-        check_status(st, "mam_bwd_count_f32");
+        const int st = mam_bwd_count_ex_f32(a.data_ptr<float>(), w.data_ptr<float>(), b_layout, grad.data_ptr<float>(),
+                                            argmax.data_ptr<int32_t>(), argmin.data_ptr<int32_t>(), da.data_ptr<float>(),
+                                            da_km ? MAM_DA_KM : MAM_DA_MK, dw.data_ptr<float>(),
+                                            count ? hmax.data_ptr<int32_t>() : nullptr,
+                                            count ? hmin.data_ptr<int32_t>() : nullptr, (float)scale, M, K, N,
+                                            stream.stream());
+        check_status(st, "mam_bwd_count_ex_f32");
     }
     if (count) return {da, dw, hmax, hmin};
     return {da, dw};
@@ -241,6 +242,44 @@ std::vector<at::Tensor> linear_backward_count(const at::Tensor& x, const at::Ten
                                               const at::Tensor& argmax, const at::Tensor& argmin, double scale) {
     return backward_impl(x, weight, MAM_B_NK, grad, argmax, argmin, scale, true);
 }
+// ------------------------------------------------------------------ convolution as patch rows
+// rows[B*Ho*Wo, C*kH*kW] of x[B,C,H,W]
+at::Tensor conv_im2col(const at::Tensor& x, int64_t kH, int64_t kW, int64_t sh, int64_t sw, int64_t ph, int64_t pw) {
+    TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kFloat && x.dim() == 4, "x must be a float32 CUDA [B,C,H,W] tensor");
+    auto xc = x.contiguous();
+    const int64_t B = xc.size(0), C = xc.size(1), H = xc.size(2), W = xc.size(3);
+    TORCH_CHECK(H + 2 * ph >= kH && W + 2 * pw >= kW, "kernel larger than the padded input");
+    const int64_t Ho = (H + 2 * ph - kH) / sh + 1, Wo = (W + 2 * pw - kW) / sw + 1;
+    c10::cuda::CUDAGuard guard(x.device());
+    auto rows = at::empty({B * Ho * Wo, C * kH * kW}, xc.options());
+    if (rows.numel() == 0) return rows;
+    auto stream = at::cuda::getCurrentCUDAStream();
+    check_status(mam_im2col_f32(xc.data_ptr<float>(), rows.data_ptr<float>(), B, C, H, W, (int)kH, (int)kW, (int)sh,
+                                (int)sw, (int)ph, (int)pw, stream.stream()),
+                 "mam_im2col_f32");
+    return rows;
+}
+// dx[B,C,H,W] from the transposed row gradients cols_t[C*kH*kW, B*Ho*Wo]
+at::Tensor conv_col2im(const at::Tensor& cols_t, int64_t B, int64_t C, int64_t H, int64_t W, int64_t kH, int64_t kW,
+                       int64_t sh, int64_t sw, int64_t ph, int64_t pw) {
+    check_matrix(cols_t, "cols_t");
+    const int64_t Ho = (H + 2 * ph - kH) / sh + 1, Wo = (W + 2 * pw - kW) / sw + 1;
+    TORCH_CHECK(cols_t.size(0) == C * kH * kW && cols_t.size(1) == B * Ho * Wo, "cols_t must be [C*kH*kW, B*Ho*Wo]");
+    c10::cuda::CUDAGuard guard(cols_t.device());
+    auto dx = at::empty({B, C, H, W}, cols_t.options());
+    if (dx.numel() == 0) return dx;
+    auto stream = at::cuda::getCurrentCUDAStream();
+    check_status(mam_col2im_f32(cols_t.data_ptr<float>(), dx.data_ptr<float>(), B, C, H, W, (int)kH, (int)kW, (int)sh,
+                                (int)sw, (int)ph, (int)pw, stream.stream()),
+                 "mam_col2im_f32");
+    return dx;
+}
+// {dx transposed [K,M], dw}: the backward of linear_forward with the row gradients laid out for conv_col2im
+std::vector<at::Tensor> linear_backward_km(const at::Tensor& x, const at::Tensor& weight, const at::Tensor& grad,
+                                           const at::Tensor& argmax, const at::Tensor& argmin, double scale) {
+    return backward_impl(x, weight, MAM_B_NK, grad, argmax, argmin, scale, false, true);
+}
+
 // hits[0] = hit_max[N,K], hits[1] = hit_min[N,K]: how many rows selected each weight
 std::vector<at::Tensor> selection_hits(const at::Tensor& argmax, const at::Tensor& argmin, int64_t K) {
     check_matrix(argmax, "argmax", at::kInt);
@@ -390,6 +429,9 @@ TORCH_LIBRARY(mamtorch_b200, m) {
     m.def("linear_forward(Tensor x, Tensor weight, Tensor? bias, Tensor? dense, float alpha, float beta, bool want_idx) -> Tensor[]");
     m.def("linear_backward(Tensor x, Tensor weight, Tensor grad, Tensor argmax, Tensor argmin, float scale) -> Tensor[]");
     m.def("linear_backward_count(Tensor x, Tensor weight, Tensor grad, Tensor argmax, Tensor argmin, float scale) -> Tensor[]");
+    m.def("linear_backward_km(Tensor x, Tensor weight, Tensor grad, Tensor argmax, Tensor argmin, float scale) -> Tensor[]");
+    m.def("conv_im2col(Tensor x, int kH, int kW, int sh, int sw, int ph, int pw) -> Tensor");
+    m.def("conv_col2im(Tensor cols_t, int B, int C, int H, int W, int kH, int kW, int sh, int sw, int ph, int pw) -> Tensor");
     m.def("selection_hits(Tensor argmax, Tensor argmin, int K) -> Tensor[]");
     m.def("selection_count_update_(Tensor(a!) count, Tensor hit_max, Tensor hit_min) -> Tensor(a!)");
     m.def("dense_nt(Tensor a, Tensor w) -> Tensor");
@@ -401,6 +443,9 @@ TORCH_LIBRARY_IMPL(mamtorch_b200, CUDA, m) {
     m.impl("linear_forward", &linear_forward);
     m.impl("linear_backward", &linear_backward);
     m.impl("linear_backward_count", &linear_backward_count);
+    m.impl("linear_backward_km", &linear_backward_km);
+    m.impl("conv_im2col", &conv_im2col);
+    m.impl("conv_col2im", &conv_col2im);
     m.impl("selection_hits", &selection_hits);
     m.impl("selection_count_update_", &selection_count_update_);
     m.impl("csr_linear_forward", &csr_linear_forward);

@@ -1,4 +1,4 @@
-"""MAM convolutions as im2col + the fully-connected kernels.
+"""MAM convolutions as patch rows (im2col) + the fully-connected kernels.
 
 The reference carries convolution only as never-compiled text backups
 (`mamtorch/nn/backup/mamconv2d.txt:20-177`, `mamconv1d.txt`, kernels in
@@ -22,6 +22,8 @@ import torch.nn.functional as F
 
 from . import functional as MF
 
+_ops = torch.ops.mamtorch_b200
+
 __all__ = ["MAMConv1d", "MAMConv2d", "mam_conv2d"]
 
 
@@ -29,22 +31,66 @@ def _pair(v):
     return tuple(v) if isinstance(v, (tuple, list)) else (v, v)
 
 
+class _MamConv2d(torch.autograd.Function):
+    """MAM convolution on patch rows: one im2col pass, the fully-connected kernels, and for the input
+    gradient the backward's transposed row gradients folded by a gather kernel (no atomics).  The
+    patch rows are kept for the backward (it reads the two selected activations per output)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, dense, alpha, beta, stride, padding):
+        B, C, H, W = x.shape
+        Fo, _, kH, kW = weight.shape
+        (sh, sw), (ph, pw) = stride, padding
+        Ho, Wo = (H + 2 * ph - kH) // sh + 1, (W + 2 * pw - kW) // sw + 1
+        rows = _ops.conv_im2col(x, kH, kW, sh, sw, ph, pw)                    # [B*Ho*Wo, C*kH*kW]
+        w2d = weight.reshape(Fo, -1).contiguous()
+        dflat = None
+        if dense is not None:
+            dflat = dense.permute(0, 2, 3, 1).reshape(B * Ho * Wo, Fo).contiguous()
+        y, amax, amin = _ops.linear_forward(rows, w2d, bias, dflat, alpha, beta, True)
+        ctx.save_for_backward(rows, w2d, amax, amin)
+        ctx.geom = (B, C, H, W, Fo, kH, kW, sh, sw, ph, pw, Ho, Wo)
+        ctx.alpha, ctx.beta = alpha, beta
+        ctx.has_bias, ctx.has_dense = bias is not None, dense is not None
+        img = lambda t: t.view(B, Ho, Wo, Fo).permute(0, 3, 1, 2)
+        amax, amin = img(amax), img(amin)
+        ctx.mark_non_differentiable(amax, amin)
+        return img(y), amax, amin
+
+    @staticmethod
+    def backward(ctx, gy, _g1, _g2):
+        rows, w2d, amax, amin = ctx.saved_tensors
+        B, C, H, W, Fo, kH, kW, sh, sw, ph, pw, Ho, Wo = ctx.geom
+        g2d = gy.permute(0, 2, 3, 1).reshape(B * Ho * Wo, Fo).contiguous()
+        dx = dw = dbias = ddense = None
+        if ctx.needs_input_grad[0] or ctx.needs_input_grad[1]:
+            cols_t, dw2d = _ops.linear_backward_km(rows, w2d, g2d, amax, amin, ctx.alpha)
+            if ctx.needs_input_grad[0]:
+                dx = _ops.conv_col2im(cols_t, B, C, H, W, kH, kW, sh, sw, ph, pw)
+            dw = dw2d.view(Fo, C, kH, kW)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            dbias = g2d.sum(0)
+        if ctx.has_dense and ctx.needs_input_grad[3]:
+            ddense = gy * ctx.beta
+        return dx, dw, dbias, ddense, None, None, None, None
+
+
 def mam_conv2d(x, weight, bias=None, stride=1, padding=0, dense=None, alpha=1.0, beta=0.0, need_indices=True):
     """x[B,C,H,W], weight[F,C,kH,kW] -> (y[B,F,Ho,Wo], argmax, argmin) with indices into C*kH*kW."""
+    stride, padding = _pair(stride), _pair(padding)
+    wants_grad = torch.is_grad_enabled() and any(
+        t is not None and t.requires_grad for t in (x, weight, bias, dense))
+    if need_indices or wants_grad:
+        y, amax, amin = _MamConv2d.apply(x, weight, bias, dense, float(alpha), float(beta), stride, padding)
+        return (y, amax, amin) if need_indices else (y, None, None)
     B, C, H, W = x.shape
     Fo, _, kH, kW = weight.shape
-    sh, sw = _pair(stride)
-    ph, pw = _pair(padding)
-    Ho = (H + 2 * ph - kH) // sh + 1
-    Wo = (W + 2 * pw - kW) // sw + 1
-    cols = F.unfold(x, (kH, kW), padding=(ph, pw), stride=(sh, sw))          # [B, K, L]
-    rows = cols.transpose(1, 2).reshape(B * Ho * Wo, C * kH * kW)            # one row per pixel
-    dflat = None
-    if dense is not None:
-        dflat = dense.permute(0, 2, 3, 1).reshape(B * Ho * Wo, Fo)
-    y, amax, amin = MF.mam_linear(rows, weight.reshape(Fo, -1), bias, dflat, alpha, beta, need_indices)
-    img = lambda t: None if t is None else t.view(B, Ho, Wo, Fo).permute(0, 3, 1, 2)
-    return img(y), img(amax), img(amin)
+    (sh, sw), (ph, pw) = stride, padding
+    Ho, Wo = (H + 2 * ph - kH) // sh + 1, (W + 2 * pw - kW) // sw + 1
+    rows = _ops.conv_im2col(x, kH, kW, sh, sw, ph, pw)
+    dflat = None if dense is None else dense.permute(0, 2, 3, 1).reshape(B * Ho * Wo, Fo).contiguous()
+    y, = _ops.linear_forward(rows, weight.reshape(Fo, -1).contiguous(), bias, dflat, float(alpha), float(beta), False)
+    return y.view(B, Ho, Wo, Fo).permute(0, 3, 1, 2), None, None
 
 
 def to_legacy_index(idx, in_channels, kH, kW):

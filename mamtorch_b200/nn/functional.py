@@ -28,6 +28,23 @@ def _(x, weight, grad, argmax, argmin, scale):
     return [torch.empty_like(x), torch.empty_like(weight)]
 
 
+@torch.library.register_fake("mamtorch_b200::linear_backward_km")
+def _(x, weight, grad, argmax, argmin, scale):
+    return [x.new_empty((x.size(1), x.size(0))), torch.empty_like(weight)]
+
+
+@torch.library.register_fake("mamtorch_b200::conv_im2col")
+def _(x, kH, kW, sh, sw, ph, pw):
+    B, C, H, W = x.shape
+    Ho, Wo = (H + 2 * ph - kH) // sh + 1, (W + 2 * pw - kW) // sw + 1
+    return x.new_empty((B * Ho * Wo, C * kH * kW))
+
+
+@torch.library.register_fake("mamtorch_b200::conv_col2im")
+def _(cols_t, B, C, H, W, kH, kW, sh, sw, ph, pw):
+    return cols_t.new_empty((B, C, H, W))
+
+
 @torch.library.register_fake("mamtorch_b200::linear_backward_count")
 def _(x, weight, grad, argmax, argmin, scale):
     shape = (weight.size(0), weight.size(1))

@@ -137,7 +137,9 @@ def mam_conv2d_forward(x, w, bias=None, stride=1, padding=0):
     rows = conv2d_as_rows(x.cpu(), (kH, kW), stride=stride, padding=padding)
     y, imax, imin = mam_forward(rows, w.reshape(F_, -1).T.contiguous().cpu(),
                                 bias=0.0 if bias is None else bias.cpu())
-    Ho = (H + 2 * padding - kH) // stride + 1
-    Wo = (W + 2 * padding - kW) // stride + 1
+    pair = lambda v: tuple(v) if isinstance(v, (tuple, list)) else (v, v)
+    (sh, sw), (ph, pw) = pair(stride), pair(padding)
+    Ho = (H + 2 * ph - kH) // sh + 1
+    Wo = (W + 2 * pw - kW) // sw + 1
     to_img = lambda t: t.reshape(B, Ho, Wo, F_).permute(0, 3, 1, 2).contiguous()
     return to_img(y), to_img(imax), to_img(imin)

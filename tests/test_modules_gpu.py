@@ -225,6 +225,40 @@ def test_beta_blended_training_step(cuda):
     assert_grad_close(db.cpu().numpy(), db_ref.numpy(), rtol=1e-3)
 
 
+def test_beta_blended_configuration_full_size(cuda):
+    """The blended-training configuration at its full size (M=N=K=4096, beta=0.5, x and W with
+    variance K^-0.5).  Too large for the CPU oracle, so check what holds at any size: the MAM term of a
+    beta=0 call equals the sum of the two products its indices point at, bit for bit; the beta=0.5 call
+    returns the same indices; and its output is within 1e-3 relative of 0.5*MAM + 0.5*(x.W^T) with the
+    product taken in full fp32."""
+    import mamtorch_b200 as mamtorch
+
+    M = N = K = 4096
+    beta = 0.5
+    g = torch.Generator().manual_seed(0)
+    std = K ** -0.25
+    x = (torch.randn(M, K, generator=g) * std).to(cuda)
+    w = (torch.randn(N, K, generator=g) * std).to(cuda)
+    b = w.T.contiguous()
+    zero_bias = torch.zeros(N, device=cuda)
+    c0, imax0, imin0 = mamtorch.kernel.v3.fullyconnected(x, b, zero_bias, 0.0)
+    c, imax, imin = mamtorch.kernel.v3.fullyconnected(x, b, zero_bias, beta)
+    assert torch.equal(imax, imax0) and torch.equal(imin, imin0)
+    assert int(imax.min()) >= 0 and int(imax.max()) < K and int(imin.min()) >= 0 and int(imin.max()) < K
+    cols = torch.arange(N, device=cuda)[None, :].expand(M, N)
+    want = x.gather(1, imax.long()) * w[cols, imax.long()] + x.gather(1, imin.long()) * w[cols, imin.long()]
+    assert torch.equal(c0, want)
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        dense = x @ b
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+    ref = beta * dense.double() + (1 - beta) * c0.double()
+    err = (c.double() - ref).abs().max().item()
+    assert err <= 1e-3 * ref.abs().max().item()
+
+
 def test_conv_benchmark_shape_properties(cuda):
     """The convolution configuration at full size (input [128,64,56,56], 3x3, 64->128 channels,
     stride 1, pad 1: GEMM M=401408, K=576, N=128).  Too large for the CPU oracle, so check what holds
