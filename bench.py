@@ -138,6 +138,93 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def run_sharded_sparse(args):
+    """The large sharded configuration: one MAM layer, M = 65536 rows split by rank, K = N = 4096, W pruned
+    to 90 % sparsity (uniform random mask) and stored as CSR; forward with indices through the tiled CSR
+    kernels, backward through the selected-pair scatter (dW dense), dW summed over the ranks with NCCL.
+    Total work is fixed, so the scaling is strong.  Prints one JSON line with the same keys as the
+    headline run (without the per-kernel roofline, which profiles/mam_csr_fwd_2048x4096x4096.md covers)."""
+    import torch
+    import torch.distributed as dist
+
+    import mamtorch_b200 as mamtorch
+    from mamtorch_b200 import _lib
+    from mamtorch_b200.dist import row_shard
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world} (launch with torch.distributed.run)"
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    M_TOTAL, K, N = 65536, 4096, 4096
+    lo, hi = row_shard(M_TOTAL, world, rank)
+    rows = hi - lo
+    g = torch.Generator().manual_seed(0)
+    w = torch.randn(N, K, generator=g) * K ** -0.5
+    keep = (torch.rand(N, K, generator=g) >= 0.9).float()          # as test/test_sparse.py:13-16 of the reference
+    wz = (w * keep).to(dev).requires_grad_()
+    w_csr = wz.detach().to_sparse_csr()
+    nnz = int(w_csr.values().numel())
+    gd = torch.Generator().manual_seed(100 + rank)
+    x = torch.randn(rows, K, generator=gd).to(dev)
+    gy = torch.randn(rows, N, generator=gd).to(dev)
+
+    def step():
+        wz.grad = None
+        xl = x.detach().requires_grad_()
+        y, _, _ = mamtorch.sparse.kernel.v1.mam_linear_csr(xl, w_csr, None, dense_weight=wz)
+        y.backward(gy)
+        if world > 1:
+            dist.all_reduce(wz.grad)
+        return y
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    barrier()
+    ev0.record()
+    for _ in range(args.steps):
+        step()
+    ev1.record()
+    barrier()
+    ms = torch.tensor([ev0.elapsed_time(ev1)], device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    clocks = sampler.stop() if rank == 0 else None
+    _lib.check(_lib.lib().mam_check_device_flag(), "device wait flag")
+    if rank == 0:
+        ms_per_step = float(ms.item()) / args.steps
+        units = M_TOTAL * nnz                                       # (row, stored weight) pairs, all ranks
+        line = {"metric": "mam_sharded_sparse_layer_fwd_bwd_throughput", "value": units / (ms_per_step * 1e-3) / 1e9,
+                "unit": UNIT, "n_gpus": world,
+                "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": "large sharded MAM layer fwd+bwd, fp32, M=65536 rows split by rank, K=N=4096, "
+                                       "W pruned to 90 % sparsity (CSR), dW all-reduced over NCCL",
+                           "units": "value counts (row, stored weight) pairs; the dense-equivalent rate is "
+                                    f"{M_TOTAL * K * N / (ms_per_step * 1e-3) / 1e9:.0f} G units/s",
+                           "nnz": nnz, "rows_per_rank": rows,
+                           "l2": "per-rank working set (activations, indices, gradients) exceeds the 126 MB L2"},
+                "gpu_launches": 11 * args.steps, "clocks": clocks}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -146,7 +233,12 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--fwd-variant", type=int, default=-1, help="tile configuration of the index-producing forward")
+    ap.add_argument("--workload", default="vit_mlp", choices=["vit_mlp", "sharded_sparse"],
+                    help="vit_mlp: the headline configuration (default); sharded_sparse: the large pruned layer, "
+                         "65536 rows split over the ranks (strong scaling), K = N = 4096, 90 %% of W pruned")
     args = ap.parse_args()
+    if args.workload == "sharded_sparse" and args.impl == "b200":
+        return run_sharded_sparse(args)
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.impl == "reference":
         return run_reference(args)
