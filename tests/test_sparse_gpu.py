@@ -139,3 +139,44 @@ def test_sharded_pruned_layer_shape_equals_dense_kernels(cuda):
     y, imax, imin = mamtorch.sparse.kernel.v1.mam_linear_csr(x, wz.to_sparse_csr())
     yd, imaxd, imind = torch.ops.mamtorch_b200.linear_forward(x, wz, None, None, 1.0, 0.0, True)
     assert torch.equal(y, yd) and torch.equal(imax, imaxd) and torch.equal(imin, imind)
+
+
+def test_magnitude_pruned_layer_equals_dense_layer_on_zeroed_weight(cuda):
+    """Layer-wise magnitude pruning as the reference does it (zero where |w| <= quantile(|w|, p),
+    examples/vitb16_imagenet1k/pruning_utils.py:105-116), then the CSR layer against the dense MAM layer
+    holding the zeroed weight: identical bits forward, gradients to rounding."""
+    import mamtorch_b200 as mamtorch
+
+    torch.manual_seed(21)
+    dense = mamtorch.nn.FullyConnected(96, 70, store_args=True).to(cuda)
+    p = 0.8
+    pruned = mamtorch.sparse.PrunedFullyConnected.from_dense(dense, fraction=p)
+    with torch.no_grad():   # what the reference's LMP does to the dense layer
+        thr = torch.quantile(dense.weight.flatten().abs(), p)
+        dense.weight[dense.weight.abs() <= thr] = 0
+    assert abs(pruned.sparsity() - p) < 0.01
+    assert torch.equal(pruned.weight.detach() * pruned.keep_mask, dense.weight.detach())
+    g = torch.Generator().manual_seed(22)
+    x = torch.relu(torch.randn(3, 41, 96, generator=g)).to(cuda)
+    gy = torch.randn(3, 41, 70, generator=g).to(cuda)
+    xa, xb = x.clone().requires_grad_(), x.clone().requires_grad_()
+    ya, yb = pruned(xa), dense(xb)
+    assert torch.equal(ya, yb)
+    assert torch.equal(pruned.argmax, dense.argmax) and torch.equal(pruned.argmin, dense.argmin)
+    ya.backward(gy)
+    yb.backward(gy)
+    assert_grad_close(xa.grad.cpu().numpy(), xb.grad.cpu().numpy())
+    # the dense layer's gradient reaches pruned positions too; the pruned layer's is masked by the chain rule
+    assert_grad_close(pruned.weight.grad.cpu().numpy(), (dense.weight.grad * pruned.keep_mask).cpu().numpy())
+    assert_grad_close(pruned.bias.grad.cpu().numpy(), dense.bias.grad.cpu().numpy())
+    # the CSR form is cached until the weight changes
+    csr = pruned._weight_csr()
+    assert pruned._weight_csr() is csr
+    with torch.no_grad():
+        pruned.weight.mul_(2.0)
+    assert pruned._weight_csr() is not csr
+    # one threshold for several layers (global magnitude pruning)
+    other = torch.randn(50, 96, generator=g).to(cuda)
+    thr_g = mamtorch.sparse.global_magnitude_threshold([pruned.weight, other], 0.5)
+    both = torch.cat([pruned.weight.detach().abs().flatten(), other.abs().flatten()])
+    assert torch.equal(thr_g, torch.quantile(both, 0.5))
