@@ -1,0 +1,106 @@
+"""Host-side logic that needs no device: the ViT layer-swap helpers, the pruning thresholds and masks,
+the module's vanishing-contribution schedule, and argument checks of the newer C-ABI entry points."""
+import ctypes
+import math
+
+import pytest
+import torch
+from torch import nn
+
+from mamtorch_b200 import _lib
+from mamtorch_b200.nn import FullyConnected
+from mamtorch_b200.nn import vit as mv
+from mamtorch_b200.sparse import (PrunedFullyConnected, global_magnitude_threshold, magnitude_keep_mask,
+                                  magnitude_threshold)
+
+
+def test_mlp_dense_paths_follow_the_reference_naming():
+    assert mv.mlp_dense_paths(2) == ["vit.encoder.layer.0.intermediate.dense", "vit.encoder.layer.1.intermediate.dense",
+                                     "vit.encoder.layer.0.output.dense", "vit.encoder.layer.1.output.dense"]
+    assert mv.mlp_dense_paths(-1, output=False) == ["vit.encoder.layer.11.intermediate.dense"]
+    assert mv.mlp_dense_paths(1, intermediate=False, prefix="enc") == ["enc.0.output.dense"]
+
+
+class _Tiny(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.block = nn.ModuleDict({"fc1": nn.Linear(6, 10), "act": nn.ReLU(), "fc2": nn.Linear(10, 4, bias=False)})
+        self.norm = nn.LayerNorm(4)
+
+
+def test_swap_takes_over_weights_and_schedule_steps_every_layer():
+    torch.manual_seed(0)
+    m = _Tiny()
+    w1, b1, w2 = m.block["fc1"].weight.data, m.block["fc1"].bias.data, m.block["fc2"].weight.data
+    mv.swap_linear_for_mam(m, ["block.fc1", "block.fc2"], vcon_steps=4, vcon_type="linear")
+    l1, l2 = m.block["fc1"], m.block["fc2"]
+    assert isinstance(l1, FullyConnected) and isinstance(l2, FullyConnected)
+    assert l1.weight.data_ptr() == w1.data_ptr() and l1.bias.data_ptr() == b1.data_ptr()
+    assert l2.weight.data_ptr() == w2.data_ptr() and l2.bias is None
+    assert mv.mam_layers(m) == [l1, l2]
+    assert (l1.beta, l1.alpha) == (1.0, 0.0)
+    for expect in (0.75, 0.5, 0.25, 0.0):
+        mv.vcon_step_all(m)
+        assert l1.beta == pytest.approx(expect) and l2.beta == pytest.approx(expect)
+        assert l1.alpha == pytest.approx(1.0 - expect)
+    mv.vcon_step_all(m)   # stays at zero
+    assert l1.beta == 0 and l1.alpha == 1.0
+    with pytest.raises(TypeError):
+        mv.swap_linear_for_mam(m, ["norm"])
+
+
+def test_exponential_schedule_reaches_eps_after_its_steps():
+    layer = FullyConnected(4, 3, vcon_steps=10, vcon_type="exponential", vcon_eps=1e-3)
+    for _ in range(9):
+        layer.vcon_step()
+    assert layer.beta == pytest.approx(math.exp(math.log(1e-3) * 0.9))
+    layer.vcon_step()
+    assert layer.beta == 0 and layer.alpha == 1.0
+
+
+def test_magnitude_thresholds_and_masks_match_the_reference_rule():
+    g = torch.Generator().manual_seed(1)
+    w = torch.randn(40, 30, generator=g)
+    for p in (0.0, 0.3, 0.9, 1.0):
+        thr = magnitude_threshold(w, p)
+        assert torch.equal(thr, torch.quantile(w.flatten().abs(), p))
+        keep = magnitude_keep_mask(w, thr)
+        zeroed = w.clone()
+        zeroed[zeroed.abs() <= thr] = 0          # examples/vitb16_imagenet1k/pruning_utils.py:105-107
+        assert torch.equal(w * keep, zeroed)
+    w2 = torch.randn(10, 30, generator=g) * 3
+    thr_g = global_magnitude_threshold([w, w2], 0.5)
+    assert torch.equal(thr_g, torch.quantile(torch.cat([w.flatten().abs(), w2.flatten().abs()]), 0.5))
+    with pytest.raises(ValueError):
+        magnitude_threshold(w, 1.5)
+
+
+def test_pruned_layer_bookkeeping_on_cpu():
+    torch.manual_seed(2)
+    lin = nn.Linear(20, 12)
+    layer = PrunedFullyConnected.from_dense(lin, fraction=0.75)
+    assert torch.equal(layer.weight.detach(), lin.weight.detach()) and torch.equal(layer.bias.detach(), lin.bias.detach())
+    assert abs(layer.sparsity() - 0.75) <= 1.0 / lin.weight.numel() + 1e-6
+    csr = layer._weight_csr()
+    assert csr.layout == torch.sparse_csr and csr.values().numel() == int(layer.keep_mask.sum())
+    assert layer._weight_csr() is csr
+    layer.prune_(threshold=float("inf"))
+    assert layer.sparsity() == 1.0 and layer._weight_csr().values().numel() == 0
+    with pytest.raises(ValueError):
+        layer.prune_()
+
+
+def test_newer_entry_points_reject_bad_arguments_without_a_device():
+    L = _lib.lib()
+    null = None
+    one = ctypes.c_void_p(16)   # never dereferenced: every call below fails its argument check first
+    assert L.mam_csr_fwd_workspace_bytes(0, 64, 64, 10) == 0
+    assert L.mam_csr_fwd_workspace_bytes(16, 64, 64, 10) == 0            # fewer than 32 rows: lane-per-entry kernel
+    need = L.mam_csr_fwd_workspace_bytes(4096, 4096, 4096, 1 << 20)
+    assert need >= 4096 * 4096 * 4 + (1 << 20) * 16 and need % 256 == 0
+    assert L.mam_csr_fwd_ws_f32(null, one, one, one, 0, null, one, null, null, 64, 64, 64, null, 0, null) == 1
+    assert L.mam_csr_fwd_ws_f32(one, one, one, one, 0, null, one, one, null, 64, 64, 64, null, 0, null) == 1
+    assert L.mam_im2col_f32(one, one, 1, 1, 4, 4, 5, 5, 1, 1, 0, 0, null) == 1                 # kernel larger than input
+    assert L.mam_im2col_f32(one, null, 1, 1, 4, 4, 3, 3, 1, 1, 0, 0, null) == 1
+    assert L.mam_col2im_f32(one, one, 1, 1, 4, 4, 3, 3, 0, 1, 0, 0, null) == 1                 # zero stride
+    assert L.mam_bwd_count_ex_f32(one, one, 1, one, one, one, one, 7, one, null, null, 1.0, 4, 4, 4, null) == 1
