@@ -41,6 +41,19 @@ WORKLOAD = ("ViT-B/16 MAM MLP pair fwd+bwd, fp32, M=12608 tokens per rank, 768->
             "arg-indices, selected-pair backward, selection count on")
 
 
+M_TOTAL_OUTPUTS = M_TOKENS * (D_FF + D_MODEL)   # outputs of both layers per rank
+
+
+def measured_hbm_gbs() -> float:
+    """Copy bandwidth measured on this pool's B200s (MEASURED_PEAKS.json beside this file), else the
+    6650 GB/s of an earlier measurement."""
+    try:
+        with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"])
+    except (OSError, KeyError, ValueError):
+        return 6650.0
+
+
 def fp32_peaks(sms: int, mhz: float):
     lanes = sms * 128 * mhz * 1e6
     # mix_ceiling: what the (mul, max, min) instruction mix can sustain on sm_100a, measured with
@@ -379,6 +392,17 @@ def main():
     recorded = L.mam_timer_disarm()
     torch.cuda.synchronize()
     kernel_ms = [a.elapsed_time(b) for a, b in ev_pairs[:recorded]]
+    # the other kernels of the step, each class timed by the library's own events over three extra steps
+    # (two launches per step: layer 1 and layer 2)
+    other_ms = {}
+    for name, kid in (("index_resolver", 1), ("backward_scatter", 3), ("selection_hits", 4)):
+        _lib.check(L.mam_timer_arm(starts, stops, cap, kid), "mam_timer_arm")
+        for _ in range(3):
+            step(x_dev, gy_dev)
+        n_rec = L.mam_timer_disarm()
+        torch.cuda.synchronize()
+        per_launch = [a.elapsed_time(b) for a, b in ev_pairs[:n_rec]]
+        other_ms[name] = sum(per_launch) / 3 if per_launch else float("nan")
     e2e_ms = timed(lambda: run_from_host(args.steps), 1)
     clocks = sampler.stop() if rank == 0 else None
     _lib.check(L.mam_check_device_flag(), "device wait flag")
@@ -420,6 +444,21 @@ def main():
                     "h2d_bytes_per_step": x_host.numel() * 4 + gy_host.numel() * 4,
                     "d2h_bytes_per_step": y_host.numel() * 4 + 4},
             "gpu_launches": 10 * args.steps, "clocks": clocks, "roofline": roofline}
+    # per-step time of every kernel class and, for the two HBM-style kernels, algorithmic bytes over time
+    # against the measured copy bandwidth (both layers: M x 768 x 3072 and M x 3072 x 768)
+    hbm_peak = measured_hbm_gbs()
+    mn, mk_nk = M_TOTAL_OUTPUTS, 2 * (M_TOKENS * D_MODEL + M_TOKENS * D_FF + 2 * D_MODEL * D_FF)
+    bwd_bytes = 12 * mn + 4 * mk_nk
+    sel_bytes = 8 * mn + 8 * 2 * D_MODEL * D_FF
+    line["kernels_ms_per_step"] = {"forward_main_loop": 2 * kavg, **other_ms}
+    line["roofline_other_kernels"] = [
+        {"kernel": "mam_bwd_kernel", "bound": "hbm", "achieved": bwd_bytes / (other_ms["backward_scatter"] * 1e-3) / 1e9,
+         "peak": hbm_peak, "unit": "GB/s", "frac": bwd_bytes / (other_ms["backward_scatter"] * 1e-3) / 1e9 / hbm_peak,
+         "note": "12*M*N + 8*(M*K + N*K) bytes per layer; in practice bound by the LSU data pipe (uncoalesced gathers, "
+                 "fp32 atomics), see profiles/step_kernels_4736x768x3072.md"},
+        {"kernel": "mam_selcount_kernel", "bound": "hbm", "achieved": sel_bytes / (other_ms["selection_hits"] * 1e-3) / 1e9,
+         "peak": hbm_peak, "unit": "GB/s", "frac": sel_bytes / (other_ms["selection_hits"] * 1e-3) / 1e9 / hbm_peak,
+         "note": "8*M*N + 8*N*K bytes per layer"}]
     if world == 1 and not args.no_cpu_baseline:
         cv, threads, sample = cpu_reference_sample(256, 3)
         line["cpu_baseline"] = {"value": cv, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample}
