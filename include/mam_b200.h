@@ -48,7 +48,11 @@ const char* mam_last_cuda_error(void);
 int mam_check_device_flag(void);
 
 /* Selects the tile configuration of the tiled forward kernels: -1 (default) picks by shape,
- * other values index mam_fwd_variant_name().  A tuning / benchmarking knob, process-wide. */
+ * other values index mam_fwd_variant_name().  A tuning / benchmarking knob, process-wide.
+ * with_indices = 0 / 1 addresses the values-only / index-producing forward.  Two more selectors ride on
+ * the same call for cross-checks and timing comparisons: with_indices = 2 chooses the index resolver
+ * (variant 0 = tiled, the default; 1 = one thread per output), with_indices = 3 the backward form
+ * (variant 0 or 1 = single kernel, the default; 2 = separate dX and dW kernels). */
 int mam_set_fwd_variant(int with_indices, int variant);
 const char* mam_fwd_variant_name(int with_indices, int variant);
 
