@@ -160,6 +160,18 @@ int mam_im2col_f32(const float* x, float* rows, int64_t B, int64_t C, int64_t H,
 int mam_col2im_f32(const float* cols_t, float* dx, int64_t B, int64_t C, int64_t H, int64_t W,
                    int kH, int kW, int sh, int sw, int ph, int pw, void* stream);
 
+/* Backward of the MAM convolution straight from the input: like mam_bwd_count_ex_f32(..., MAM_B_NK,
+ * MAM_DA_KM, ...) on the patch rows of x, but the two selected activations per output are read where they
+ * live in x[B,C,H,W] (zero in the padding), so the patch rows need not be kept after the forward.
+ * w is the weight viewed as [N, C*kH*kW], grad / argmax / argmin are [B*Ho*Wo, N], cols_t receives the
+ * transposed row gradients [C*kH*kW, B*Ho*Wo] (feed it to mam_col2im_f32), dw like w.  Stands in for
+ * mamconv2d_backward of the reference's text backups (mamtorch/kernel/backup/mamconv2d_backward.txt:21-124). */
+int mam_conv_bwd_f32(const float* x, const float* w, const float* grad,
+                     const int32_t* argmax, const int32_t* argmin,
+                     float* cols_t, float* dw, float scale,
+                     int64_t B, int64_t C, int64_t H, int64_t W,
+                     int kH, int kW, int sh, int sw, int ph, int pw, int64_t N, void* stream);
+
 /* Selection hits: hit_max[n,k] += #rows m with argmax[m,n]==k, hit_min likewise ([N,K] int32,
  * accumulated into, so zero them first for per-call counts).  The device-side form of the
  * bookkeeping in FullyConnected.update_selection_count (mamtorch/nn/v4/fullyconnected.py:114-131). */

@@ -9,6 +9,7 @@
 // Sums are formed in a different order than the reference's, so gradients agree to rounding
 // (1e-5 relative in the tests), not bit for bit.
 #pragma once
+#include "mam_conv.cuh"
 #include "mam_ptx.cuh"
 
 namespace mamb200 {
@@ -18,12 +19,15 @@ constexpr int BWD_THREADS = 256;
 // B_NK: w is W[N,K] and dw has the same layout; otherwise b[K,N].
 // DA_KM: da is written transposed, da[k*M + m] (what the convolution's fold kernel wants: unit stride
 // along the output pixels); a CTA's rows are consecutive, so every k still gets one whole sector.
-template <bool B_NK, bool DA_KM = false>
+// CONV: a is not a matrix of patch rows but the convolution input x[B,C,H,W] itself; row m is output
+// pixel (b, ho, wo) and a[m][k] is read where the patch element k = (c*kH+kh)*kW+kw lives in x (zero
+// in the padding), so the patch rows need not be kept for the backward.
+template <bool B_NK, bool DA_KM = false, bool CONV = false>
 __global__ void __launch_bounds__(BWD_THREADS)
 mam_bwd_kernel(const float* __restrict__ a, const float* __restrict__ w, const float* __restrict__ g,
                const int* __restrict__ argmax, const int* __restrict__ argmin,
                float* __restrict__ da, float* __restrict__ dw,
-               long long M, long long K, long long N, int rows_per_cta, float scale) {
+               long long M, long long K, long long N, int rows_per_cta, float scale, ConvGeom cg = ConvGeom{}) {
     extern __shared__ float da_s[];  // [rows_per_cta][K]
     const long long m0 = (long long)blockIdx.x * rows_per_cta;
     const int rows = (int)min((long long)rows_per_cta, M - m0);
@@ -32,6 +36,29 @@ mam_bwd_kernel(const float* __restrict__ a, const float* __restrict__ w, const f
     for (int r = 0; r < rows; ++r) {
         const long long m = m0 + r;
         const float* arow = a + m * K;
+        // CONV: where this output pixel's patch starts in the input
+        const float* xb = a;
+        int h0 = 0, w0 = 0;
+        if constexpr (CONV) {
+            const int wo = (int)(m % cg.Wo);
+            const long long t = m / cg.Wo;
+            const int ho = (int)(t % cg.Ho);
+            xb = a + (t / cg.Ho) * (long long)cg.C * cg.H * cg.W;
+            h0 = ho * cg.sh - cg.ph;
+            w0 = wo * cg.sw - cg.pw;
+        }
+        auto a_at = [&](int k) -> float {
+            if constexpr (CONV) {
+                const int taps = cg.kH * cg.kW;
+                const int c = k / taps, rr = k - c * taps;
+                const int kh = rr / cg.kW, kw = rr - kh * cg.kW;
+                const int h = h0 + kh, ww = w0 + kw;
+                if ((unsigned)h >= (unsigned)cg.H || (unsigned)ww >= (unsigned)cg.W) return 0.f;
+                return xb[((long long)c * cg.H + h) * cg.W + ww];
+            } else {
+                return arow[k];
+            }
+        };
         float* dar = da_s + (long long)r * K;
         for (long long n = threadIdx.x; n < N; n += BWD_THREADS) {
             const float gv = __fmul_rn(g[m * N + n], scale);
@@ -41,12 +68,12 @@ mam_bwd_kernel(const float* __restrict__ a, const float* __restrict__ w, const f
             if (ok1) {
                 const long long wi = B_NK ? n * K + k1 : (long long)k1 * N + n;
                 atomicAdd(&dar[k1], __fmul_rn(w[wi], gv));
-                atomicAdd(&dw[wi], __fmul_rn(arow[k1], gv));
+                atomicAdd(&dw[wi], __fmul_rn(a_at(k1), gv));
             }
             if (ok2) {
                 const long long wi = B_NK ? n * K + k2 : (long long)k2 * N + n;
                 atomicAdd(&dar[k2], __fmul_rn(w[wi], gv));
-                atomicAdd(&dw[wi], __fmul_rn(arow[k2], gv));
+                atomicAdd(&dw[wi], __fmul_rn(a_at(k2), gv));
             }
         }
     }

@@ -503,7 +503,8 @@ int mam_bwd_count_ex_f32(const float* a, const float* b, int b_layout, const flo
         auto launch = [&](auto kern) -> int {
             MAM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             TimedLaunch t(MAM_KERNEL_BWD, cs);
-            kern<<<(unsigned)grid, BWD_THREADS, smem, cs>>>(a, b, grad, argmax, argmin, da, db, M, K, N, rows, scale);
+            kern<<<(unsigned)grid, BWD_THREADS, smem, cs>>>(a, b, grad, argmax, argmin, da, db, M, K, N, rows, scale,
+                                                            ConvGeom{});
             return MAM_OK;
         };
         const bool nk = b_layout == MAM_B_NK, km = da_layout == MAM_DA_KM;
@@ -534,6 +535,40 @@ int conv_geom(ConvGeom* g, int64_t B, int64_t C, int64_t H, int64_t W, int kH, i
     return MAM_OK;
 }
 }  // namespace
+
+int mam_conv_bwd_f32(const float* x, const float* w, const float* grad, const int32_t* argmax, const int32_t* argmin,
+                     float* cols_t, float* dw, float scale, int64_t B, int64_t C, int64_t H, int64_t W, int kH, int kW,
+                     int sh, int sw, int ph, int pw, int64_t N, void* stream) {
+    if (bad_ptr(x) || bad_ptr(w) || bad_ptr(grad) || bad_ptr(argmax) || bad_ptr(argmin) || bad_ptr(cols_t) ||
+        bad_ptr(dw) || N <= 0)
+        return MAM_ERR_INVALID_ARGUMENT;
+    ConvGeom g;
+    int st = conv_geom(&g, B, C, H, W, kH, kW, sh, sw, ph, pw);
+    if (st != MAM_OK) return st;
+    const long long M = (long long)g.B * g.Ho * g.Wo, K = (long long)g.C * g.kH * g.kW;
+    const DevInfo* d = nullptr;
+    st = device_info(&d);
+    if (st != MAM_OK) return st;
+    if (K * 4 > d->max_smem - 1024) return MAM_ERR_UNSUPPORTED;
+    cudaStream_t cs = (cudaStream_t)stream;
+    int rows = (int)((32 * 1024) / (K * 4));
+    if (rows < 1) rows = 1;
+    if (rows > 8) rows = 8;
+    if (16 * K * 4 <= 48 * 1024) rows = 16;   // transposed row gradients: longer runs per patch element
+    const size_t smem = (size_t)rows * (size_t)K * 4;
+    const long long grid = (M + rows - 1) / rows;
+    if (grid > 2147483647LL) return MAM_ERR_UNSUPPORTED;
+    MAM_CUDA(cudaMemsetAsync(dw, 0, (size_t)K * (size_t)N * 4, cs));
+    MAM_CUDA(cudaFuncSetAttribute(mam_bwd_kernel<true, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  (int)smem));
+    {
+        TimedLaunch t(MAM_KERNEL_BWD, cs);
+        mam_bwd_kernel<true, true, true><<<(unsigned)grid, BWD_THREADS, smem, cs>>>(x, w, grad, argmax, argmin, cols_t,
+                                                                                     dw, M, K, N, rows, scale, g);
+    }
+    MAM_CUDA(cudaGetLastError());
+    return MAM_OK;
+}
 
 int mam_im2col_f32(const float* x, float* rows, int64_t B, int64_t C, int64_t H, int64_t W, int kH, int kW, int sh,
                    int sw, int ph, int pw, void* stream) {

@@ -274,6 +274,38 @@ at::Tensor conv_col2im(const at::Tensor& cols_t, int64_t B, int64_t C, int64_t H
                  "mam_col2im_f32");
     return dx;
 }
+// {cols_t [C*kH*kW, B*Ho*Wo], dw [N, C*kH*kW]}: convolution backward reading the selected activations from x itself
+std::vector<at::Tensor> conv_backward(const at::Tensor& x, const at::Tensor& w2d, const at::Tensor& grad,
+                                      const at::Tensor& argmax, const at::Tensor& argmin, double scale, int64_t kH,
+                                      int64_t kW, int64_t sh, int64_t sw, int64_t ph, int64_t pw) {
+    TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kFloat && x.dim() == 4, "x must be a float32 CUDA [B,C,H,W] tensor");
+    check_matrix(w2d, "weight");
+    check_matrix(grad, "grad");
+    check_matrix(argmax, "argmax", at::kInt);
+    check_matrix(argmin, "argmin", at::kInt);
+    auto xc = x.contiguous();
+    const int64_t B = xc.size(0), C = xc.size(1), H = xc.size(2), W = xc.size(3);
+    const int64_t Ho = (H + 2 * ph - kH) / sh + 1, Wo = (W + 2 * pw - kW) / sw + 1;
+    const int64_t M = B * Ho * Wo, K = C * kH * kW, N = w2d.size(0);
+    TORCH_CHECK(w2d.size(1) == K, "weight must be [N, C*kH*kW]");
+    TORCH_CHECK(grad.size(0) == M && grad.size(1) == N, "grad must be [B*Ho*Wo, N]");
+    TORCH_CHECK(argmax.sizes() == grad.sizes() && argmin.sizes() == grad.sizes(), "index shapes must match grad");
+    c10::cuda::CUDAGuard guard(x.device());
+    auto cols_t = at::empty({K, M}, xc.options());
+    auto dw = at::empty_like(w2d);
+    if (M == 0 || N == 0 || K == 0) {
+        cols_t.zero_();
+        dw.zero_();
+        return {cols_t, dw};
+    }
+    auto stream = at::cuda::getCurrentCUDAStream();
+    check_status(mam_conv_bwd_f32(xc.data_ptr<float>(), w2d.data_ptr<float>(), grad.data_ptr<float>(),
+                                  argmax.data_ptr<int32_t>(), argmin.data_ptr<int32_t>(), cols_t.data_ptr<float>(),
+                                  dw.data_ptr<float>(), (float)scale, B, C, H, W, (int)kH, (int)kW, (int)sh, (int)sw,
+                                  (int)ph, (int)pw, N, stream.stream()),
+                 "mam_conv_bwd_f32");
+    return {cols_t, dw};
+}
 // {dx transposed [K,M], dw}: the backward of linear_forward with the row gradients laid out for conv_col2im
 std::vector<at::Tensor> linear_backward_km(const at::Tensor& x, const at::Tensor& weight, const at::Tensor& grad,
                                            const at::Tensor& argmax, const at::Tensor& argmin, double scale) {
@@ -430,6 +462,7 @@ TORCH_LIBRARY(mamtorch_b200, m) {
     m.def("linear_backward(Tensor x, Tensor weight, Tensor grad, Tensor argmax, Tensor argmin, float scale) -> Tensor[]");
     m.def("linear_backward_count(Tensor x, Tensor weight, Tensor grad, Tensor argmax, Tensor argmin, float scale) -> Tensor[]");
     m.def("linear_backward_km(Tensor x, Tensor weight, Tensor grad, Tensor argmax, Tensor argmin, float scale) -> Tensor[]");
+    m.def("conv_backward(Tensor x, Tensor weight, Tensor grad, Tensor argmax, Tensor argmin, float scale, int kH, int kW, int sh, int sw, int ph, int pw) -> Tensor[]");
     m.def("conv_im2col(Tensor x, int kH, int kW, int sh, int sw, int ph, int pw) -> Tensor");
     m.def("conv_col2im(Tensor cols_t, int B, int C, int H, int W, int kH, int kW, int sh, int sw, int ph, int pw) -> Tensor");
     m.def("selection_hits(Tensor argmax, Tensor argmin, int K) -> Tensor[]");
@@ -444,6 +477,7 @@ TORCH_LIBRARY_IMPL(mamtorch_b200, CUDA, m) {
     m.impl("linear_backward", &linear_backward);
     m.impl("linear_backward_count", &linear_backward_count);
     m.impl("linear_backward_km", &linear_backward_km);
+    m.impl("conv_backward", &conv_backward);
     m.impl("conv_im2col", &conv_im2col);
     m.impl("conv_col2im", &conv_col2im);
     m.impl("selection_hits", &selection_hits);

@@ -34,7 +34,8 @@ def _pair(v):
 class _MamConv2d(torch.autograd.Function):
     """MAM convolution on patch rows: one im2col pass, the fully-connected kernels, and for the input
     gradient the backward's transposed row gradients folded by a gather kernel (no atomics).  The
-    patch rows are kept for the backward (it reads the two selected activations per output)."""
+    patch rows live only during the forward: the backward reads the two selected activations per
+    output from the input itself."""
 
     @staticmethod
     def forward(ctx, x, weight, bias, dense, alpha, beta, stride, padding):
@@ -48,7 +49,7 @@ class _MamConv2d(torch.autograd.Function):
         if dense is not None:
             dflat = dense.permute(0, 2, 3, 1).reshape(B * Ho * Wo, Fo).contiguous()
         y, amax, amin = _ops.linear_forward(rows, w2d, bias, dflat, alpha, beta, True)
-        ctx.save_for_backward(rows, w2d, amax, amin)
+        ctx.save_for_backward(x, w2d, amax, amin)
         ctx.geom = (B, C, H, W, Fo, kH, kW, sh, sw, ph, pw, Ho, Wo)
         ctx.alpha, ctx.beta = alpha, beta
         ctx.has_bias, ctx.has_dense = bias is not None, dense is not None
@@ -59,12 +60,12 @@ class _MamConv2d(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, gy, _g1, _g2):
-        rows, w2d, amax, amin = ctx.saved_tensors
+        x, w2d, amax, amin = ctx.saved_tensors
         B, C, H, W, Fo, kH, kW, sh, sw, ph, pw, Ho, Wo = ctx.geom
         g2d = gy.permute(0, 2, 3, 1).reshape(B * Ho * Wo, Fo).contiguous()
         dx = dw = dbias = ddense = None
         if ctx.needs_input_grad[0] or ctx.needs_input_grad[1]:
-            cols_t, dw2d = _ops.linear_backward_km(rows, w2d, g2d, amax, amin, ctx.alpha)
+            cols_t, dw2d = _ops.conv_backward(x, w2d, g2d, amax, amin, ctx.alpha, kH, kW, sh, sw, ph, pw)
             if ctx.needs_input_grad[0]:
                 dx = _ops.conv_col2im(cols_t, B, C, H, W, kH, kW, sh, sw, ph, pw)
             dw = dw2d.view(Fo, C, kH, kW)

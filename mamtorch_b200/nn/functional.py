@@ -33,6 +33,11 @@ def _(x, weight, grad, argmax, argmin, scale):
     return [x.new_empty((x.size(1), x.size(0))), torch.empty_like(weight)]
 
 
+@torch.library.register_fake("mamtorch_b200::conv_backward")
+def _(x, weight, grad, argmax, argmin, scale, kH, kW, sh, sw, ph, pw):
+    return [x.new_empty((weight.size(1), grad.size(0))), torch.empty_like(weight)]
+
+
 @torch.library.register_fake("mamtorch_b200::conv_im2col")
 def _(x, kH, kW, sh, sw, ph, pw):
     B, C, H, W = x.shape

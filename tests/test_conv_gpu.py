@@ -73,6 +73,31 @@ def test_backward_transposed_row_gradients(shape, cuda):
                                   1.0, M, K, N, capi._stream()) == 1
 
 
+@pytest.mark.parametrize("geom", [GEOMS[0], GEOMS[1], GEOMS[3], GEOMS[5]])
+def test_conv_backward_from_the_input_equals_backward_on_patch_rows(geom, cuda):
+    """mam_conv_bwd_f32 reads the selected activations from x; mam_bwd_count_ex_f32 reads them from the patch
+    rows: same row gradients (same summation order per CTA), dW to rounding (atomics)."""
+    B, C, H, W, kH, kW, sh, sw, ph, pw = geom
+    L = _lib.lib()
+    g = torch.Generator().manual_seed(7 + sum(geom))
+    x = torch.randn(B, C, H, W, generator=g).to(cuda)
+    Ho, Wo = (H + 2 * ph - kH) // sh + 1, (W + 2 * pw - kW) // sw + 1
+    M, K, N = B * Ho * Wo, C * kH * kW, 9
+    w = (torch.randn(N, K, generator=g) * K ** -0.5).to(cuda)
+    gy = torch.randn(M, N, generator=g).to(cuda)
+    rows = torch.empty(M, K, device=cuda)
+    _lib.check(L.mam_im2col_f32(_p(x), _p(rows), B, C, H, W, kH, kW, sh, sw, ph, pw, capi._stream()), "mam_im2col_f32")
+    _, imax, imin = capi.forward(rows, w, capi.NK)
+    ct_a, dw_a = torch.empty(K, M, device=cuda), torch.empty_like(w)
+    ct_b, dw_b = torch.empty(K, M, device=cuda), torch.empty_like(w)
+    _lib.check(L.mam_bwd_count_ex_f32(_p(rows), _p(w), capi.NK, _p(gy), _p(imax), _p(imin), _p(ct_a), 1, _p(dw_a), None,
+                                      None, 0.5, M, K, N, capi._stream()), "mam_bwd_count_ex_f32")
+    _lib.check(L.mam_conv_bwd_f32(_p(x), _p(w), _p(gy), _p(imax), _p(imin), _p(ct_b), _p(dw_b), 0.5, B, C, H, W, kH, kW,
+                                  sh, sw, ph, pw, N, capi._stream()), "mam_conv_bwd_f32")
+    assert_grad_close(ct_b.cpu().numpy(), ct_a.cpu().numpy())
+    assert_grad_close(dw_b.cpu().numpy(), dw_a.cpu().numpy())
+
+
 def test_strided_padded_conv_module_gradients(cuda):
     import mamtorch_b200 as mamtorch
 
