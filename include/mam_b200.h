@@ -221,6 +221,19 @@ int mam_csr_fwd_ws_f32(const float* a, const int64_t* crow, const int64_t* col, 
 int mam_spmm_csr_f32(const int64_t* crow, const int64_t* col, const float* val, const float* b,
                      float* c, int64_t N, int64_t K, int64_t Mc, void* stream);
 
+/* The same product through the tiled kernel, which wants scratch from the caller for the regrouped
+ * entries (8 bytes per entry plus 12 bytes per (row, 64-column stage) pair; 256-byte aligned;
+ * mam_spmm_csr_workspace_bytes returns 0 where the tiled form does not apply or does not pay: Mc < 64,
+ * Mc % 4 != 0, fewer than two stored entries per (row, stage) pair on average, less than ~1e9
+ * multiply-adds, or extents beyond its 32-bit offsets).  With workspace == NULL, or where the tiled
+ * form cannot run (Mc < 64, Mc % 4 != 0, b or c not 16-byte aligned), the call runs mam_spmm_csr_f32; a
+ * caller that passes a large enough workspace although the query answered 0 for lack of work still
+ * gets the tiled kernel.  Entries of a row are summed in ascending column order in both. */
+size_t mam_spmm_csr_workspace_bytes(int64_t N, int64_t K, int64_t Mc, int64_t nnz);
+int mam_spmm_csr_ws_f32(const int64_t* crow, const int64_t* col, const float* val, int64_t nnz,
+                        const float* b, float* c, int64_t N, int64_t K, int64_t Mc,
+                        void* workspace, size_t workspace_bytes, void* stream);
+
 /* out[C,R] = transpose(in[R,C]); replaces the .T.contiguous() copies of the reference's glue
  * (mamtorch/nn/v4/fullyconnected.py:141, mamtorch/kernel/v4/csrc/cuda/fullyconnected.cu:66). */
 int mam_transpose_f32(const float* in, float* out, int64_t R, int64_t C, void* stream);

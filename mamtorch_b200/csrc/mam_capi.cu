@@ -776,7 +776,7 @@ int mam_csr_fwd_ws_f32(const float* a, const int64_t* crow, const int64_t* col, 
         csr_scan_sums_kernel<<<1, 1024, 0, cs>>>(block_sums, nb);
         csr_scan_apply_kernel<<<(unsigned)nb, 1024, 0, cs>>>(counts, block_sums, seg, segs);
     }
-    csr_tile_fill_kernel<<<seg_blocks, 256, 0, cs>>>(crow_ll, col_ll, val, seg, list, rlist, N, w.nks);
+    csr_tile_fill_kernel<<<seg_blocks, 256, 0, cs>>>(crow_ll, col_ll, val, seg, list, rlist, N, w.nks, 0);
     MAM_CUDA(cudaGetLastError());
 
     CUtensorMap tmAT;
@@ -811,6 +811,88 @@ int mam_csr_fwd_ws_f32(const float* a, const int64_t* crow, const int64_t* col, 
     if (2 * row_bytes <= 110 * 1024) st = launch_resolve(mam_csr_resolve_kernel<2>, 2);
     else st = launch_resolve(mam_csr_resolve_kernel<1>, 1);
     if (st != MAM_OK) return st;
+    MAM_CUDA(cudaGetLastError());
+    return MAM_OK;
+}
+
+namespace {
+struct SpmmWs {
+    size_t counts_off, seg_off, k0_off, list_off, total;
+    int nks;
+};
+SpmmWs spmm_ws_layout(int64_t N, int64_t K, int64_t nnz) {
+    SpmmWs w{};
+    w.nks = (int)((K + CT_KS - 1) / CT_KS);
+    const size_t segs = (size_t)w.nks * (size_t)N;
+    size_t off = 0;
+    w.counts_off = off; off += round256(segs * 4);
+    w.seg_off = off;    off += round256((segs + 1) * 4);
+    w.k0_off = off;     off += round256((size_t)N * 4);
+    w.list_off = off;   off += round256(((size_t)nnz + segs) * sizeof(CsrEntry));
+    w.total = off;
+    return w;
+}
+bool spmm_tiled_applies(int64_t N, int64_t K, int64_t Mc, int64_t nnz, const float* b, const float* c) {
+    const long long nks = (K + CT_KS - 1) / CT_KS;
+    return Mc >= 64 && Mc % 4 == 0 && (b == nullptr || aligned16(b)) && (c == nullptr || aligned16(c)) &&
+           nks * N < (1LL << 30) && nnz + nks * N < (1LL << 30) && K < (1LL << 31) &&
+           (N + SP_BN - 1) / SP_BN < (1LL << 31) && (Mc + CT_BM - 1) / CT_BM <= 65535;
+}
+}  // namespace
+
+size_t mam_spmm_csr_workspace_bytes(int64_t N, int64_t K, int64_t Mc, int64_t nnz) {
+    if (N <= 0 || K <= 0 || Mc <= 0 || nnz < 0 || !spmm_tiled_applies(N, K, Mc, nnz, nullptr, nullptr)) return 0;
+    // The tiled kernel pays only with enough entries per (row, stage) segment and enough work to cover the
+    // regrouping launches: below ~3 % density or ~1e9 multiply-adds the thread-per-output kernel wins
+    // (measured: 4096^2 x 4096 at 90 % sparsity 1.29 vs 3.2 ms, at 99 % 0.59 vs 0.39 ms).  Answering 0 here
+    // steers callers to it; a caller that passes a workspace anyway gets the tiled kernel.
+    const long long nks = (K + CT_KS - 1) / CT_KS;
+    if (nnz < 2 * N * nks || (double)nnz * (double)Mc < 1e9) return 0;
+    return spmm_ws_layout(N, K, nnz).total;
+}
+
+int mam_spmm_csr_ws_f32(const int64_t* crow, const int64_t* col, const float* val, int64_t nnz, const float* b,
+                        float* c, int64_t N, int64_t K, int64_t Mc, void* workspace, size_t workspace_bytes,
+                        void* stream) {
+    if (bad_ptr(crow) || bad_ptr(b) || bad_ptr(c) || N <= 0 || K <= 0 || Mc <= 0 || nnz < 0)
+        return MAM_ERR_INVALID_ARGUMENT;
+    if (workspace == nullptr || !spmm_tiled_applies(N, K, Mc, nnz, b, c))
+        return mam_spmm_csr_f32(crow, col, val, b, c, N, K, Mc, stream);
+    const SpmmWs w = spmm_ws_layout(N, K, nnz);
+    if (workspace_bytes < w.total || (reinterpret_cast<uintptr_t>(workspace) & 255u)) return MAM_ERR_WORKSPACE;
+    const DevInfo* d = nullptr;
+    int st = device_info(&d);
+    if (st != MAM_OK) return st;
+    if (SP_SMEM_BYTES > d->max_smem) return MAM_ERR_UNSUPPORTED;
+    cudaStream_t cs = (cudaStream_t)stream;
+    unsigned char* ws = static_cast<unsigned char*>(workspace);
+    int* counts = reinterpret_cast<int*>(ws + w.counts_off);
+    int* seg = reinterpret_cast<int*>(ws + w.seg_off);
+    int* k0 = reinterpret_cast<int*>(ws + w.k0_off);
+    CsrEntry* list = reinterpret_cast<CsrEntry*>(ws + w.list_off);
+    const long long segs = (long long)w.nks * N;
+    const unsigned seg_blocks = (unsigned)((segs + 255) / 256);
+    const long long* crow_ll = reinterpret_cast<const long long*>(crow);
+    const long long* col_ll = reinterpret_cast<const long long*>(col);
+    csr_tile_count_kernel<<<seg_blocks, 256, 0, cs>>>(crow_ll, col_ll, counts, k0, N, K, w.nks);
+    {
+        int* block_sums = reinterpret_cast<int*>(list);
+        const long long nb = (segs + 1 + CSR_SCAN_BLOCK - 1) / CSR_SCAN_BLOCK;
+        csr_scan_block_sums_kernel<<<(unsigned)nb, 1024, 0, cs>>>(counts, block_sums, segs);
+        csr_scan_sums_kernel<<<1, 1024, 0, cs>>>(block_sums, nb);
+        csr_scan_apply_kernel<<<(unsigned)nb, 1024, 0, cs>>>(counts, block_sums, seg, segs);
+    }
+    csr_tile_fill_kernel<<<seg_blocks, 256, 0, cs>>>(crow_ll, col_ll, val, seg, list, nullptr, N, w.nks, 1);
+    MAM_CUDA(cudaGetLastError());
+    CUtensorMap tmB;
+    st = encode_2d_plain(&tmB, b, Mc, K, Mc * 4, CT_BM, CT_KS);
+    if (st != MAM_OK) return st;
+    int* flag = nullptr;
+    MAM_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&flag), g_wait_gave_up));
+    SpmmTiledParams prm{seg, list, c, N, K, Mc, w.nks, flag};
+    const dim3 grid((unsigned)((N + SP_BN - 1) / SP_BN), (unsigned)((Mc + CT_BM - 1) / CT_BM));
+    MAM_CUDA(cudaFuncSetAttribute(mam_spmm_tiled_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SP_SMEM_BYTES));
+    mam_spmm_tiled_kernel<<<grid, CT_THREADS, SP_SMEM_BYTES, cs>>>(tmB, prm);
     MAM_CUDA(cudaGetLastError());
     return MAM_OK;
 }

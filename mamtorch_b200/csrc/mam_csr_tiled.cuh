@@ -191,7 +191,7 @@ csr_scan_apply_kernel(const int* __restrict__ counts, const int* __restrict__ bl
 __global__ void __launch_bounds__(256)
 csr_tile_fill_kernel(const long long* __restrict__ crow, const long long* __restrict__ col,
                      const float* __restrict__ val, const int* __restrict__ seg, CsrEntry* __restrict__ list,
-                     CsrColEntry* __restrict__ rlist, long long N, int nks) {
+                     CsrColEntry* __restrict__ rlist, long long N, int nks, int pad_with_zero) {
     const long long idx = (long long)blockIdx.x * 256 + threadIdx.x;
     if (idx >= (long long)nks * N) return;
     const int s = (int)(idx / N);
@@ -208,11 +208,14 @@ csr_tile_fill_kernel(const long long* __restrict__ crow, const long long* __rest
         rlast.k = (unsigned)col[t] | (t + 1 == hi ? CSR_LAST : 0u);
         rlast.v = last.v;
         list[p] = last;
-        rlist[p++] = rlast;
+        if (rlist) rlist[p] = rlast;
+        ++p;
     }
     if ((hi - lo) & 1) {
+        // max/min are idempotent, so their padding repeats the last entry; a sum needs a zero instead
+        if (pad_with_zero) last.v = 0.f;
         list[p] = last;
-        rlist[p] = rlast;
+        if (rlist) rlist[p] = rlast;
     }
 }
 
@@ -553,6 +556,167 @@ mam_csr_resolve_kernel(const float* __restrict__ a, const CsrColEntry* __restric
                 const long long o = (m0 + q / 2) * N + n;
                 ((q & 1) ? argmin : argmax)[o] = (int)min(bk[q], (unsigned)(K - 1));
             }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// C[N, Mc] = A_csr[N, K] . B[K, Mc] in the ordinary sum semiring, on the same machinery: B is already
+// "k-major with the other index contiguous", exactly what the MAM kernel above wants of the transposed
+// activations, so a CTA takes 128 columns of B/C and 128 rows of A; B arrives by TMA in stages of 64
+// rows, every lane owns 4 adjacent columns, every warp 8 rows of A whose stored entries are broadcast
+// and applied with fma.rn.f32x2.  Entries of a row are applied in ascending column order, so a result
+// does not depend on the tiling.  Stands in for cusparsemm_csr / cusparsemm_coo of the reference
+// (mamtorch/sparse/kernel/v1/csrc/cuda/cusparsemm_csr.cu:19-77, cusparsemm_coo.cu:19-76).
+constexpr int SP_WROWS = 8;
+constexpr int SP_BN = CT_WARPS * SP_WROWS;
+constexpr int SP_STAGES = 6;
+constexpr int SP_LOOKAHEAD = SP_STAGES - 2;
+constexpr int SP_SMEM_BYTES = 1024 + SP_STAGES * CT_STAGE_BYTES + CT_EB_BYTES + 2 * SP_STAGES * 8;
+
+struct SpmmTiledParams {
+    const int* seg;
+    const CsrEntry* list;
+    float* c;
+    long long N, K, Mc;
+    int nks;
+    int* error;
+};
+
+__device__ __forceinline__ f32x2_t fma2(f32x2_t a, f32x2_t b, f32x2_t c) {
+    f32x2_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+
+__global__ void __launch_bounds__(CT_THREADS, 1)
+mam_spmm_tiled_kernel(const __grid_constant__ CUtensorMap tmB, const SpmmTiledParams prm) {
+    extern __shared__ unsigned char sp_smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>(
+        (reinterpret_cast<uintptr_t>(sp_smem_raw) + 1023) & ~uintptr_t(1023));
+    int4* eb_all = reinterpret_cast<int4*>(smem + SP_STAGES * CT_STAGE_BYTES);
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + SP_STAGES * CT_STAGE_BYTES + CT_EB_BYTES);
+    uint64_t* empty_bar = full_bar + SP_STAGES;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const long long N = prm.N;
+    const long long n_cta = (long long)blockIdx.x * SP_BN;
+    const long long j0 = (long long)blockIdx.y * CT_BM;
+    const int nks = prm.nks;
+
+    if (tid == 0) {
+        for (int s = 0; s < SP_STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], CT_WARPS);
+        }
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    int p_ks = 0, p_stage = 0;
+    uint32_t p_phase = 0;
+    auto produce_one = [&]() -> bool {
+        if (p_ks >= nks) return true;
+        if (!mbar_wait_bounded(&empty_bar[p_stage], p_phase ^ 1u)) return false;
+        mbar_expect_tx(&full_bar[p_stage], CT_STAGE_BYTES);
+        tma_load_2d(smem + p_stage * CT_STAGE_BYTES, &tmB, &full_bar[p_stage], (int)j0, p_ks * CT_KS);
+        if (++p_stage == SP_STAGES) { p_stage = 0; p_phase ^= 1u; }
+        ++p_ks;
+        return true;
+    };
+    if (tid == 0) {
+        tma_prefetch_desc(&tmB);
+        for (int i = 0; i < SP_LOOKAHEAD; ++i) produce_one();
+    }
+
+    const long long n_w = n_cta + warp * SP_WROWS;
+    int4* eb = eb_all + warp * CT_EB_PAIRS;
+    const int4* list4 = reinterpret_cast<const int4*>(prm.list);
+    f32x2_t acc[SP_WROWS][2];   // 4 adjacent columns of C per row of A, as two packed pairs
+#pragma unroll
+    for (int j = 0; j < SP_WROWS; ++j) acc[j][0] = acc[j][1] = pack2(0.f, 0.f);
+
+    auto load_seg = [&](int ks) -> int {
+        const long long r = min(n_w + (long long)lane, N);
+        return (lane <= SP_WROWS && ks < nks) ? __ldg(prm.seg + (long long)ks * N + r) : 0;
+    };
+    int seg_next = load_seg(0);
+    int4 pre = make_int4(0, 0, 0, 0);
+    {
+        const int p0 = __shfl_sync(0xffffffffu, seg_next, 0) >> 1, p1 = __shfl_sync(0xffffffffu, seg_next, SP_WROWS) >> 1;
+        if (p0 + lane < p1) pre = __ldg(list4 + p0 + lane);
+    }
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int ks = 0; ks < nks; ++ks) {
+        const int seg_cur = seg_next;
+        seg_next = load_seg(ks + 1);
+        int bnd[SP_WROWS + 1];
+#pragma unroll
+        for (int j = 0; j <= SP_WROWS; ++j) bnd[j] = __shfl_sync(0xffffffffu, seg_cur, j) >> 1;
+        int4 mine = pre;
+        {
+            const int p0 = __shfl_sync(0xffffffffu, seg_next, 0) >> 1, p1 = __shfl_sync(0xffffffffu, seg_next, SP_WROWS) >> 1;
+            pre = make_int4(0, 0, 0, 0);
+            if (p0 + lane < p1) pre = __ldg(list4 + p0 + lane);
+        }
+        if (tid == 0 && !produce_one()) atomicExch(prm.error, 1);
+        if (!mbar_wait_bounded(&full_bar[stage], phase)) {
+            atomicExch(prm.error, 1);
+            ok = false;
+            break;
+        }
+        const uint32_t xs = smem_u32(smem) + (uint32_t)(stage * CT_STAGE_BYTES) + (uint32_t)lane * 16u;
+        const uint32_t ebs = smem_u32(eb);
+        for (int off = bnd[0]; off < bnd[SP_WROWS]; off += CT_EB_PAIRS) {
+            if (off > bnd[0]) {
+                mine = make_int4(0, 0, 0, 0);
+                if (off + lane < bnd[SP_WROWS]) mine = __ldg(list4 + off + lane);
+            }
+            __syncwarp();
+            eb[lane] = mine;
+            __syncwarp();
+            static_for<0, SP_WROWS>([&](auto jc) {
+                constexpr int j = decltype(jc)::value;
+                const int lo = max(bnd[j], off) - off, hi = min(bnd[j + 1], off + CT_EB_PAIRS) - off;
+#pragma unroll 2
+                for (int q = lo; q < hi; ++q) {
+                    int4 e;
+                    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                                 : "=r"(e.x), "=r"(e.y), "=r"(e.z), "=r"(e.w)
+                                 : "r"(ebs + (uint32_t)q * 16u)
+                                 : "memory");
+                    const ulonglong2 x0 = lds128_at<0>(xs + (uint32_t)e.x);
+                    const ulonglong2 x1 = lds128_at<0>(xs + (uint32_t)e.z);
+                    const float v0 = __int_as_float(e.y), v1 = __int_as_float(e.w);
+                    const f32x2_t vv0 = pack2(v0, v0), vv1 = pack2(v1, v1);
+                    acc[j][0] = fma2(x1.x, vv1, fma2(x0.x, vv0, acc[j][0]));
+                    acc[j][1] = fma2(x1.y, vv1, fma2(x0.y, vv0, acc[j][1]));
+                }
+            });
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty_bar[stage]);
+        if (++stage == SP_STAGES) { stage = 0; phase ^= 1u; }
+    }
+    if (!ok) return;   // nothing after the loop needs the whole CTA
+    // each lane writes its 4 adjacent columns of every row: 512 contiguous bytes per row and warp
+    const long long j = j0 + 4 * lane;
+#pragma unroll
+    for (int r = 0; r < SP_WROWS; ++r) {
+        const long long n = n_w + r;
+        if (n >= N) break;
+        float v[4];
+        unpack2(acc[r][0], v[0], v[1]);
+        unpack2(acc[r][1], v[2], v[3]);
+        float* o = prm.c + n * prm.Mc + j;
+        if (j + 3 < prm.Mc) {
+            *reinterpret_cast<float4*>(o) = make_float4(v[0], v[1], v[2], v[3]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                if (j + i < prm.Mc) o[i] = v[i];
         }
     }
 }

@@ -402,9 +402,14 @@ at::Tensor spmm_csr(const at::Tensor& a, const at::Tensor& b) {
     if (val.numel() == 0) return c;
     auto bc = b.contiguous();
     auto stream = at::cuda::getCurrentCUDAStream();
-    check_status(mam_spmm_csr_f32(crow.data_ptr<int64_t>(), col.data_ptr<int64_t>(), val.data_ptr<float>(),
-                                  bc.data_ptr<float>(), c.data_ptr<float>(), N, K, Mc, stream.stream()),
-                 "mam_spmm_csr_f32");
+    const int64_t nnz = val.numel();
+    const size_t wsb = mam_spmm_csr_workspace_bytes(N, K, Mc, nnz);   // 0: the tiled kernel does not apply
+    at::Tensor ws;
+    if (wsb) ws = at::empty({(int64_t)wsb}, bc.options().dtype(at::kByte));
+    check_status(mam_spmm_csr_ws_f32(crow.data_ptr<int64_t>(), col.data_ptr<int64_t>(), val.data_ptr<float>(), nnz,
+                                     bc.data_ptr<float>(), c.data_ptr<float>(), N, K, Mc, wsb ? ws.data_ptr() : nullptr,
+                                     wsb, stream.stream()),
+                 "mam_spmm_csr_ws_f32");
     return c;
 }
 at::Tensor spmm_coo(const at::Tensor& a, const at::Tensor& b) { return spmm_csr(a.to_sparse_csr(), b); }

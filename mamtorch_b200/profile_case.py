@@ -6,7 +6,10 @@ captures are taken on.
 ops: fwd_idx (forward with indices: tiled kernel + index resolver), fwd_val (values only),
 bwd (selected-pair backward), selcount, step (forward + backward + selection count of one layer
 through the nn module), dense_tf32 (tcgen05 product of the beta term), csr_fwd (forward on a weight
-pruned to 90 % sparsity, CSR).  Inputs are seeded N(0,1) activations and N(0,1/K) weights in [N,K] layout.
+pruned to `--sparsity`, CSR), spmm (the ordinary product c[N,M] = w_csr[N,K] . xT[K,M] behind `cusparsemm`;
+with `--compare` also `torch.sparse.mm`, i.e. cuSPARSE, on the same operands).  Inputs are seeded N(0,1)
+activations and N(0,1/K) weights in [N,K] layout.  The last line reports the CUDA-event time per repetition
+(the first repetition is not timed).
 """
 import argparse
 
@@ -16,7 +19,9 @@ import torch
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--shape", default="4096x1024x2048", help="MxKxN")
-    ap.add_argument("--op", default="fwd_idx", choices=["fwd_idx", "fwd_val", "bwd", "selcount", "step", "dense_tf32", "csr_fwd"])
+    ap.add_argument("--op", default="fwd_idx", choices=["fwd_idx", "fwd_val", "bwd", "selcount", "step", "dense_tf32", "csr_fwd", "spmm"])
+    ap.add_argument("--sparsity", type=float, default=0.9, help="share of zeroed weights for csr_fwd / spmm")
+    ap.add_argument("--compare", action="store_true", help="spmm: time torch.sparse.mm on the same operands too")
     ap.add_argument("--reps", type=int, default=3)
     ap.add_argument("--variant", type=int, default=-1, help="tile configuration of the tiled forward (-1 auto)")
     args = ap.parse_args()
@@ -36,7 +41,14 @@ def main():
         _lib.check(_lib.lib().mam_set_fwd_variant(0, args.variant), "variant")
     ops = torch.ops.mamtorch_b200
     y, imax, imin = ops.linear_forward(x, w, None, None, 1.0, 0.0, True)
-    for _ in range(args.reps):
+    if args.op in ("csr_fwd", "spmm"):
+        keep = (torch.rand(N, K, generator=g) >= args.sparsity).float().to(dev)
+        w_csr = (w * keep).to_sparse_csr()
+        xT = x.t().contiguous()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for rep in range(args.reps + 1):
+        if rep == min(1, args.reps):
+            e0.record()
         if args.op == "fwd_idx":
             y, imax, imin = ops.linear_forward(x, w, None, None, 1.0, 0.0, True)
         elif args.op == "fwd_val":
@@ -48,18 +60,30 @@ def main():
         elif args.op == "dense_tf32":
             y = ops.dense_nt(x, w)
         elif args.op == "csr_fwd":
-            if "w_csr" not in locals():
-                keep = (torch.rand(N, K, generator=g) >= 0.9).float().to(dev)
-                w_csr = (w * keep).to_sparse_csr()
             y, imax, imin = mamtorch.sparse.kernel.v1.mam_linear_csr(x, w_csr)
+        elif args.op == "spmm":
+            y = mamtorch.sparse.kernel.v1.cusparsemm(w_csr, xT)
         else:
             layer = mamtorch.nn.FullyConnected(K, N, store_args=True).to(dev)
             out = layer(x.clone().requires_grad_())
             out.backward(gy)
             layer.update_selection_count()
+    e1.record()
     torch.cuda.synchronize()
     _lib.check(_lib.lib().mam_check_device_flag(), "device wait flag")
-    print(f"ok {args.op} {M}x{K}x{N} checksum {float(y.double().sum()):.6e}")
+    ms = e0.elapsed_time(e1) / max(args.reps, 1)
+    extra = ""
+    if args.op == "spmm" and args.compare:
+        ref = torch.sparse.mm(w_csr, xT)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(args.reps):
+            ref = torch.sparse.mm(w_csr, xT)
+        e1.record()
+        torch.cuda.synchronize()
+        extra = (f" torch_sparse_mm_ms {e0.elapsed_time(e1) / max(args.reps, 1):.4f}"
+                 f" max_abs_diff {float((y - ref).abs().max()):.3e}")
+    print(f"ok {args.op} {M}x{K}x{N} checksum {float(y.double().sum()):.6e} ms_per_rep {ms:.4f}{extra}")
 
 
 if __name__ == "__main__":
