@@ -18,7 +18,9 @@ CUDA events recorded by the library around each of its launches during the timed
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
 `--impl reference` times the CPU restatement of the reference's own torch path (oracle/) on the
-host cores on a bounded row sample of the same workload.
+host cores on a bounded row sample of the same workload.  `--impl reference_cuda` (an extra arm, not
+part of the default run) times the reference's own CUDA operators on the GPU where
+oracle/build_ref_cuda.py has built them.
 """
 import argparse
 import ctypes
@@ -238,12 +240,121 @@ def run_sharded_sparse(args):
         dist.destroy_process_group()
 
 
+def run_reference_cuda(args):
+    """The reference's own CUDA kernels (its default training path: the v4 operators) on this GPU,
+    built from the reference's sources by oracle/build_ref_cuda.py.  The step is the reference module's
+    own sequence -- `weight.T.contiguous()`, `fullyconnected`, bias add
+    (mamtorch/nn/v4/fullyconnected.py:141-199), `fullyconnected_backward` through the registered
+    autograd formula (mamtorch/kernel/v4/fullyconnected.py:24-40), `update_selection_count`
+    (mamtorch/nn/v4/fullyconnected.py:114-131) -- on the same workload as the default arm.  This
+    process never imports mamtorch_b200 (both define the mamtorch_kernel_v4 operator namespace)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    so = os.path.join(ROOT, "oracle", "_ref", "mamtorch_kernel_v4.so")
+    if not os.path.exists(so):
+        print(json.dumps({"impl": "reference_cuda", "unavailable": "oracle/_ref/mamtorch_kernel_v4.so not built "
+                          "(python oracle/build_ref_cuda.py --reference DIR)"}), flush=True)
+        return
+    import torch
+
+    if not torch.cuda.is_available():
+        print(json.dumps({"impl": "reference_cuda", "unavailable": "no CUDA device"}), flush=True)
+        return
+    torch.ops.load_library(so)
+    ops = torch.ops.mamtorch_kernel_v4
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    g = torch.Generator().manual_seed(0)
+    w1 = (torch.randn(D_FF, D_MODEL, generator=g) * D_MODEL ** -0.5).to(dev)
+    w2 = (torch.randn(D_MODEL, D_FF, generator=g) * D_FF ** -0.5).to(dev)
+    b1, b2 = torch.zeros(D_FF, device=dev), torch.zeros(D_MODEL, device=dev)
+    gd = torch.Generator().manual_seed(100)
+    x = torch.randn(M_TOKENS, D_MODEL, generator=gd).to(dev)
+    gy = torch.randn(M_TOKENS, D_MODEL, generator=gd).to(dev)
+    counts = [torch.zeros(D_FF, D_MODEL, dtype=torch.int32, device=dev),
+              torch.zeros(D_MODEL, D_FF, dtype=torch.int32, device=dev)]
+    parts = {"forward": 0.0, "backward": 0.0, "selection_count": 0.0}
+
+    def ev():
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        return e
+
+    def layer_forward(inp, weight, bias):
+        w = weight.T.contiguous()
+        c, amax, amin = ops.fullyconnected(inp, w)
+        c += bias.view(1, -1)
+        return c, amax, amin, w
+
+    def layer_backward(inp, w, grad, amax, amin):
+        a_grad, b_grad = ops.fullyconnected_backward(inp, w, grad.contiguous(), amax, amin)
+        return a_grad, b_grad.T, grad.sum(0)      # weight gradient through the transpose, bias gradient
+
+    def count(cnt, amax, amin):
+        rows, cols = amax.shape
+        col = torch.arange(cols).repeat(rows).to(dev)
+        cnt[col, amax.flatten().long()] += 1
+        col = torch.arange(cols).repeat(rows).to(dev)
+        cnt[col, amin.flatten().long()] += 1
+
+    def step(record):
+        t0 = ev()
+        h, i1, j1, w1t = layer_forward(x, w1, b1)
+        y, i2, j2, w2t = layer_forward(h, w2, b2)
+        t1 = ev()
+        dh, dw2, db2 = layer_backward(h, w2t, gy, i2, j2)
+        dx, dw1, db1 = layer_backward(x, w1t, dh, i1, j1)
+        t2 = ev()
+        count(counts[0], i1, j1)
+        count(counts[1], i2, j2)
+        t3 = ev()
+        if record:
+            torch.cuda.synchronize()
+            parts["forward"] += t0.elapsed_time(t1)
+            parts["backward"] += t1.elapsed_time(t2)
+            parts["selection_count"] += t2.elapsed_time(t3)
+        return y
+
+    for _ in range(max(args.warmup, 1)):
+        step(False)
+    torch.cuda.synchronize()
+    # sanity of the build: the index-packing operator against the reference's own exact values-only operator
+    w1t = w1.T.contiguous()
+    approx_gap = float((ops.fullyconnected(x, w1t)[0] - ops.fullyconnected_fast(x, w1t)).abs().max())
+    f0 = ev()
+    for _ in range(args.steps):
+        ops.fullyconnected_fast(x, w1t)
+    f1 = ev()
+    t0 = ev()
+    for _ in range(args.steps):
+        step(True)
+    t1 = ev()
+    torch.cuda.synchronize()
+    fast_ms = f0.elapsed_time(f1) / args.steps
+    ms = t0.elapsed_time(t1) / args.steps
+    value = UNITS_PER_STEP / (ms * 1e-3) / 1e9
+    kernels_ms = (parts["forward"] + parts["backward"]) / args.steps
+    line = {"impl": "reference_cuda", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD,
+                       "note": "the reference's v4 CUDA operators (its default training path: indices are "
+                               "approximate by design) compiled for sm_100 and called in the reference module's "
+                               "own sequence; inputs resident in HBM"},
+            "ms_per_step_parts": {k: v / args.steps for k, v in parts.items()},
+            "value_without_selection_count": UNITS_PER_STEP / (kernels_ms * 1e-3) / 1e9,
+            "fullyconnected_fast_layer1_ms": fast_ms,
+            "fullyconnected_vs_fullyconnected_fast_max_abs_diff": approx_gap}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference", "reference_cuda"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--fwd-variant", type=int, default=-1, help="tile configuration of the index-producing forward")
     ap.add_argument("--workload", default="vit_mlp", choices=["vit_mlp", "sharded_sparse"],
@@ -255,6 +366,8 @@ def main():
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.impl == "reference":
         return run_reference(args)
+    if args.impl == "reference_cuda":
+        return run_reference_cuda(args)
 
     import torch
     import torch.distributed as dist
