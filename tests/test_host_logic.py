@@ -104,3 +104,33 @@ def test_newer_entry_points_reject_bad_arguments_without_a_device():
     assert L.mam_im2col_f32(one, null, 1, 1, 4, 4, 3, 3, 1, 1, 0, 0, null) == 1
     assert L.mam_col2im_f32(one, one, 1, 1, 4, 4, 3, 3, 0, 1, 0, 0, null) == 1                 # zero stride
     assert L.mam_bwd_count_ex_f32(one, one, 1, one, one, one, one, 7, one, null, null, 1.0, 4, 4, 4, null) == 1
+
+
+def test_spmm_workspace_query_steers_small_and_very_sparse_products_to_the_row_kernel():
+    L = _lib.lib()
+    assert L.mam_spmm_csr_workspace_bytes(4096, 4096, 4096, 4096 * 410) > 0      # ~10 % dense, 6.9e9 multiply-adds
+    assert L.mam_spmm_csr_workspace_bytes(4096, 4096, 4096, 4096 * 40) == 0       # ~1 % dense: too few per stage
+    assert L.mam_spmm_csr_workspace_bytes(1024, 1024, 1024, 1024 * 102) == 0      # too little work
+    assert L.mam_spmm_csr_workspace_bytes(4096, 4096, 62, 4096 * 410) == 0        # columns not a multiple of 4
+
+
+def test_reference_cuda_arm_reports_unavailable_without_a_device(tmp_path):
+    import json
+    import os
+    import subprocess
+    import sys
+
+    if torch.cuda.is_available():
+        pytest.skip("covers the machine without a GPU")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference_cuda", "--steps", "1"],
+                         capture_output=True, text=True, timeout=300, cwd=str(tmp_path))
+    assert out.returncode == 0
+    line = json.loads(out.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference_cuda" and "unavailable" in line
+
+
+def test_reference_cuda_build_is_a_no_op_without_a_checkout(tmp_path):
+    from oracle import build_ref_cuda
+
+    assert build_ref_cuda.build(str(tmp_path)) == []
