@@ -172,6 +172,28 @@ int mam_conv_bwd_f32(const float* x, const float* w, const float* grad,
                      int64_t B, int64_t C, int64_t H, int64_t W,
                      int kH, int kW, int sh, int sw, int ph, int pw, int64_t N, void* stream);
 
+/* Forward of the MAM convolution WITHOUT materialised patch rows: the tiled kernels fetch every 32-channel
+ * chunk of the patch rows from the channels-last input x_nhwc[B,H,W,C] by im2col-mode TMA
+ * (cp.async.bulk.tensor.4d...im2col: the copy engine walks the output pixels, applies stride, padding and
+ * the filter tap, and zero-fills outside the image).  w_taps is the weight as [N][(kw*kH + kh)*C + c], i.e.
+ * weight.permute(0, 3, 2, 1) made contiguous: channels fastest, then kh, then kw -- the reduction order of the
+ * reference's convolution text (k = c + C*(kh + kH*kw), mamtorch/kernel/backup/mamconv2d_forward.txt:128).
+ * y / argmax / argmin are [B*Ho*Wo, N] (both index pointers NULL: values only); bias, dense, blend, alpha,
+ * beta as in mam_fwd_f32.  Indices are RETURNED in the numbering k = (c*kH + kh)*kW + kw of
+ * weight.view(N, -1), the one mam_conv_bwd_f32 and mam_col2im_f32 use; among equal products the one that
+ * comes first in the reduction order above is chosen (with mam_im2col_f32 + mam_fwd_f32 it is the lowest k).
+ * MAM_ERR_UNSUPPORTED where the copy engine cannot express the problem -- C % 32 != 0, padding > 127,
+ * kernel extent > 128, stride > 8, pointers not 16-byte aligned, an input below 128 KiB, or a device
+ * without the driver entry point: mam_conv_fwd_applies() answers that (pointer alignment apart) without a
+ * device, and callers then take the patch-row route.  Stands in for mamconv2d_forward of the reference's
+ * text backups (mamtorch/kernel/backup/mamconv2d_forward.txt:25-175) and the permutes around it
+ * (mamtorch/kernel/backup/mamconv2d.txt:70-100). */
+int mam_conv_fwd_applies(int64_t B, int64_t C, int64_t H, int64_t W, int kH, int kW, int sh, int sw, int ph, int pw);
+int mam_conv_fwd_f32(const float* x_nhwc, const float* w_taps, const float* bias, const float* dense, int blend,
+                     float alpha, float beta, float* y, int32_t* argmax, int32_t* argmin,
+                     int64_t B, int64_t C, int64_t H, int64_t W,
+                     int kH, int kW, int sh, int sw, int ph, int pw, int64_t N, void* stream);
+
 /* Selection hits: hit_max[n,k] += #rows m with argmax[m,n]==k, hit_min likewise ([N,K] int32,
  * accumulated into, so zero them first for per-call counts).  The device-side form of the
  * bookkeeping in FullyConnected.update_selection_count (mamtorch/nn/v4/fullyconnected.py:114-131). */

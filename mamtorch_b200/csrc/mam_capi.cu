@@ -123,11 +123,51 @@ int encode_2d_plain(CUtensorMap* tm, const float* base, long long inner, long lo
     return MAM_OK;
 }
 
+typedef CUresult (*EncodeIm2colFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const int*, const int*, cuuint32_t, cuuint32_t,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeIm2colFn g_encode_im2col = nullptr;
+
+// The convolution input the patch rows are read from: channels-last [B][H][W][C] floats.
+struct ConvSrc {
+    const float* x_nhwc;
+    ConvGeom g;
+};
+
+// Im2col-mode map over the channels-last input: boxes of `pixels` consecutive output pixels x 32
+// channels.  The pixel box is the set of base pixels (top-left patch corners): from -pad to
+// extent + pad - (k - 1) exclusive, walked with the convolution stride; the filter tap comes with
+// every load as an offset.  Zero fill outside the image.
+int encode_im2col_rows(CUtensorMap* tm, const ConvSrc& cv, int pixels, bool swizzle) {
+    if (!g_encode_im2col) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        MAM_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &fn, cudaEnableDefault, &q));
+        if (q != cudaDriverEntryPointSuccess || !fn) return cuda_fail(cudaErrorNotSupported);
+        g_encode_im2col = reinterpret_cast<EncodeIm2colFn>(fn);
+    }
+    const ConvGeom& g = cv.g;
+    cuuint64_t gdim[4] = {(cuuint64_t)g.C, (cuuint64_t)g.W, (cuuint64_t)g.H, (cuuint64_t)g.B};
+    cuuint64_t gstr[3] = {(cuuint64_t)g.C * 4, (cuuint64_t)g.W * g.C * 4, (cuuint64_t)g.H * g.W * g.C * 4};
+    int lower[2] = {-g.pw, -g.ph};
+    int upper[2] = {g.pw - (g.kW - 1), g.ph - (g.kH - 1)};
+    cuuint32_t estr[4] = {1, (cuuint32_t)g.sw, (cuuint32_t)g.sh, 1};
+    CUresult r = g_encode_im2col(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(cv.x_nhwc), gdim, gstr,
+                                 lower, upper, (cuuint32_t)FWD_BK, (cuuint32_t)pixels, estr,
+                                 CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                 swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return cuda_fail(cudaErrorInvalidValue);
+    return MAM_OK;
+}
+
 template <class Cfg>
-int launch_tiled(const float* a, const float* w, const FwdParams& prm, const DevInfo& d, cudaStream_t st) {
+int launch_tiled(const float* a, const float* w, const FwdParams& prm, const DevInfo& d, cudaStream_t st,
+                 const ConvSrc* cv = nullptr) {
     if (Cfg::SMEM_BYTES > d.max_smem) return MAM_ERR_UNSUPPORTED;
     CUtensorMap tmA, tmW;
-    int s = encode_rows_k(&tmA, a, prm.M, prm.K, Cfg::BM);
+    int s = cv ? encode_im2col_rows(&tmA, *cv, Cfg::BM, true) : encode_rows_k(&tmA, a, prm.M, prm.K, Cfg::BM);
     if (s != MAM_OK) return s;
     s = encode_rows_k(&tmW, w, prm.N, prm.K, Cfg::BN);
     if (s != MAM_OK) return s;
@@ -190,6 +230,103 @@ int launch_csr(const float* a, const int64_t* crow, const int64_t* col, const fl
     mam_csr_fwd_kernel<R><<<(unsigned)grid, CSR_WARPS * 32, smem, cs>>>(
         a, reinterpret_cast<const long long*>(crow), reinterpret_cast<const long long*>(col), val, bias, y, argmax,
         argmin, M, K, N);
+    MAM_CUDA(cudaGetLastError());
+    return MAM_OK;
+}
+
+// Tile configuration of the tiled forward for an M x N problem.
+int auto_variant(bool want_idx, int64_t M, int64_t N, const DevInfo& d) {
+    if (want_idx) return 1;  // 4x8 outputs per thread, 64x128 tile
+    // Candidates differ in speed per unit (measured, units/clk/SM) and in how well their tile
+    // count fills whole waves of SMs; pick the best product of the two.
+    struct Cand { int variant; long long bm, bn; double rate; };
+    const Cand cands[3] = {{2, 128, 128, 42.9}, {3, 96, 128, 40.0}, {6, 64, 128, 39.3}};
+    double best = -1.0;
+    int variant = 2;
+    for (const Cand& c : cands) {
+        const long long tiles = ((M + c.bm - 1) / c.bm) * ((N + c.bn - 1) / c.bn);
+        const long long waves = (tiles + d.sms - 1) / d.sms;
+        // work actually executed includes the padding of edge tiles
+        const double useful = (double)M * (double)N / ((double)waves * d.sms * c.bm * c.bn);
+        if (useful * c.rate > best) {
+            best = useful * c.rate;
+            variant = c.variant;
+        }
+    }
+    return variant;
+}
+
+// What the im2col-mode loads can express: whole 32-channel chunks, corners and tap offsets inside the
+// instruction's fields ([-128, 127] and [0, 255] for two spatial dimensions), strides up to 8, and an
+// input of at least 128 KiB (smaller im2col maps are not encoded reliably by current drivers).
+bool conv_implicit_applies(const ConvGeom& g, const float* x_nhwc) {
+    if (g.C % 32 != 0 || !aligned16(x_nhwc)) return false;
+    if (g.pw > 127 || g.ph > 127 || g.kW > 128 || g.kH > 128 || g.sw > 8 || g.sh > 8) return false;
+    if (g.pw - (g.kW - 1) < -128 || g.ph - (g.kH - 1) < -128) return false;
+    if ((long long)g.B * g.H * g.W * g.C * 4 < 131072) return false;
+    if ((long long)g.C * g.kH * g.kW / FWD_BK >= 65535) return false;
+    return true;
+}
+
+// The tiled forward (and, with indices, the resolver behind it) on K-contiguous operands a[M,K] (or,
+// with `cv`, patch rows read from a channels-last convolution input) and w[N,K].
+int run_tiled(const float* a, const float* w, float* y, int32_t* argmax, int32_t* argmin, int64_t M, int64_t K,
+              int64_t N, const EpilogueArgs& ep, int variant, const DevInfo& d, cudaStream_t cs, const ConvSrc* cv) {
+    const bool want_idx = argmax != nullptr;
+    int st = MAM_OK;
+    int* flag = nullptr;
+    MAM_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&flag), g_wait_gave_up));
+    FwdParams prm{y, argmax, argmin, M, K, N, ep, 1.0f, flag, Im2colRows{}};
+    if (cv) {
+        const ConvGeom& g = cv->g;
+        prm.conv = Im2colRows{g.C / 32, g.C, g.kH, g.kW, g.Ho, g.Wo, g.sh, g.sw, g.ph, g.pw};
+    }
+    if (!want_idx) {
+        switch (variant) {
+            case 0: st = launch_tiled<ValCfg0>(a, w, prm, d, cs, cv); break;
+            case 1: st = launch_tiled<ValCfg1>(a, w, prm, d, cs, cv); break;
+            case 2: st = launch_tiled<ValCfg2>(a, w, prm, d, cs, cv); break;
+            case 3: st = launch_tiled<ValCfg3>(a, w, prm, d, cs, cv); break;
+            case 4: st = launch_tiled<ValCfg4>(a, w, prm, d, cs, cv); break;
+            case 5: st = launch_tiled<ValCfg5>(a, w, prm, d, cs, cv); break;
+            case 6: st = launch_tiled<ValCfg6>(a, w, prm, d, cs, cv); break;
+            default: st = launch_tiled<ValCfg7>(a, w, prm, d, cs, cv); break;
+        }
+        return st;
+    }
+    switch (variant) {
+        case 0: st = launch_tiled<IdxCfg0>(a, w, prm, d, cs, cv); break;
+        case 1: st = launch_tiled<IdxCfg1>(a, w, prm, d, cs, cv); break;
+        case 2: st = launch_tiled<IdxCfg2>(a, w, prm, d, cs, cv); break;
+        case 3: st = launch_tiled<IdxCfg3>(a, w, prm, d, cs, cv); break;
+        case 4: st = launch_tiled<IdxCfg4>(a, w, prm, d, cs, cv); break;
+        case 5: st = launch_tiled<IdxCfg5>(a, w, prm, d, cs, cv); break;
+        case 6: st = launch_tiled<IdxCfg6>(a, w, prm, d, cs, cv); break;
+        default: st = launch_tiled<IdxCfg7>(a, w, prm, d, cs, cv); break;
+    }
+    if (st != MAM_OK) return st;
+    const int nkc = (int)((K + FWD_BK - 1) / FWD_BK);
+    if (cv && nkc > ResolveCfg::NK_MAX) return MAM_ERR_UNSUPPORTED;
+    if ((nkc <= ResolveCfg::NK_MAX && g_resolve_simple == 0) || cv) {
+        CUtensorMap tmA, tmW;
+        st = cv ? encode_im2col_rows(&tmA, *cv, ResolveCfg::RM, false) : encode_rows_k(&tmA, a, M, K, ResolveCfg::RM, false);
+        if (st != MAM_OK) return st;
+        st = encode_rows_k(&tmW, w, N, K, ResolveCfg::RN, false);
+        if (st != MAM_OK) return st;
+        const long long tiles = ((M + ResolveCfg::RM - 1) / ResolveCfg::RM) * ((N + ResolveCfg::RN - 1) / ResolveCfg::RN);
+        if (tiles > 2147483647LL) return MAM_ERR_UNSUPPORTED;
+        MAM_CUDA(cudaFuncSetAttribute(mam_resolve_tiled_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      ResolveCfg::SMEM_BYTES));
+        TimedLaunch t(MAM_KERNEL_FWD_RESOLVE, cs);
+        mam_resolve_tiled_kernel<<<(unsigned)tiles, ResolveCfg::THREADS, ResolveCfg::SMEM_BYTES, cs>>>(
+            tmA, tmW, argmax, argmin, M, K, N, flag, prm.conv);
+    } else {
+        const long long total = M * N;
+        const long long blocks = (total + 255) / 256;
+        if (blocks > 2147483647LL) return MAM_ERR_UNSUPPORTED;
+        TimedLaunch t(MAM_KERNEL_FWD_RESOLVE, cs);
+        mam_resolve_kernel<<<(unsigned)blocks, 256, 0, cs>>>(a, w, argmax, argmin, M, K, N);
+    }
     MAM_CUDA(cudaGetLastError());
     return MAM_OK;
 }
@@ -335,24 +472,8 @@ int mam_fwd_f32(const float* a, const float* b, int b_layout, const float* bias,
     if (variant == -1) {
         if (!(tma_ok && M * N >= 4096)) {
             variant = -2;
-        } else if (want_idx) {
-            variant = 1;  // 4x8 outputs per thread, 64x128 tile
         } else {
-            // Candidates differ in speed per unit (measured, units/clk/SM) and in how well their tile
-            // count fills whole waves of SMs; pick the best product of the two.
-            struct Cand { int variant; long long bm, bn; double rate; };
-            const Cand cands[3] = {{2, 128, 128, 42.9}, {3, 96, 128, 40.0}, {6, 64, 128, 39.3}};
-            double best = -1.0;
-            for (const Cand& c : cands) {
-                const long long tiles = ((M + c.bm - 1) / c.bm) * ((N + c.bn - 1) / c.bn);
-                const long long waves = (tiles + d->sms - 1) / d->sms;
-                // work actually executed includes the padding of edge tiles
-                const double useful = (double)M * (double)N / ((double)waves * d->sms * c.bm * c.bn);
-                if (useful * c.rate > best) {
-                    best = useful * c.rate;
-                    variant = c.variant;
-                }
-            }
+            variant = auto_variant(want_idx, M, N, *d);
         }
     }
     if (variant >= 0 && !tma_ok) variant = -2;
@@ -379,56 +500,7 @@ int mam_fwd_f32(const float* a, const float* b, int b_layout, const float* bias,
         if (st != MAM_OK) return st;
         w = static_cast<const float*>(workspace);
     }
-    int* flag = nullptr;
-    MAM_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&flag), g_wait_gave_up));
-    FwdParams prm{y, argmax, argmin, M, K, N, ep, 1.0f, flag};
-    if (!want_idx) {
-        switch (variant) {
-            case 0: st = launch_tiled<ValCfg0>(a, w, prm, *d, cs); break;
-            case 1: st = launch_tiled<ValCfg1>(a, w, prm, *d, cs); break;
-            case 2: st = launch_tiled<ValCfg2>(a, w, prm, *d, cs); break;
-            case 3: st = launch_tiled<ValCfg3>(a, w, prm, *d, cs); break;
-            case 4: st = launch_tiled<ValCfg4>(a, w, prm, *d, cs); break;
-            case 5: st = launch_tiled<ValCfg5>(a, w, prm, *d, cs); break;
-            case 6: st = launch_tiled<ValCfg6>(a, w, prm, *d, cs); break;
-            default: st = launch_tiled<ValCfg7>(a, w, prm, *d, cs); break;
-        }
-        return st;
-    }
-    switch (variant) {
-        case 0: st = launch_tiled<IdxCfg0>(a, w, prm, *d, cs); break;
-        case 1: st = launch_tiled<IdxCfg1>(a, w, prm, *d, cs); break;
-        case 2: st = launch_tiled<IdxCfg2>(a, w, prm, *d, cs); break;
-        case 3: st = launch_tiled<IdxCfg3>(a, w, prm, *d, cs); break;
-        case 4: st = launch_tiled<IdxCfg4>(a, w, prm, *d, cs); break;
-        case 5: st = launch_tiled<IdxCfg5>(a, w, prm, *d, cs); break;
-        case 6: st = launch_tiled<IdxCfg6>(a, w, prm, *d, cs); break;
-        default: st = launch_tiled<IdxCfg7>(a, w, prm, *d, cs); break;
-    }
-    if (st != MAM_OK) return st;
-    const int nkc = (int)((K + FWD_BK - 1) / FWD_BK);
-    if (nkc <= ResolveCfg::NK_MAX && g_resolve_simple == 0) {
-        CUtensorMap tmA, tmW;
-        st = encode_rows_k(&tmA, a, M, K, ResolveCfg::RM, false);
-        if (st != MAM_OK) return st;
-        st = encode_rows_k(&tmW, w, N, K, ResolveCfg::RN, false);
-        if (st != MAM_OK) return st;
-        const long long tiles = ((M + ResolveCfg::RM - 1) / ResolveCfg::RM) * ((N + ResolveCfg::RN - 1) / ResolveCfg::RN);
-        if (tiles > 2147483647LL) return MAM_ERR_UNSUPPORTED;
-        MAM_CUDA(cudaFuncSetAttribute(mam_resolve_tiled_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      ResolveCfg::SMEM_BYTES));
-        TimedLaunch t(MAM_KERNEL_FWD_RESOLVE, cs);
-        mam_resolve_tiled_kernel<<<(unsigned)tiles, ResolveCfg::THREADS, ResolveCfg::SMEM_BYTES, cs>>>(
-            tmA, tmW, argmax, argmin, M, K, N, flag);
-    } else {
-        const long long total = M * N;
-        const long long blocks = (total + 255) / 256;
-        if (blocks > 2147483647LL) return MAM_ERR_UNSUPPORTED;
-        TimedLaunch t(MAM_KERNEL_FWD_RESOLVE, cs);
-        mam_resolve_kernel<<<(unsigned)blocks, 256, 0, cs>>>(a, w, argmax, argmin, M, K, N);
-    }
-    MAM_CUDA(cudaGetLastError());
-    return MAM_OK;
+    return run_tiled(a, w, y, argmax, argmin, M, K, N, ep, variant, *d, cs, nullptr);
 }
 
 int mam_fwd_kn_static_f32(const float* a, const float* b, float* y, int32_t* argmax, int32_t* argmin, int64_t M,
@@ -568,6 +640,34 @@ int mam_conv_bwd_f32(const float* x, const float* w, const float* grad, const in
     }
     MAM_CUDA(cudaGetLastError());
     return MAM_OK;
+}
+
+int mam_conv_fwd_applies(int64_t B, int64_t C, int64_t H, int64_t W, int kH, int kW, int sh, int sw, int ph, int pw) {
+    ConvGeom g;
+    if (conv_geom(&g, B, C, H, W, kH, kW, sh, sw, ph, pw) != MAM_OK) return 0;
+    return conv_implicit_applies(g, nullptr) ? 1 : 0;
+}
+
+int mam_conv_fwd_f32(const float* x_nhwc, const float* w_taps, const float* bias, const float* dense, int blend,
+                     float alpha, float beta, float* y, int32_t* argmax, int32_t* argmin, int64_t B, int64_t C,
+                     int64_t H, int64_t W, int kH, int kW, int sh, int sw, int ph, int pw, int64_t N, void* stream) {
+    if (bad_ptr(x_nhwc) || bad_ptr(w_taps) || bad_ptr(y) || N <= 0) return MAM_ERR_INVALID_ARGUMENT;
+    if ((argmax == nullptr) != (argmin == nullptr)) return MAM_ERR_INVALID_ARGUMENT;
+    ConvGeom g;
+    int st = conv_geom(&g, B, C, H, W, kH, kW, sh, sw, ph, pw);
+    if (st != MAM_OK) return st;
+    if (!conv_implicit_applies(g, x_nhwc) || !aligned16(w_taps)) return MAM_ERR_UNSUPPORTED;
+    const long long M = (long long)g.B * g.Ho * g.Wo, K = (long long)g.C * g.kH * g.kW;
+    if (M >= (1LL << 31) || N >= (1LL << 31)) return MAM_ERR_UNSUPPORTED;
+    const DevInfo* d = nullptr;
+    st = device_info(&d);
+    if (st != MAM_OK) return st;
+    const bool want_idx = argmax != nullptr;
+    int variant = g_variant[want_idx ? 1 : 0];
+    if (variant < 0) variant = auto_variant(want_idx, M, N, *d);
+    ConvSrc cv{x_nhwc, g};
+    EpilogueArgs ep{bias, dense, alpha, beta, blend};
+    return run_tiled(nullptr, w_taps, y, argmax, argmin, M, K, N, ep, variant, *d, (cudaStream_t)stream, &cv);
 }
 
 int mam_im2col_f32(const float* x, float* rows, int64_t B, int64_t C, int64_t H, int64_t W, int kH, int kW, int sh,

@@ -58,6 +58,28 @@ struct FwdCfg {
     static_assert(STAGES >= 3, "need one stage of slack so the issuing warp never waits on its peers");
 };
 
+// Patch rows of a convolution read straight from the channels-last input by im2col-mode TMA instead
+// of from a materialised [M, K] matrix.  Row m is output pixel (n, ho, wo), m = (n*Ho + ho)*Wo + wo;
+// column k' = (kh + kH*kw)*C + c (channels fastest, then kh, then kw: the order of the reference's
+// convolution text, mamtorch/kernel/backup/mamconv2d_forward.txt:128), so a 32-wide chunk is 32
+// channels of one filter tap.  c32 = C / 32 (0: not a convolution).
+struct Im2colRows {
+    int c32, C, kH, kW, Ho, Wo, sh, sw, ph, pw;
+};
+
+// Issues the copy of chunk kc of the rows starting at output pixel m0 (thread-0 helper).
+__device__ __forceinline__ void im2col_chunk_load(void* dst, const void* tmap, uint64_t* bar, const Im2colRows& cv,
+                                                  long long m0, int kc) {
+    const int tap = kc / cv.c32, cc = kc - tap * cv.c32;
+    const int kw = tap / cv.kH, kh = tap - kw * cv.kH;
+    const int hw = cv.Ho * cv.Wo;
+    const int n = (int)(m0 / hw);
+    const int rem = (int)(m0 - (long long)n * hw);
+    const int ho = rem / cv.Wo, wo = rem - ho * cv.Wo;
+    tma_load_im2col_4d(dst, tmap, bar, cc * 32, wo * cv.sw - cv.pw, ho * cv.sh - cv.ph, n, (uint16_t)kw,
+                       (uint16_t)kh);
+}
+
 struct FwdParams {
     float* y;
     int* cid_max;  // TRACK: chunk ids (later resolved in place to exact k)
@@ -66,6 +88,7 @@ struct FwdParams {
     EpilogueArgs ep;
     float one;     // 1.0f kept opaque to the compiler (see merge below)
     int* error;    // set to 1 when a bounded wait gave up
+    Im2colRows conv;  // c32 != 0: tmA is an im2col-mode map of the channels-last convolution input
 };
 
 // compile-time loop: f receives std::integral_constant<int, I>, so I can feed "n" asm operands
@@ -132,7 +155,10 @@ mam_fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         const int tm = (int)(p_tile / ntn), tn = (int)(p_tile % ntn);
         mbar_expect_tx(&full_bar[p_stage], Cfg::STAGE_BYTES);
         unsigned char* sa = smem + p_stage * Cfg::STAGE_BYTES;
-        tma_load_2d(sa, &tmA, &full_bar[p_stage], p_kc * FWD_BK, tm * Cfg::BM);
+        if (prm.conv.c32)
+            im2col_chunk_load(sa, &tmA, &full_bar[p_stage], prm.conv, (long long)tm * Cfg::BM, p_kc);
+        else
+            tma_load_2d(sa, &tmA, &full_bar[p_stage], p_kc * FWD_BK, tm * Cfg::BM);
         tma_load_2d(sa + Cfg::A_BYTES, &tmW, &full_bar[p_stage], p_kc * FWD_BK, tn * Cfg::BN);
         if (++p_stage == STAGES) { p_stage = 0; p_phase ^= 1u; }
         if (++p_kc == nk) { p_kc = 0; p_tile += gridDim.x; }
@@ -341,7 +367,7 @@ struct ResolveCfg {
 __global__ void __launch_bounds__(ResolveCfg::THREADS, 2)
 mam_resolve_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW,
                          int* __restrict__ argmax, int* __restrict__ argmin,
-                         long long M, long long K, long long N, int* error) {
+                         long long M, long long K, long long N, int* error, const Im2colRows conv) {
     using C = ResolveCfg;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(
@@ -377,7 +403,10 @@ mam_resolve_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         if (!mbar_wait_bounded(&empty_bar[p_stage], p_phase ^ 1u)) return false;
         mbar_expect_tx(&full_bar[p_stage], C::STAGE_BYTES);
         unsigned char* sa = smem + p_stage * C::STAGE_BYTES;
-        tma_load_2d(sa, &tmA, &full_bar[p_stage], p_kc * FWD_BK, (int)m0);
+        if (conv.c32)
+            im2col_chunk_load(sa, &tmA, &full_bar[p_stage], conv, m0, p_kc);
+        else
+            tma_load_2d(sa, &tmA, &full_bar[p_stage], p_kc * FWD_BK, (int)m0);
         tma_load_2d(sa + C::A_BYTES, &tmW, &full_bar[p_stage], p_kc * FWD_BK, (int)n0);
         if (++p_stage == C::STAGES) { p_stage = 0; p_phase ^= 1u; }
         ++p_kc;
@@ -468,6 +497,15 @@ mam_resolve_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         const unsigned char* Ws = As + C::A_BYTES;
         const int nq = (kc + 1 < nk) ? FWD_BK / 4 : tail_quads;
         const int t_end = start[kc + 1];
+        // Convolution rows: the chunk is 32 channels of one tap; indices leave in the numbering
+        // k = (c*kH + kh)*kW + kw of weight.view(F, -1), i.e. kout = kout0 + e * kH*kW for element e.
+        int kout0 = kc * FWD_BK, kout_step = 1;
+        if (conv.c32) {
+            const int tap = kc / conv.c32, cc = kc - tap * conv.c32;
+            const int kw = tap / conv.kH, kh = tap - kw * conv.kH;
+            kout_step = conv.kH * conv.kW;
+            kout0 = cc * 32 * kout_step + kh * conv.kW + kw;
+        }
         for (int t = start[kc] + tid; t < t_end; t += C::THREADS) {
             const unsigned code = tasks[t];
             const int o = (int)(code >> 1);
@@ -513,7 +551,7 @@ mam_resolve_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
             if (p2 == best) e = 2;
             if (p1 == best) e = 1;
             if (p0 == best) e = 0;
-            const int kbest = kc * FWD_BK + bq * 4 + e;
+            const int kbest = kout0 + (bq * 4 + e) * kout_step;
             const long long m = m0 + ra, n = n0 + rw;
             if (code & 1u) argmin[m * N + n] = kbest; else argmax[m * N + n] = kbest;
         }

@@ -91,6 +91,20 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const void* tmap, ui
         "l"(tmap), "r"(smem_u32(bar)), "r"(x), "r"(y)
         : "memory");
 }
+// Im2col-mode load of a 4-d (C, W, H, N) channels-last tensor: `pixels per column` consecutive
+// output pixels starting at base pixel (w, h) of image n, each shifted by the filter tap (off_w,
+// off_h), `channels per pixel` channels from c.  Base pixels advance by the map's traversal strides
+// and wrap from one output row (and image) to the next inside the map's pixel box; pixels outside
+// the image read as zero.  c must keep the 16-byte rule (a multiple of 4 floats).
+__device__ __forceinline__ void tma_load_im2col_4d(void* smem_dst, const void* tmap, uint64_t* bar, int32_t c,
+                                                   int32_t w, int32_t h, int32_t n, uint16_t off_w,
+                                                   uint16_t off_h) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};" ::"r"(smem_u32(smem_dst)),
+        "l"(tmap), "r"(smem_u32(bar)), "r"(c), "r"(w), "r"(h), "r"(n), "h"(off_w), "h"(off_h)
+        : "memory");
+}
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }

@@ -259,6 +259,58 @@ at::Tensor conv_im2col(const at::Tensor& x, int64_t kH, int64_t kW, int64_t sh, 
                  "mam_im2col_f32");
     return rows;
 }
+// Whether conv_forward_implicit can take a convolution of this geometry (no device needed).
+bool conv_implicit_applies(int64_t B, int64_t C, int64_t H, int64_t W, int64_t kH, int64_t kW, int64_t sh, int64_t sw,
+                           int64_t ph, int64_t pw) {
+    return mam_conv_fwd_applies(B, C, H, W, (int)kH, (int)kW, (int)sh, (int)sw, (int)ph, (int)pw) != 0;
+}
+// {y[B*Ho*Wo, N]} or {y, argmax, argmin}: forward straight from the channels-last input x_nhwc[B,H,W,C] with the
+// weight in tap order w_taps[N, kH*kW*C] (weight.permute(0, 3, 2, 1)); indices numbered as weight.view(N, -1)
+std::vector<at::Tensor> conv_forward_implicit(const at::Tensor& x_nhwc, const at::Tensor& w_taps,
+                                              const c10::optional<at::Tensor>& bias,
+                                              const c10::optional<at::Tensor>& dense_t, double alpha, double beta,
+                                              int64_t kH, int64_t kW, int64_t sh, int64_t sw, int64_t ph, int64_t pw,
+                                              bool want_idx) {
+    TORCH_CHECK(x_nhwc.is_cuda() && x_nhwc.scalar_type() == at::kFloat && x_nhwc.dim() == 4 && x_nhwc.is_contiguous(),
+                "x_nhwc must be a contiguous float32 CUDA [B,H,W,C] tensor");
+    check_matrix(w_taps, "w_taps");
+    const int64_t B = x_nhwc.size(0), H = x_nhwc.size(1), W = x_nhwc.size(2), C = x_nhwc.size(3);
+    TORCH_CHECK(H + 2 * ph >= kH && W + 2 * pw >= kW, "kernel larger than the padded input");
+    const int64_t Ho = (H + 2 * ph - kH) / sh + 1, Wo = (W + 2 * pw - kW) / sw + 1;
+    const int64_t M = B * Ho * Wo, K = C * kH * kW, N = w_taps.size(0);
+    TORCH_CHECK(w_taps.size(1) == K, "w_taps must be [N, kH*kW*C]");
+    const float* bias_p = nullptr;
+    const float* dense_p = nullptr;
+    at::Tensor bias_c, dense_c;
+    if (bias.has_value() && bias->defined()) {
+        TORCH_CHECK(bias->is_cuda() && bias->scalar_type() == at::kFloat && bias->numel() == N, "bias must be float32 [N]");
+        bias_c = bias->contiguous();
+        bias_p = bias_c.data_ptr<float>();
+    }
+    if (dense_t.has_value() && dense_t->defined()) {
+        check_matrix(*dense_t, "dense");
+        TORCH_CHECK(dense_t->size(0) == M && dense_t->size(1) == N, "dense must be [B*Ho*Wo, N]");
+        dense_c = *dense_t;
+        dense_p = dense_c.data_ptr<float>();
+    }
+    const bool blend = !(alpha == 1.0 && beta == 0.0);
+    c10::cuda::CUDAGuard guard(x_nhwc.device());
+    auto y = at::empty({M, N}, x_nhwc.options());
+    at::Tensor amax, amin;
+    if (want_idx) {
+        amax = at::empty({M, N}, x_nhwc.options().dtype(at::kInt));
+        amin = at::empty({M, N}, x_nhwc.options().dtype(at::kInt));
+    }
+    auto stream = at::cuda::getCurrentCUDAStream();
+    check_status(mam_conv_fwd_f32(x_nhwc.data_ptr<float>(), w_taps.data_ptr<float>(), bias_p, dense_p, blend ? 1 : 0,
+                                  (float)alpha, (float)beta, y.data_ptr<float>(),
+                                  want_idx ? amax.data_ptr<int32_t>() : nullptr,
+                                  want_idx ? amin.data_ptr<int32_t>() : nullptr, B, C, H, W, (int)kH, (int)kW, (int)sh,
+                                  (int)sw, (int)ph, (int)pw, N, stream.stream()),
+                 "mam_conv_fwd_f32");
+    if (!want_idx) return {y};
+    return {y, amax, amin};
+}
 // dx[B,C,H,W] from the transposed row gradients cols_t[C*kH*kW, B*Ho*Wo]
 at::Tensor conv_col2im(const at::Tensor& cols_t, int64_t B, int64_t C, int64_t H, int64_t W, int64_t kH, int64_t kW,
                        int64_t sh, int64_t sw, int64_t ph, int64_t pw) {
@@ -469,6 +521,8 @@ TORCH_LIBRARY(mamtorch_b200, m) {
     m.def("linear_backward_km(Tensor x, Tensor weight, Tensor grad, Tensor argmax, Tensor argmin, float scale) -> Tensor[]");
     m.def("conv_backward(Tensor x, Tensor weight, Tensor grad, Tensor argmax, Tensor argmin, float scale, int kH, int kW, int sh, int sw, int ph, int pw) -> Tensor[]");
     m.def("conv_im2col(Tensor x, int kH, int kW, int sh, int sw, int ph, int pw) -> Tensor");
+    m.def("conv_forward_implicit(Tensor x_nhwc, Tensor w_taps, Tensor? bias, Tensor? dense, float alpha, float beta, int kH, int kW, int sh, int sw, int ph, int pw, bool need_indices) -> Tensor[]");
+    m.def("conv_implicit_applies(int B, int C, int H, int W, int kH, int kW, int sh, int sw, int ph, int pw) -> bool", &conv_implicit_applies);
     m.def("conv_col2im(Tensor cols_t, int B, int C, int H, int W, int kH, int kW, int sh, int sw, int ph, int pw) -> Tensor");
     m.def("selection_hits(Tensor argmax, Tensor argmin, int K) -> Tensor[]");
     m.def("selection_count_update_(Tensor(a!) count, Tensor hit_max, Tensor hit_min) -> Tensor(a!)");
@@ -484,6 +538,7 @@ TORCH_LIBRARY_IMPL(mamtorch_b200, CUDA, m) {
     m.impl("linear_backward_km", &linear_backward_km);
     m.impl("conv_backward", &conv_backward);
     m.impl("conv_im2col", &conv_im2col);
+    m.impl("conv_forward_implicit", &conv_forward_implicit);
     m.impl("conv_col2im", &conv_col2im);
     m.impl("selection_hits", &selection_hits);
     m.impl("selection_count_update_", &selection_count_update_);

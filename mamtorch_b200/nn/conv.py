@@ -12,6 +12,19 @@ and attributes (weight [F,C,kH,kW], bias, beta schedule, argmax/argmin, selectio
     `to_legacy_index` converts.
 
 Each output pixel is one row of a GEMM-shaped MAM problem: M = B*Ho*Wo, K = C*kH*kW, N = F.
+
+`reduction_order` chooses which of several EQUAL products an index names, and with it the data path:
+
+  "unfold" (default)  the lowest k in the numbering above: patch rows are written once by
+                      `conv_im2col` and the fully-connected kernels run on them;
+  "taps"              the first in the backup's own reduction order (channels fastest, then kh, then
+                      kw).  No patch rows exist: the kernels fetch 32-channel chunks of them from the
+                      channels-last input by im2col-mode TMA (`conv_forward_implicit`).  Needs
+                      C % 32 == 0 (otherwise the same order is produced through permuted patch rows).
+
+Values are identical in both; indices are always NUMBERED k = (c*kH + kh)*kW + kw and differ between
+the two orders only where a maximum or minimum is attained more than once (zero products of padding
+or of ReLU'd inputs).
 """
 from __future__ import annotations
 
@@ -24,7 +37,7 @@ from . import functional as MF
 
 _ops = torch.ops.mamtorch_b200
 
-__all__ = ["MAMConv1d", "MAMConv2d", "mam_conv2d"]
+__all__ = ["MAMConv1d", "MAMConv2d", "mam_conv2d", "tap_order_permutation", "to_legacy_index"]
 
 
 def _pair(v):
@@ -38,17 +51,16 @@ class _MamConv2d(torch.autograd.Function):
     output from the input itself."""
 
     @staticmethod
-    def forward(ctx, x, weight, bias, dense, alpha, beta, stride, padding):
+    def forward(ctx, x, weight, bias, dense, alpha, beta, stride, padding, taps=False):
         B, C, H, W = x.shape
         Fo, _, kH, kW = weight.shape
         (sh, sw), (ph, pw) = stride, padding
         Ho, Wo = (H + 2 * ph - kH) // sh + 1, (W + 2 * pw - kW) // sw + 1
-        rows = _ops.conv_im2col(x, kH, kW, sh, sw, ph, pw)                    # [B*Ho*Wo, C*kH*kW]
         w2d = weight.reshape(Fo, -1).contiguous()
         dflat = None
         if dense is not None:
             dflat = dense.permute(0, 2, 3, 1).reshape(B * Ho * Wo, Fo).contiguous()
-        y, amax, amin = _ops.linear_forward(rows, w2d, bias, dflat, alpha, beta, True)
+        y, amax, amin = _forward_rows(x, weight, w2d, bias, dflat, alpha, beta, (kH, kW, sh, sw, ph, pw), taps, True)
         ctx.save_for_backward(x, w2d, amax, amin)
         ctx.geom = (B, C, H, W, Fo, kH, kW, sh, sw, ph, pw, Ho, Wo)
         ctx.alpha, ctx.beta = alpha, beta
@@ -73,24 +85,58 @@ class _MamConv2d(torch.autograd.Function):
             dbias = g2d.sum(0)
         if ctx.has_dense and ctx.needs_input_grad[3]:
             ddense = gy * ctx.beta
-        return dx, dw, dbias, ddense, None, None, None, None
+        return dx, dw, dbias, ddense, None, None, None, None, None
 
 
-def mam_conv2d(x, weight, bias=None, stride=1, padding=0, dense=None, alpha=1.0, beta=0.0, need_indices=True):
+def tap_order_permutation(in_channels, kH, kW, device=None):
+    """perm[k'] = k: position k' = (kw*kH + kh)*C + c of the backup's reduction order -> the index
+    k = (c*kH + kh)*kW + kw of `weight.view(F, -1)`."""
+    return torch.arange(in_channels * kH * kW, device=device).view(in_channels, kH, kW).permute(2, 1, 0).reshape(-1)
+
+
+def _forward_rows(x, weight, w2d, bias, dflat, alpha, beta, geom, taps, need_indices):
+    """The row-form forward: [y[M,F]] or [y, argmax, argmin] with indices numbered like weight.view(F, -1)."""
+    kH, kW, sh, sw, ph, pw = geom
+    B, C, H, W = x.shape
+    Fo = weight.size(0)
+    if not taps:
+        rows = _ops.conv_im2col(x, kH, kW, sh, sw, ph, pw)                    # [B*Ho*Wo, C*kH*kW]
+        return _ops.linear_forward(rows, w2d, bias, dflat, alpha, beta, need_indices)
+    w_taps = weight.permute(0, 3, 2, 1).reshape(Fo, -1).contiguous()          # [F, (kw, kh, c)]
+    if _ops.conv_implicit_applies(B, C, H, W, kH, kW, sh, sw, ph, pw):
+        x_nhwc = x.permute(0, 2, 3, 1).contiguous()                           # a view if x is channels_last
+        if x_nhwc.data_ptr() % 16 == 0:
+            return _ops.conv_forward_implicit(x_nhwc, w_taps, bias, dflat, alpha, beta, kH, kW, sh, sw, ph, pw,
+                                              need_indices)
+    # same reduction order through explicit patch rows with permuted columns
+    perm = tap_order_permutation(C, kH, kW, x.device)
+    rows = _ops.conv_im2col(x, kH, kW, sh, sw, ph, pw).index_select(1, perm)
+    out = _ops.linear_forward(rows, w_taps, bias, dflat, alpha, beta, need_indices)
+    if need_indices:
+        perm32 = perm.to(torch.int32)
+        out = [out[0], perm32[out[1].long()], perm32[out[2].long()]]
+    return out
+
+
+def mam_conv2d(x, weight, bias=None, stride=1, padding=0, dense=None, alpha=1.0, beta=0.0, need_indices=True,
+               reduction_order="unfold"):
     """x[B,C,H,W], weight[F,C,kH,kW] -> (y[B,F,Ho,Wo], argmax, argmin) with indices into C*kH*kW."""
+    if reduction_order not in ("unfold", "taps"):
+        raise ValueError("reduction_order must be 'unfold' or 'taps'")
+    taps = reduction_order == "taps"
     stride, padding = _pair(stride), _pair(padding)
     wants_grad = torch.is_grad_enabled() and any(
         t is not None and t.requires_grad for t in (x, weight, bias, dense))
     if need_indices or wants_grad:
-        y, amax, amin = _MamConv2d.apply(x, weight, bias, dense, float(alpha), float(beta), stride, padding)
+        y, amax, amin = _MamConv2d.apply(x, weight, bias, dense, float(alpha), float(beta), stride, padding, taps)
         return (y, amax, amin) if need_indices else (y, None, None)
     B, C, H, W = x.shape
     Fo, _, kH, kW = weight.shape
     (sh, sw), (ph, pw) = stride, padding
     Ho, Wo = (H + 2 * ph - kH) // sh + 1, (W + 2 * pw - kW) // sw + 1
-    rows = _ops.conv_im2col(x, kH, kW, sh, sw, ph, pw)
     dflat = None if dense is None else dense.permute(0, 2, 3, 1).reshape(B * Ho * Wo, Fo).contiguous()
-    y, = _ops.linear_forward(rows, weight.reshape(Fo, -1).contiguous(), bias, dflat, float(alpha), float(beta), False)
+    y, = _forward_rows(x, weight, weight.reshape(Fo, -1).contiguous(), bias, dflat, float(alpha), float(beta),
+                       (kH, kW, sh, sw, ph, pw), taps, False)
     return y.view(B, Ho, Wo, Fo).permute(0, 3, 1, 2), None, None
 
 
@@ -156,8 +202,11 @@ class _ConvBase(torch.nn.Module):
 
 class MAMConv2d(_ConvBase):
     def __init__(self, in_channels, out_channels, kernel_size, bias=True, stride=1, padding=0,
-                 padding_mode="zeros", beta=False, beta_decay="linear", beta_epochs=1):
+                 padding_mode="zeros", beta=False, beta_decay="linear", beta_epochs=1, reduction_order="unfold"):
         super().__init__()
+        if reduction_order not in ("unfold", "taps"):
+            raise ValueError("reduction_order must be 'unfold' or 'taps'")
+        self.reduction_order = reduction_order
         self.in_channels, self.out_channels = in_channels, out_channels
         self.kernel_size, self.stride, self.padding, self.padding_mode = kernel_size, stride, padding, padding_mode
         kH, kW = _pair(kernel_size)
@@ -189,7 +238,7 @@ class MAMConv2d(_ConvBase):
             dense = F.conv2d(x, self.weight, stride=(self.hstride, self.wstride), padding=(ph, pw))
         y, self.argmax, self.argmin = mam_conv2d(x, self.weight, self.bias, (self.hstride, self.wstride), (ph, pw),
                                                  dense, 1 - self.beta if blend else 1.0,
-                                                 self.beta if blend else 0.0)
+                                                 self.beta if blend else 0.0, reduction_order=self.reduction_order)
         return y
 
 
@@ -197,8 +246,11 @@ class MAMConv1d(_ConvBase):
     """1-D form (`mamtorch/nn/backup/mamconv1d.txt`): a 2-D convolution with a height of one."""
 
     def __init__(self, in_channels, out_channels, kernel_size, bias=True, stride=1, padding=0,
-                 padding_mode="zeros", beta=False, beta_decay="linear", beta_epochs=1):
+                 padding_mode="zeros", beta=False, beta_decay="linear", beta_epochs=1, reduction_order="unfold"):
         super().__init__()
+        if reduction_order not in ("unfold", "taps"):
+            raise ValueError("reduction_order must be 'unfold' or 'taps'")
+        self.reduction_order = reduction_order
         self.in_channels, self.out_channels = in_channels, out_channels
         self.kernel_size, self.stride, self.padding, self.padding_mode = kernel_size, stride, padding, padding_mode
         self.weight = torch.nn.Parameter(torch.empty(out_channels, in_channels, kernel_size))
@@ -221,7 +273,8 @@ class MAMConv1d(_ConvBase):
         blend = self.beta >= 10e-5
         dense = F.conv1d(x, self.weight, stride=self.stride, padding=p).unsqueeze(2) if blend else None
         y, amax, amin = mam_conv2d(x.unsqueeze(2), self.weight.unsqueeze(2), self.bias, (1, self.stride), (0, p),
-                                   dense, 1 - self.beta if blend else 1.0, self.beta if blend else 0.0)
+                                   dense, 1 - self.beta if blend else 1.0, self.beta if blend else 0.0,
+                                   reduction_order=self.reduction_order)
         self.argmax, self.argmin = amax.squeeze(2), amin.squeeze(2)
         return y.squeeze(2)
 

@@ -45,6 +45,16 @@ def _(x, kH, kW, sh, sw, ph, pw):
     return x.new_empty((B * Ho * Wo, C * kH * kW))
 
 
+@torch.library.register_fake("mamtorch_b200::conv_forward_implicit")
+def _(x_nhwc, w_taps, bias, dense, alpha, beta, kH, kW, sh, sw, ph, pw, need_indices):
+    B, H, W, C = x_nhwc.shape
+    Ho, Wo = (H + 2 * ph - kH) // sh + 1, (W + 2 * pw - kW) // sw + 1
+    y = x_nhwc.new_empty((B * Ho * Wo, w_taps.size(0)))
+    if not need_indices:
+        return [y]
+    return [y, y.new_empty(y.shape, dtype=torch.int32), y.new_empty(y.shape, dtype=torch.int32)]
+
+
 @torch.library.register_fake("mamtorch_b200::conv_col2im")
 def _(cols_t, B, C, H, W, kH, kW, sh, sw, ph, pw):
     return cols_t.new_empty((B, C, H, W))

@@ -124,3 +124,111 @@ def test_strided_padded_conv_module_gradients(cuda):
     assert_grad_close(x.grad.cpu().numpy(), xw.grad.numpy())
     assert_grad_close(conv.weight.grad.cpu().numpy(), ww.grad.numpy())
     assert_grad_close(conv.bias.grad.cpu().numpy(), gy.sum((0, 2, 3)).cpu().numpy())
+
+
+# ---------------------------------------------------------------- forward without patch rows (im2col-mode TMA)
+IMPLICIT_GEOMS = [  # B, C, H, W, kH, kW, sh, sw, ph, pw, N   (C % 32 == 0, input >= 128 KiB)
+    (4, 64, 14, 14, 3, 3, 1, 1, 1, 1, 128),
+    (2, 32, 33, 37, 3, 3, 2, 2, 1, 1, 70),
+    (3, 96, 20, 17, 5, 3, 1, 2, 2, 0, 33),
+    (2, 32, 40, 40, 1, 1, 1, 1, 0, 0, 130),
+    (1, 32, 64, 48, 2, 4, 3, 1, 0, 3, 17),
+    (5, 32, 19, 23, 3, 3, 1, 1, 2, 2, 64),     # padding larger than "same"
+]
+
+
+def _tap_order_oracle(x, w, geom, relu=False):
+    """The oracle on patch rows whose columns are in the order (kw, kh, c) -- channels fastest, then kh, then
+    kw -- with indices mapped back to the numbering of weight.view(N, -1)."""
+    from mamtorch_b200.nn.conv import tap_order_permutation
+
+    B, C, H, W, kH, kW, sh, sw, ph, pw, N = geom
+    rows = mam_oracle.conv2d_as_rows(x.cpu(), (kH, kW), stride=(sh, sw), padding=(ph, pw))
+    perm = tap_order_permutation(C, kH, kW)
+    y, imax, imin = mam_oracle.mam_forward(rows[:, perm], w.cpu().reshape(N, -1)[:, perm].T.contiguous())
+    return y, perm[imax], perm[imin]
+
+
+@pytest.mark.parametrize("relu", [False, True])
+@pytest.mark.parametrize("geom", IMPLICIT_GEOMS)
+def test_implicit_conv_forward_matches_the_oracle_in_tap_order(geom, relu, cuda):
+    B, C, H, W, kH, kW, sh, sw, ph, pw, N = geom
+    L = _lib.lib()
+    assert L.mam_conv_fwd_applies(B, C, H, W, kH, kW, sh, sw, ph, pw) == 1
+    g = torch.Generator().manual_seed(sum(geom))
+    x = torch.randn(B, C, H, W, generator=g)
+    if relu:
+        x = torch.relu(x)           # half of the activations exactly zero: extremes tie at zero all the time
+    w = torch.randn(N, C, kH, kW, generator=g) * (C * kH * kW) ** -0.5
+    if relu:
+        w = w.abs()                 # every product >= 0, so every minimum is a tie among the zeros
+    Ho, Wo = (H + 2 * ph - kH) // sh + 1, (W + 2 * pw - kW) // sw + 1
+    M = B * Ho * Wo
+    x_nhwc = x.permute(0, 2, 3, 1).contiguous().to(cuda)
+    w_taps = w.permute(0, 3, 2, 1).reshape(N, -1).contiguous().to(cuda)
+    y = torch.empty(M, N, device=cuda)
+    imax = torch.empty(M, N, dtype=torch.int32, device=cuda)
+    imin = torch.empty_like(imax)
+    _lib.check(L.mam_conv_fwd_f32(_p(x_nhwc), _p(w_taps), None, None, 0, 1.0, 0.0, _p(y), _p(imax), _p(imin), B, C, H, W,
+                                  kH, kW, sh, sw, ph, pw, N, capi._stream()), "mam_conv_fwd_f32")
+    torch.cuda.synchronize()
+    _lib.check(L.mam_check_device_flag(), "device wait flag")
+    y_ref, imax_ref, imin_ref = _tap_order_oracle(x, w, geom)
+    assert torch.equal(y.cpu(), y_ref)
+    assert torch.equal(imax.cpu().long(), imax_ref) and torch.equal(imin.cpu().long(), imin_ref)
+    # values only: same kernel family without tracking
+    y2 = torch.empty_like(y)
+    _lib.check(L.mam_conv_fwd_f32(_p(x_nhwc), _p(w_taps), None, None, 0, 1.0, 0.0, _p(y2), None, None, B, C, H, W,
+                                  kH, kW, sh, sw, ph, pw, N, capi._stream()), "mam_conv_fwd_f32")
+    assert torch.equal(y2, y)
+
+
+def test_implicit_conv_forward_rejects_what_the_copy_engine_cannot_express(cuda):
+    L = _lib.lib()
+    assert L.mam_conv_fwd_applies(4, 48, 14, 14, 3, 3, 1, 1, 1, 1) == 0        # channels not a multiple of 32
+    assert L.mam_conv_fwd_applies(1, 32, 8, 8, 3, 3, 1, 1, 1, 1) == 0          # input below 128 KiB
+    assert L.mam_conv_fwd_applies(4, 64, 14, 14, 3, 3, 9, 1, 1, 1) == 0        # stride beyond the traversal field
+    assert L.mam_conv_fwd_applies(4, 64, 14, 14, 3, 3, 1, 1, 1, 1) == 1
+    x = torch.zeros(4, 14, 14, 48, device=cuda)
+    w = torch.zeros(8, 9 * 48, device=cuda)
+    y = torch.empty(4 * 14 * 14, 8, device=cuda)
+    assert L.mam_conv_fwd_f32(_p(x), _p(w), None, None, 0, 1.0, 0.0, _p(y), None, None, 4, 48, 14, 14, 3, 3, 1, 1, 1, 1,
+                              8, capi._stream()) == 2
+    assert L.mam_conv_fwd_f32(None, _p(w), None, None, 0, 1.0, 0.0, _p(y), None, None, 4, 64, 14, 14, 3, 3, 1, 1, 1, 1,
+                              8, capi._stream()) == 1
+
+
+@pytest.mark.parametrize("channels", [64, 5])      # 64: im2col-mode TMA; 5: same order through permuted patch rows
+def test_conv_module_in_tap_order_matches_the_patch_row_module(channels, cuda):
+    import mamtorch_b200 as mamtorch
+
+    torch.manual_seed(21)
+    a = mamtorch.nn.MAMConv2d(channels, 24, 3, stride=1, padding=1).to(cuda)
+    b = mamtorch.nn.MAMConv2d(channels, 24, 3, stride=1, padding=1, reduction_order="taps").to(cuda)
+    b.load_state_dict(a.state_dict())
+    x = torch.randn(4, channels, 18, 15, generator=torch.Generator().manual_seed(22)).to(cuda)
+    xa, xb = x.clone().requires_grad_(), x.clone().requires_grad_()
+    ya, yb = a(xa), b(xb)
+    assert torch.equal(ya, yb)
+    # continuous random data: no two products are equal, so both orders name the same positions
+    assert torch.equal(a.argmax, b.argmax) and torch.equal(a.argmin, b.argmin)
+    gy = torch.randn(ya.shape, generator=torch.Generator().manual_seed(23)).to(cuda)
+    ya.backward(gy)
+    yb.backward(gy)
+    assert_grad_close(xb.grad.cpu().numpy(), xa.grad.cpu().numpy())
+    assert_grad_close(b.weight.grad.cpu().numpy(), a.weight.grad.cpu().numpy())
+    # values-only path (no autograd, no indices asked for)
+    with torch.no_grad():
+        from mamtorch_b200.nn.conv import mam_conv2d
+        y3, _, _ = mam_conv2d(x, b.weight, b.bias, 1, 1, need_indices=False, reduction_order="taps")
+    assert torch.equal(y3, yb.detach())
+    # ties: ReLU'd input, positive weights -> the two orders must each agree with their own oracle
+    xr = torch.relu(x)
+    with torch.no_grad():
+        w_pos = b.weight.abs()
+        y4, imax4, imin4 = mam_conv2d(xr, w_pos, None, 1, 1, reduction_order="taps")
+    geom = (4, channels, 18, 15, 3, 3, 1, 1, 1, 1, 24)
+    y_ref, imax_ref, imin_ref = _tap_order_oracle(xr, w_pos, geom)
+    flat = lambda t: t.permute(0, 2, 3, 1).reshape(-1, 24).cpu()
+    assert torch.equal(flat(y4), y_ref)
+    assert torch.equal(flat(imax4).long(), imax_ref) and torch.equal(flat(imin4).long(), imin_ref)

@@ -134,3 +134,28 @@ def test_reference_cuda_build_is_a_no_op_without_a_checkout(tmp_path):
     from oracle import build_ref_cuda
 
     assert build_ref_cuda.build(str(tmp_path)) == []
+
+
+def test_implicit_convolution_applicability_needs_no_device():
+    L = _lib.lib()
+    assert L.mam_conv_fwd_applies(128, 64, 56, 56, 3, 3, 1, 1, 1, 1) == 1       # the benchmark's convolution
+    assert L.mam_conv_fwd_applies(128, 3, 224, 224, 7, 7, 2, 2, 3, 3) == 0      # 3 input channels
+    assert L.mam_conv_fwd_applies(1, 32, 8, 8, 3, 3, 1, 1, 1, 1) == 0           # input below 128 KiB
+    assert L.mam_conv_fwd_applies(8, 64, 56, 56, 3, 3, 1, 1, 200, 1) == 0       # padding outside the corner field
+    assert L.mam_conv_fwd_applies(8, 64, 56, 56, 60, 3, 1, 1, 1, 1) == 0        # kernel larger than the padded input
+    null, one = None, ctypes.c_void_p(16)
+    assert L.mam_conv_fwd_f32(null, one, null, null, 0, 1.0, 0.0, one, null, null, 8, 64, 56, 56, 3, 3, 1, 1, 1, 1, 8, null) == 1
+    assert L.mam_conv_fwd_f32(one, one, null, null, 0, 1.0, 0.0, one, one, null, 8, 64, 56, 56, 3, 3, 1, 1, 1, 1, 8, null) == 1
+
+
+def test_tap_order_permutation_and_legacy_index():
+    from mamtorch_b200.nn.conv import tap_order_permutation, to_legacy_index
+
+    C, kH, kW = 5, 3, 2
+    perm = tap_order_permutation(C, kH, kW)
+    assert sorted(perm.tolist()) == list(range(C * kH * kW))
+    for pos, k in enumerate(perm.tolist()):
+        c, kh, kw = k // (kH * kW), (k // kW) % kH, k % kW
+        assert pos == (kw * kH + kh) * C + c
+    # position in tap order == the legacy index of the reference's text
+    assert torch.equal(to_legacy_index(perm, C, kH, kW), torch.arange(C * kH * kW))
