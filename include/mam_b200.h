@@ -91,6 +91,16 @@ int mam_fwd_f32(const float* a, const float* b, int b_layout,
                 int64_t M, int64_t K, int64_t N,
                 void* workspace, size_t workspace_bytes, void* stream);
 
+/* Values-only forward with K cut into consecutive slices of split_width columns (the last one may be
+ * shorter): y[m,n] = sum over slices, in ascending order, of (max + min over the slice's products), then the
+ * blend / bias epilogue of mam_fwd_f32.  One launch for what the reference module's `splits` option does with
+ * one kernel call and one addition pass per slice (mamtorch/nn/v4/fullyconnected.py:164-176).  a[M,K] and
+ * w[N,K] (the weight as stored).  MAM_ERR_UNSUPPORTED unless split_width % 32 == 0, split_width < K, K % 4 == 0
+ * and both operands are 16-byte aligned: callers then run slice by slice. */
+int mam_fwd_splits_f32(const float* a, const float* w, const float* bias, const float* dense, int blend,
+                       float alpha, float beta, float* y, int64_t M, int64_t K, int64_t N,
+                       int64_t split_width, void* stream);
+
 /* Forward for callers that cannot allocate device memory.  (No counterpart in the reference:
  * its host code allocates freely through ATen.)
  *

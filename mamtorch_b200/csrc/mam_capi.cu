@@ -192,6 +192,7 @@ using ValCfg4 = FwdCfg<4, 8, 4, 3, 4, false, 2, false>;         // 64x192 tile, 
 using ValCfg5 = FwdCfg<4, 8, 4, 2, 4, false, 2, false, false>;  // 64x128 tile, 256 threads, scalar multiplies
 using ValCfg6 = FwdCfg<4, 8, 4, 2, 4, false, 2, true>;          // 64x128 tile, 256 threads
 using ValCfg7 = FwdCfg<4, 4, 8, 2, 6, false, 4, false>;         // 128x64 tile, 512 threads
+using SplitCfg = FwdCfg<4, 8, 4, 2, 4, false, 2, false, true, true>;   // 64x128 tile, slices of K summed in the kernel
 using IdxCfg0 = FwdCfg<4, 8, 4, 2, 4, true, 2, false, false>;   // 64x128 tile, 256 threads, scalar multiplies
 using IdxCfg1 = FwdCfg<4, 8, 4, 2, 4, true, 2, false>;          // 64x128 tile, 256 threads
 using IdxCfg2 = FwdCfg<4, 8, 4, 2, 4, true, 1, false>;
@@ -276,7 +277,7 @@ int run_tiled(const float* a, const float* w, float* y, int32_t* argmax, int32_t
     int st = MAM_OK;
     int* flag = nullptr;
     MAM_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&flag), g_wait_gave_up));
-    FwdParams prm{y, argmax, argmin, M, K, N, ep, 1.0f, flag, Im2colRows{}};
+    FwdParams prm{y, argmax, argmin, M, K, N, ep, 1.0f, flag, Im2colRows{}, 0};
     if (cv) {
         const ConvGeom& g = cv->g;
         prm.conv = Im2colRows{g.C / 32, g.C, g.kH, g.kW, g.Ho, g.Wo, g.sh, g.sw, g.ph, g.pw};
@@ -501,6 +502,25 @@ int mam_fwd_f32(const float* a, const float* b, int b_layout, const float* bias,
         w = static_cast<const float*>(workspace);
     }
     return run_tiled(a, w, y, argmax, argmin, M, K, N, ep, variant, *d, cs, nullptr);
+}
+
+int mam_fwd_splits_f32(const float* a, const float* w, const float* bias, const float* dense, int blend, float alpha,
+                       float beta, float* y, int64_t M, int64_t K, int64_t N, int64_t split_width, void* stream) {
+    if (bad_ptr(a) || bad_ptr(w) || bad_ptr(y) || M <= 0 || K <= 0 || N <= 0 || split_width <= 0)
+        return MAM_ERR_INVALID_ARGUMENT;
+    if (K >= (1LL << 31) || N >= (1LL << 31) || M >= (1LL << 31)) return MAM_ERR_UNSUPPORTED;
+    // slices must end on chunk boundaries and there must be more than one of them
+    if (split_width % FWD_BK != 0 || split_width >= K || K % 4 != 0 || !aligned16(a) || !aligned16(w) ||
+        K / FWD_BK >= 65535)
+        return MAM_ERR_UNSUPPORTED;
+    const DevInfo* d = nullptr;
+    int st = device_info(&d);
+    if (st != MAM_OK) return st;
+    int* flag = nullptr;
+    MAM_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&flag), g_wait_gave_up));
+    EpilogueArgs ep{bias, dense, alpha, beta, blend};
+    FwdParams prm{y, nullptr, nullptr, M, K, N, ep, 1.0f, flag, Im2colRows{}, (int)(split_width / FWD_BK)};
+    return launch_tiled<SplitCfg>(a, w, prm, *d, (cudaStream_t)stream);
 }
 
 int mam_fwd_kn_static_f32(const float* a, const float* b, float* y, int32_t* argmax, int32_t* argmin, int64_t M,

@@ -23,6 +23,15 @@ struct EpilogueArgs {
 
 // y = alpha*(vmax+vmin) + beta*dense + bias, every step individually rounded (no contraction),
 // in the order of the reference's host glue (mamtorch/kernel/v3/csrc/cuda/fullyconnected.cu:153-160).
+__device__ __forceinline__ float mam_epilogue_term(float s, const EpilogueArgs& e, long long m, long long n,
+                                                   long long N) {
+    if (e.blend) {
+        s = __fmul_rn(s, e.alpha);
+        if (e.dense) s = __fadd_rn(s, __fmul_rn(e.dense[m * N + n], e.beta));
+    }
+    if (e.bias) s = __fadd_rn(s, e.bias[n]);
+    return s;
+}
 __device__ __forceinline__ float mam_epilogue(float vmax, float vmin, const EpilogueArgs& e,
                                               long long m, long long n, long long N) {
     float s = __fadd_rn(vmax, vmin);

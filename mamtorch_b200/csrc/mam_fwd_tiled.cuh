@@ -32,8 +32,12 @@ namespace mamb200 {
 constexpr int FWD_BK = 32;  // floats per row per stage = one 128-byte swizzle span
 
 template <int TM_, int TN_, int WM_, int WN_, int STAGES_, bool TRACK_, int UQ_ = 8, bool BATCH_ = false,
-          bool MUL2_ = true>
+          bool MUL2_ = true, bool SPLIT_ = false>
 struct FwdCfg {
+    // K cut into slices of prm.split_chunks chunks: y = sum over slices of (max + min) of the slice, added in
+    // ascending slice order -- the module's `splits` (mamtorch/nn/v4/fullyconnected.py:164-176) in one launch
+    static constexpr bool SPLIT = SPLIT_;
+    static_assert(!(SPLIT_ && TRACK_), "slices are summed in the values-only kernel");
     static constexpr bool MUL2 = MUL2_;     // packed mul.rn.f32x2 (true) or four scalar multiplies
     static constexpr int UQ = UQ_;          // 16-byte k groups per unrolled loop body
     static constexpr bool BATCH = BATCH_;   // form all products of a W row before any max/min
@@ -89,6 +93,7 @@ struct FwdParams {
     float one;     // 1.0f kept opaque to the compiler (see merge below)
     int* error;    // set to 1 when a bounded wait gave up
     Im2colRows conv;  // c32 != 0: tmA is an im2col-mode map of the channels-last convolution input
+    int split_chunks; // Cfg::SPLIT: 32-wide chunks per slice of K
 };
 
 // compile-time loop: f receives std::integral_constant<int, I>, so I can feed "n" asm operands
@@ -203,7 +208,30 @@ mam_fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
             }
         }
 
+        float ysum[Cfg::SPLIT ? TM : 1][Cfg::SPLIT ? TN : 1];
+        int next_split = prm.split_chunks;
+        if constexpr (Cfg::SPLIT) {
+#pragma unroll
+            for (int i = 0; i < TM; ++i)
+#pragma unroll
+                for (int j = 0; j < TN; ++j) ysum[i][j] = 0.f;
+        }
         for (int kc = 0; kc < nk; ++kc) {
+            if constexpr (Cfg::SPLIT) {
+                if (kc == next_split) {   // a slice of K ends: bank its max + min, start the next one
+                    next_split += prm.split_chunks;
+#pragma unroll
+                    for (int i = 0; i < TM; ++i)
+#pragma unroll
+                        for (int j = 0; j < TN; ++j) {
+                            const float t = __fadd_rn(vmax[i][j], vmin[i][j]);
+                            // the first slice stands alone (0 + t would turn -0 into +0)
+                            ysum[i][j] = (kc == prm.split_chunks) ? t : __fadd_rn(ysum[i][j], t);
+                            vmax[i][j] = -INFINITY;
+                            vmin[i][j] = INFINITY;
+                        }
+                }
+            }
             if (tid == 0 && !produce_one()) atomicExch(prm.error, 1);
             if (!mbar_wait_bounded(&full_bar[stage], phase)) {
                 atomicExch(prm.error, 1);
@@ -323,7 +351,11 @@ mam_fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
             for (int j = 0; j < TN; ++j) {
                 const long long n = ncol0 + j * 8;
                 if (n >= N) continue;
-                prm.y[m * N + n] = mam_epilogue(vmax[i][j], vmin[i][j], prm.ep, m, n, N);
+                if constexpr (Cfg::SPLIT)
+                    prm.y[m * N + n] = mam_epilogue_term(
+                        __fadd_rn(ysum[i][j], __fadd_rn(vmax[i][j], vmin[i][j])), prm.ep, m, n, N);
+                else
+                    prm.y[m * N + n] = mam_epilogue(vmax[i][j], vmin[i][j], prm.ep, m, n, N);
                 if constexpr (TRACK) {
                     unsigned short cmax, cmin;
                     const uint32_t amax = id_addr + (uint32_t)(((i * TN + j) * 2 + 0) * Cfg::CONSUMERS * 2);

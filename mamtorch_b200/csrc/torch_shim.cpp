@@ -233,6 +233,40 @@ std::vector<at::Tensor> linear_forward(const at::Tensor& x, const at::Tensor& we
     if (!want_idx) return {r.y};
     return {r.y, r.argmax, r.argmin};
 }
+// y[M,N] with K cut into slices of split_width columns, each contributing its own max + min; an empty tensor
+// where the single-launch form does not apply (the caller then goes slice by slice)
+at::Tensor linear_forward_splits(const at::Tensor& x, const at::Tensor& weight, const c10::optional<at::Tensor>& bias,
+                                 const c10::optional<at::Tensor>& dense_t, double alpha, double beta,
+                                 int64_t split_width) {
+    check_matrix(x, "x");
+    check_matrix(weight, "weight");
+    const int64_t M = x.size(0), K = x.size(1), N = weight.size(0);
+    TORCH_CHECK(weight.size(1) == K, "weight must be [N, K]");
+    const float* bias_p = nullptr;
+    const float* dense_p = nullptr;
+    at::Tensor bias_c;
+    if (bias.has_value() && bias->defined()) {
+        TORCH_CHECK(bias->is_cuda() && bias->scalar_type() == at::kFloat && bias->numel() == N, "bias must be float32 [N]");
+        bias_c = bias->contiguous();
+        bias_p = bias_c.data_ptr<float>();
+    }
+    if (dense_t.has_value() && dense_t->defined()) {
+        check_matrix(*dense_t, "dense");
+        TORCH_CHECK(dense_t->size(0) == M && dense_t->size(1) == N, "dense must be [M, N]");
+        dense_p = dense_t->data_ptr<float>();
+    }
+    c10::cuda::CUDAGuard guard(x.device());
+    if (M == 0 || N == 0) return at::empty({M, N}, x.options());
+    auto y = at::empty({M, N}, x.options());
+    const bool blend = !(alpha == 1.0 && beta == 0.0);
+    auto stream = at::cuda::getCurrentCUDAStream();
+    const int st = mam_fwd_splits_f32(x.data_ptr<float>(), weight.data_ptr<float>(), bias_p, dense_p, blend ? 1 : 0,
+                                      (float)alpha, (float)beta, y.data_ptr<float>(), M, K, N, split_width,
+                                      stream.stream());
+    if (st == MAM_ERR_UNSUPPORTED) return at::empty({0}, x.options());
+    check_status(st, "mam_fwd_splits_f32");
+    return y;
+}
 std::vector<at::Tensor> linear_backward(const at::Tensor& x, const at::Tensor& weight, const at::Tensor& grad,
                                         const at::Tensor& argmax, const at::Tensor& argmin, double scale) {
     return backward_impl(x, weight, MAM_B_NK, grad, argmax, argmin, scale);
@@ -521,6 +555,7 @@ TORCH_LIBRARY(mamtorch_b200, m) {
     m.def("linear_backward_km(Tensor x, Tensor weight, Tensor grad, Tensor argmax, Tensor argmin, float scale) -> Tensor[]");
     m.def("conv_backward(Tensor x, Tensor weight, Tensor grad, Tensor argmax, Tensor argmin, float scale, int kH, int kW, int sh, int sw, int ph, int pw) -> Tensor[]");
     m.def("conv_im2col(Tensor x, int kH, int kW, int sh, int sw, int ph, int pw) -> Tensor");
+    m.def("linear_forward_splits(Tensor x, Tensor weight, Tensor? bias, Tensor? dense, float alpha, float beta, int split_width) -> Tensor");
     m.def("conv_forward_implicit(Tensor x_nhwc, Tensor w_taps, Tensor? bias, Tensor? dense, float alpha, float beta, int kH, int kW, int sh, int sw, int ph, int pw, bool need_indices) -> Tensor[]");
     m.def("conv_implicit_applies(int B, int C, int H, int W, int kH, int kW, int sh, int sw, int ph, int pw) -> bool", &conv_implicit_applies);
     m.def("conv_col2im(Tensor cols_t, int B, int C, int H, int W, int kH, int kW, int sh, int sw, int ph, int pw) -> Tensor");
@@ -539,6 +574,7 @@ TORCH_LIBRARY_IMPL(mamtorch_b200, CUDA, m) {
     m.impl("conv_backward", &conv_backward);
     m.impl("conv_im2col", &conv_im2col);
     m.impl("conv_forward_implicit", &conv_forward_implicit);
+    m.impl("linear_forward_splits", &linear_forward_splits);
     m.impl("conv_col2im", &conv_col2im);
     m.impl("selection_hits", &selection_hits);
     m.impl("selection_count_update_", &selection_count_update_);

@@ -45,6 +45,11 @@ def _(x, kH, kW, sh, sw, ph, pw):
     return x.new_empty((B * Ho * Wo, C * kH * kW))
 
 
+@torch.library.register_fake("mamtorch_b200::linear_forward_splits")
+def _(x, weight, bias, dense, alpha, beta, split_width):
+    return x.new_empty((x.size(0), weight.size(0)))
+
+
 @torch.library.register_fake("mamtorch_b200::conv_forward_implicit")
 def _(x_nhwc, w_taps, bias, dense, alpha, beta, kH, kW, sh, sw, ph, pw, need_indices):
     B, H, W, C = x_nhwc.shape

@@ -141,6 +141,16 @@ class FullyConnected(Module):
         elif self.splits > 1:
             # K is cut into slices; every slice contributes its own max+min (reference :164-176)
             y = None
+            if not self.training and not (torch.is_grad_enabled() and (x.requires_grad or w.requires_grad)):
+                # inference: all slices in one launch (needs slice widths that are multiples of 32)
+                fused = torch.ops.mamtorch_b200.linear_forward_splits(
+                    x.contiguous(), w.contiguous(), self.bias, dense, float(self.alpha) if dense is not None else 1.0,
+                    float(self.beta) if dense is not None else 0.0, self.in_subfeatures)
+                if fused.numel() == x.size(0) * self.out_features and fused.dim() == 2:
+                    y = fused.view(input.shape[:-1] + (self.out_features,))
+                    if self.drop_rate > 0:
+                        y = F.dropout(y, self.drop_rate, self.training)
+                    return y
             bounds = [(i * self.in_subfeatures, self.in_subfeatures) for i in range(self.splits - 1)]
             bounds.append((self.in_features - self.in_subfeatures_last, self.in_subfeatures_last))
             for start, width in bounds:

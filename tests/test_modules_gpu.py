@@ -131,6 +131,51 @@ def test_module_beta_blend_splits_and_relu(cuda):
     np.testing.assert_allclose(ys.detach().cpu().numpy(), want.numpy(), rtol=1e-6, atol=1e-6)
 
 
+@pytest.mark.parametrize("case", [(300, 768, 200, 3, True, 0), (129, 200, 65, 2, False, 0), (64, 1024, 130, 4, True, 3),
+                                  (77, 96, 40, 3, True, 0), (90, 520, 31, 5, False, 0), (70, 156, 50, 5, True, 0)])
+def test_split_module_in_one_launch_equals_the_slice_by_slice_sum(case, cuda):
+    """Inference with `splits` > 1: one launch where every slice width is a multiple of 32 (an empty result
+    tells the module to go slice by slice: (200, 2) has 100-wide slices), bit for bit the ordered sum of the
+    per-slice oracle outputs, also under the beta blend and with the ragged last slice."""
+    import mamtorch_b200 as mamtorch
+
+    M, K, N, splits, bias, vsteps = case
+    torch.manual_seed(K + splits)
+    layer = mamtorch.nn.FullyConnected(K, N, splits=splits, bias=bias, vcon_steps=4 if vsteps else 0).to(cuda)
+    for _ in range(vsteps):
+        layer.vcon_step()
+    x = _rand((M, K), K, cuda)
+    layer.eval()
+    with torch.no_grad():
+        y = layer(x)
+    sub = -(-K // splits)
+    fused = torch.ops.mamtorch_b200.linear_forward_splits(x, layer.weight.detach(), None, None, 1.0, 0.0, sub)
+    assert (fused.dim() == 2) == (sub % 32 == 0 and K % 4 == 0)
+    w = layer.weight.detach().cpu()
+    want = None
+    for s0 in range(0, K, sub):
+        part, _, _ = mam_oracle.mam_forward(x.cpu()[:, s0:s0 + sub], w[:, s0:s0 + sub].T.contiguous())
+        want = part if want is None else want + part
+    if fused.dim() == 2:
+        assert torch.equal(fused.cpu(), want)
+    if vsteps:
+        want = float(layer.alpha) * want + float(layer.beta) * (x.cpu() @ w.T)
+        if bias:
+            want = want + layer.bias.detach().cpu()
+        np.testing.assert_allclose(y.cpu().numpy(), want.numpy(), rtol=2e-3, atol=2e-3 * float(want.abs().max()))
+    else:
+        if bias:
+            want = want + layer.bias.detach().cpu()
+        assert torch.equal(y.cpu(), want)
+    # training mode goes slice by slice with indices and must give the same values
+    layer.train()
+    yt = layer(x)
+    if vsteps:
+        np.testing.assert_allclose(yt.detach().cpu().numpy(), y.cpu().numpy(), rtol=1e-5, atol=1e-5)
+    else:
+        assert torch.equal(yt.detach(), y)
+
+
 def test_v1_module_and_mamdense(cuda):
     import mamtorch_b200 as mamtorch
 
