@@ -71,18 +71,30 @@ struct Im2colRows {
     int c32, C, kH, kW, Ho, Wo, sh, sw, ph, pw;
 };
 
-// Issues the copy of chunk kc of the rows starting at output pixel m0 (thread-0 helper).
-__device__ __forceinline__ void im2col_chunk_load(void* dst, const void* tmap, uint64_t* bar, const Im2colRows& cv,
-                                                  long long m0, int kc) {
-    const int tap = kc / cv.c32, cc = kc - tap * cv.c32;
-    const int kw = tap / cv.kH, kh = tap - kw * cv.kH;
-    const int hw = cv.Ho * cv.Wo;
-    const int n = (int)(m0 / hw);
-    const int rem = (int)(m0 - (long long)n * hw);
-    const int ho = rem / cv.Wo, wo = rem - ho * cv.Wo;
-    tma_load_im2col_4d(dst, tmap, bar, cc * 32, wo * cv.sw - cv.pw, ho * cv.sh - cv.ph, n, (uint16_t)kw,
-                       (uint16_t)kh);
-}
+// Where the issuing thread stands in the (tile, chunk) sequence of a convolution: base pixel of the tile
+// and the filter tap / channel block of the next chunk.  Decoding a tile costs three integer divisions,
+// stepping to the next chunk none -- the issuing thread also computes, and its warp must not fall behind
+// the others by a division sequence per chunk.
+struct Im2colCursor {
+    int n, h, w;        // image and base pixel (top-left patch corner) of the tile's first row
+    int cc, kh, kw;     // channel block and tap of the next chunk
+    __device__ __forceinline__ void start_tile(const Im2colRows& cv, long long m0) {
+        const int hw = cv.Ho * cv.Wo;
+        n = (int)(m0 / hw);
+        const int rem = (int)(m0 - (long long)n * hw);
+        const int ho = rem / cv.Wo;
+        h = ho * cv.sh - cv.ph;
+        w = (rem - ho * cv.Wo) * cv.sw - cv.pw;
+        cc = kh = kw = 0;
+    }
+    __device__ __forceinline__ void load_and_advance(void* dst, const void* tmap, uint64_t* bar, const Im2colRows& cv) {
+        tma_load_im2col_4d(dst, tmap, bar, cc * 32, w, h, n, (uint16_t)kw, (uint16_t)kh);
+        if (++cc == cv.c32) {
+            cc = 0;
+            if (++kh == cv.kH) { kh = 0; ++kw; }
+        }
+    }
+};
 
 struct FwdParams {
     float* y;
@@ -154,16 +166,19 @@ mam_fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     long long p_tile = blockIdx.x;
     int p_kc = 0, p_stage = 0;
     uint32_t p_phase = 0;
+    Im2colCursor p_cur{};
     auto produce_one = [&]() -> bool {
         if (p_tile >= ntiles) return true;
         if (!mbar_wait_bounded(&empty_bar[p_stage], p_phase ^ 1u)) return false;
         const int tm = (int)(p_tile / ntn), tn = (int)(p_tile % ntn);
         mbar_expect_tx(&full_bar[p_stage], Cfg::STAGE_BYTES);
         unsigned char* sa = smem + p_stage * Cfg::STAGE_BYTES;
-        if (prm.conv.c32)
-            im2col_chunk_load(sa, &tmA, &full_bar[p_stage], prm.conv, (long long)tm * Cfg::BM, p_kc);
-        else
+        if (prm.conv.c32) {
+            if (p_kc == 0) p_cur.start_tile(prm.conv, (long long)tm * Cfg::BM);
+            p_cur.load_and_advance(sa, &tmA, &full_bar[p_stage], prm.conv);
+        } else {
             tma_load_2d(sa, &tmA, &full_bar[p_stage], p_kc * FWD_BK, tm * Cfg::BM);
+        }
         tma_load_2d(sa + Cfg::A_BYTES, &tmW, &full_bar[p_stage], p_kc * FWD_BK, tn * Cfg::BN);
         if (++p_stage == STAGES) { p_stage = 0; p_phase ^= 1u; }
         if (++p_kc == nk) { p_kc = 0; p_tile += gridDim.x; }
@@ -430,15 +445,18 @@ mam_resolve_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     // producer state (thread 0)
     int p_kc = 0, p_stage = 0;
     uint32_t p_phase = 0;
+    Im2colCursor p_cur{};
     auto produce_one = [&]() -> bool {
         if (p_kc >= nk) return true;
         if (!mbar_wait_bounded(&empty_bar[p_stage], p_phase ^ 1u)) return false;
         mbar_expect_tx(&full_bar[p_stage], C::STAGE_BYTES);
         unsigned char* sa = smem + p_stage * C::STAGE_BYTES;
-        if (conv.c32)
-            im2col_chunk_load(sa, &tmA, &full_bar[p_stage], conv, m0, p_kc);
-        else
+        if (conv.c32) {
+            if (p_kc == 0) p_cur.start_tile(conv, m0);
+            p_cur.load_and_advance(sa, &tmA, &full_bar[p_stage], conv);
+        } else {
             tma_load_2d(sa, &tmA, &full_bar[p_stage], p_kc * FWD_BK, (int)m0);
+        }
         tma_load_2d(sa + C::A_BYTES, &tmW, &full_bar[p_stage], p_kc * FWD_BK, (int)n0);
         if (++p_stage == C::STAGES) { p_stage = 0; p_phase ^= 1u; }
         ++p_kc;
@@ -519,6 +537,7 @@ mam_resolve_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     // ---- pass C: stream the chunks, resolve the tasks of each
     int stage = 0;
     uint32_t phase = 0;
+    int r_cc = 0, r_kh = 0, r_kw = 0;   // convolution: channel block and tap of the chunk being resolved
     for (int kc = 0; kc < nk; ++kc) {
         if (tid == 0 && !produce_one()) atomicExch(error, 1);
         if (!mbar_wait_bounded(&full_bar[stage], phase)) {
@@ -532,11 +551,13 @@ mam_resolve_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         // Convolution rows: the chunk is 32 channels of one tap; indices leave in the numbering
         // k = (c*kH + kh)*kW + kw of weight.view(F, -1), i.e. kout = kout0 + e * kH*kW for element e.
         int kout0 = kc * FWD_BK, kout_step = 1;
-        if (conv.c32) {
-            const int tap = kc / conv.c32, cc = kc - tap * conv.c32;
-            const int kw = tap / conv.kH, kh = tap - kw * conv.kH;
+        if (conv.c32) {   // (r_cc, r_kh, r_kw) step with the chunks: no divisions in the loop
             kout_step = conv.kH * conv.kW;
-            kout0 = cc * 32 * kout_step + kh * conv.kW + kw;
+            kout0 = r_cc * 32 * kout_step + r_kh * conv.kW + r_kw;
+            if (++r_cc == conv.c32) {
+                r_cc = 0;
+                if (++r_kh == conv.kH) { r_kh = 0; ++r_kw; }
+            }
         }
         for (int t = start[kc] + tid; t < t_end; t += C::THREADS) {
             const unsigned code = tasks[t];
