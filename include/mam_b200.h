@@ -198,6 +198,8 @@ int mam_conv_bwd_f32(const float* x, const float* w, const float* grad,
  * device, and callers then take the patch-row route.  Stands in for mamconv2d_forward of the reference's
  * text backups (mamtorch/kernel/backup/mamconv2d_forward.txt:25-175) and the permutes around it
  * (mamtorch/kernel/backup/mamconv2d.txt:70-100). */
+/* out[B,H,W,C] = x[B,C,H,W]: the channels-last copy mam_conv_fwd_f32 reads (one pass; B <= 65535). */
+int mam_nchw_to_nhwc_f32(const float* x, float* out, int64_t B, int64_t C, int64_t H, int64_t W, void* stream);
 int mam_conv_fwd_applies(int64_t B, int64_t C, int64_t H, int64_t W, int kH, int kW, int sh, int sw, int ph, int pw);
 int mam_conv_fwd_f32(const float* x_nhwc, const float* w_taps, const float* bias, const float* dense, int blend,
                      float alpha, float beta, float* y, int32_t* argmax, int32_t* argmin,

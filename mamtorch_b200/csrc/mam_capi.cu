@@ -162,22 +162,23 @@ int encode_im2col_rows(CUtensorMap* tm, const ConvSrc& cv, int pixels, bool swiz
     return MAM_OK;
 }
 
-template <class Cfg>
+template <class Cfg, bool CONV = false>
 int launch_tiled(const float* a, const float* w, const FwdParams& prm, const DevInfo& d, cudaStream_t st,
                  const ConvSrc* cv = nullptr) {
     if (Cfg::SMEM_BYTES > d.max_smem) return MAM_ERR_UNSUPPORTED;
+    if (CONV != (cv != nullptr)) return MAM_ERR_INVALID_ARGUMENT;
     CUtensorMap tmA, tmW;
-    int s = cv ? encode_im2col_rows(&tmA, *cv, Cfg::BM, true) : encode_rows_k(&tmA, a, prm.M, prm.K, Cfg::BM);
+    int s = CONV ? encode_im2col_rows(&tmA, *cv, Cfg::BM, true) : encode_rows_k(&tmA, a, prm.M, prm.K, Cfg::BM);
     if (s != MAM_OK) return s;
     s = encode_rows_k(&tmW, w, prm.N, prm.K, Cfg::BN);
     if (s != MAM_OK) return s;
-    MAM_CUDA(cudaFuncSetAttribute(mam_fwd_tiled_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    MAM_CUDA(cudaFuncSetAttribute(mam_fwd_tiled_kernel<Cfg, CONV>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   Cfg::SMEM_BYTES));
     const long long ntiles = ((prm.M + Cfg::BM - 1) / Cfg::BM) * ((prm.N + Cfg::BN - 1) / Cfg::BN);
     const int grid = (int)(ntiles < d.sms ? ntiles : d.sms);
     {
         TimedLaunch t(MAM_KERNEL_FWD_TILED, st);
-        mam_fwd_tiled_kernel<Cfg><<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(tmA, tmW, prm);
+        mam_fwd_tiled_kernel<Cfg, CONV><<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(tmA, tmW, prm);
     }
     MAM_CUDA(cudaGetLastError());
     return MAM_OK;
@@ -282,28 +283,40 @@ int run_tiled(const float* a, const float* w, float* y, int32_t* argmax, int32_t
         const ConvGeom& g = cv->g;
         prm.conv = Im2colRows{g.C / 32, g.C, g.kH, g.kW, g.Ho, g.Wo, g.sh, g.sw, g.ph, g.pw};
     }
-    if (!want_idx) {
+    if (cv) {
+        // patch rows by im2col-mode TMA: the configurations the automatic choice makes (the tuning
+        // selector of mam_set_fwd_variant applies to the matrix form only)
+        if (!want_idx) {
+            switch (auto_variant(false, M, N, d)) {
+                case 3: return launch_tiled<ValCfg3, true>(a, w, prm, d, cs, cv);
+                case 6: return launch_tiled<ValCfg6, true>(a, w, prm, d, cs, cv);
+                default: return launch_tiled<ValCfg2, true>(a, w, prm, d, cs, cv);
+            }
+        }
+        st = launch_tiled<IdxCfg1, true>(a, w, prm, d, cs, cv);
+    } else if (!want_idx) {
         switch (variant) {
-            case 0: st = launch_tiled<ValCfg0>(a, w, prm, d, cs, cv); break;
-            case 1: st = launch_tiled<ValCfg1>(a, w, prm, d, cs, cv); break;
-            case 2: st = launch_tiled<ValCfg2>(a, w, prm, d, cs, cv); break;
-            case 3: st = launch_tiled<ValCfg3>(a, w, prm, d, cs, cv); break;
-            case 4: st = launch_tiled<ValCfg4>(a, w, prm, d, cs, cv); break;
-            case 5: st = launch_tiled<ValCfg5>(a, w, prm, d, cs, cv); break;
-            case 6: st = launch_tiled<ValCfg6>(a, w, prm, d, cs, cv); break;
-            default: st = launch_tiled<ValCfg7>(a, w, prm, d, cs, cv); break;
+            case 0: st = launch_tiled<ValCfg0>(a, w, prm, d, cs); break;
+            case 1: st = launch_tiled<ValCfg1>(a, w, prm, d, cs); break;
+            case 2: st = launch_tiled<ValCfg2>(a, w, prm, d, cs); break;
+            case 3: st = launch_tiled<ValCfg3>(a, w, prm, d, cs); break;
+            case 4: st = launch_tiled<ValCfg4>(a, w, prm, d, cs); break;
+            case 5: st = launch_tiled<ValCfg5>(a, w, prm, d, cs); break;
+            case 6: st = launch_tiled<ValCfg6>(a, w, prm, d, cs); break;
+            default: st = launch_tiled<ValCfg7>(a, w, prm, d, cs); break;
         }
         return st;
-    }
-    switch (variant) {
-        case 0: st = launch_tiled<IdxCfg0>(a, w, prm, d, cs, cv); break;
-        case 1: st = launch_tiled<IdxCfg1>(a, w, prm, d, cs, cv); break;
-        case 2: st = launch_tiled<IdxCfg2>(a, w, prm, d, cs, cv); break;
-        case 3: st = launch_tiled<IdxCfg3>(a, w, prm, d, cs, cv); break;
-        case 4: st = launch_tiled<IdxCfg4>(a, w, prm, d, cs, cv); break;
-        case 5: st = launch_tiled<IdxCfg5>(a, w, prm, d, cs, cv); break;
-        case 6: st = launch_tiled<IdxCfg6>(a, w, prm, d, cs, cv); break;
-        default: st = launch_tiled<IdxCfg7>(a, w, prm, d, cs, cv); break;
+    } else {
+        switch (variant) {
+            case 0: st = launch_tiled<IdxCfg0>(a, w, prm, d, cs); break;
+            case 1: st = launch_tiled<IdxCfg1>(a, w, prm, d, cs); break;
+            case 2: st = launch_tiled<IdxCfg2>(a, w, prm, d, cs); break;
+            case 3: st = launch_tiled<IdxCfg3>(a, w, prm, d, cs); break;
+            case 4: st = launch_tiled<IdxCfg4>(a, w, prm, d, cs); break;
+            case 5: st = launch_tiled<IdxCfg5>(a, w, prm, d, cs); break;
+            case 6: st = launch_tiled<IdxCfg6>(a, w, prm, d, cs); break;
+            default: st = launch_tiled<IdxCfg7>(a, w, prm, d, cs); break;
+        }
     }
     if (st != MAM_OK) return st;
     const int nkc = (int)((K + FWD_BK - 1) / FWD_BK);
@@ -316,11 +329,18 @@ int run_tiled(const float* a, const float* w, float* y, int32_t* argmax, int32_t
         if (st != MAM_OK) return st;
         const long long tiles = ((M + ResolveCfg::RM - 1) / ResolveCfg::RM) * ((N + ResolveCfg::RN - 1) / ResolveCfg::RN);
         if (tiles > 2147483647LL) return MAM_ERR_UNSUPPORTED;
-        MAM_CUDA(cudaFuncSetAttribute(mam_resolve_tiled_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      ResolveCfg::SMEM_BYTES));
         TimedLaunch t(MAM_KERNEL_FWD_RESOLVE, cs);
-        mam_resolve_tiled_kernel<<<(unsigned)tiles, ResolveCfg::THREADS, ResolveCfg::SMEM_BYTES, cs>>>(
-            tmA, tmW, argmax, argmin, M, K, N, flag, prm.conv);
+        if (cv) {
+            MAM_CUDA(cudaFuncSetAttribute(mam_resolve_tiled_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          ResolveCfg::SMEM_BYTES));
+            mam_resolve_tiled_kernel<true><<<(unsigned)tiles, ResolveCfg::THREADS, ResolveCfg::SMEM_BYTES, cs>>>(
+                tmA, tmW, argmax, argmin, M, K, N, flag, prm.conv);
+        } else {
+            MAM_CUDA(cudaFuncSetAttribute(mam_resolve_tiled_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          ResolveCfg::SMEM_BYTES));
+            mam_resolve_tiled_kernel<false><<<(unsigned)tiles, ResolveCfg::THREADS, ResolveCfg::SMEM_BYTES, cs>>>(
+                tmA, tmW, argmax, argmin, M, K, N, flag, prm.conv);
+        }
     } else {
         const long long total = M * N;
         const long long blocks = (total + 255) / 256;
@@ -450,6 +470,17 @@ int mam_transpose_f32(const float* in, float* out, int64_t R, int64_t C, void* s
     const long long gx = (C + 31) / 32, gy = (R + 31) / 32;
     if (gy > 65535 || gx > 2147483647LL) return MAM_ERR_UNSUPPORTED;
     mam_transpose_kernel<<<dim3((unsigned)gx, (unsigned)gy), 256, 0, (cudaStream_t)stream>>>(in, out, R, C);
+    MAM_CUDA(cudaGetLastError());
+    return MAM_OK;
+}
+
+int mam_nchw_to_nhwc_f32(const float* x, float* out, int64_t B, int64_t C, int64_t H, int64_t W, void* stream) {
+    if (bad_ptr(x) || bad_ptr(out) || B <= 0 || C <= 0 || H <= 0 || W <= 0) return MAM_ERR_INVALID_ARGUMENT;
+    const long long hw = H * W;
+    const long long gx = (hw + 31) / 32, gy = (C + 31) / 32;
+    if (gy > 65535 || B > 65535 || gx > 2147483647LL) return MAM_ERR_UNSUPPORTED;
+    mam_transpose_batched_kernel<<<dim3((unsigned)gx, (unsigned)gy, (unsigned)B), 256, 0, (cudaStream_t)stream>>>(
+        x, out, C, hw);
     MAM_CUDA(cudaGetLastError());
     return MAM_OK;
 }

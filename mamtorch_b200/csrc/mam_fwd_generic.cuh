@@ -151,4 +151,25 @@ mam_transpose_kernel(const float* __restrict__ in, float* __restrict__ out, long
     }
 }
 
+// out[b][c][r] = in[b][r][c] for `batch` matrices [R,C] stored back to back (blockIdx.z = b).  With R = channels
+// and C = H*W this turns an image batch [B,C,H,W] into the channels-last [B,H,W,C] the im2col-mode loads read.
+__global__ void __launch_bounds__(256)
+mam_transpose_batched_kernel(const float* __restrict__ in, float* __restrict__ out, long long R, long long C) {
+    __shared__ float t[32][33];
+    const long long base = (long long)blockIdx.z * R * C;
+    const long long c0 = (long long)blockIdx.x * 32, r0 = (long long)blockIdx.y * 32;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+        const long long r = r0 + ty + 8 * p, c = c0 + tx;
+        if (r < R && c < C) t[ty + 8 * p][tx] = in[base + r * C + c];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+        const long long c = c0 + ty + 8 * p, r = r0 + tx;
+        if (r < R && c < C) out[base + c * R + r] = t[tx][ty + 8 * p];
+    }
+}
+
 }  // namespace mamb200

@@ -130,7 +130,8 @@ __device__ __forceinline__ ulonglong2 lds128_at(uint32_t addr) {
     return v;
 }
 
-template <class Cfg>
+// CONV: the a-operand is fetched by im2col-mode TMA (tmA is an im2col map, prm.conv describes the geometry).
+template <class Cfg, bool CONV = false>
 __global__ void __launch_bounds__(Cfg::THREADS, 1)
 mam_fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW,
                      const FwdParams prm) {
@@ -166,14 +167,14 @@ mam_fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     long long p_tile = blockIdx.x;
     int p_kc = 0, p_stage = 0;
     uint32_t p_phase = 0;
-    Im2colCursor p_cur{};
+    [[maybe_unused]] Im2colCursor p_cur{};
     auto produce_one = [&]() -> bool {
         if (p_tile >= ntiles) return true;
         if (!mbar_wait_bounded(&empty_bar[p_stage], p_phase ^ 1u)) return false;
         const int tm = (int)(p_tile / ntn), tn = (int)(p_tile % ntn);
         mbar_expect_tx(&full_bar[p_stage], Cfg::STAGE_BYTES);
         unsigned char* sa = smem + p_stage * Cfg::STAGE_BYTES;
-        if (prm.conv.c32) {
+        if constexpr (CONV) {
             if (p_kc == 0) p_cur.start_tile(prm.conv, (long long)tm * Cfg::BM);
             p_cur.load_and_advance(sa, &tmA, &full_bar[p_stage], prm.conv);
         } else {
@@ -411,6 +412,7 @@ struct ResolveCfg {
     static constexpr int LOOKAHEAD = STAGES - 1;
 };
 
+template <bool CONV>
 __global__ void __launch_bounds__(ResolveCfg::THREADS, 2)
 mam_resolve_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW,
                          int* __restrict__ argmax, int* __restrict__ argmin,
@@ -445,13 +447,13 @@ mam_resolve_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     // producer state (thread 0)
     int p_kc = 0, p_stage = 0;
     uint32_t p_phase = 0;
-    Im2colCursor p_cur{};
+    [[maybe_unused]] Im2colCursor p_cur{};
     auto produce_one = [&]() -> bool {
         if (p_kc >= nk) return true;
         if (!mbar_wait_bounded(&empty_bar[p_stage], p_phase ^ 1u)) return false;
         mbar_expect_tx(&full_bar[p_stage], C::STAGE_BYTES);
         unsigned char* sa = smem + p_stage * C::STAGE_BYTES;
-        if (conv.c32) {
+        if constexpr (CONV) {
             if (p_kc == 0) p_cur.start_tile(conv, m0);
             p_cur.load_and_advance(sa, &tmA, &full_bar[p_stage], conv);
         } else {
@@ -537,7 +539,7 @@ mam_resolve_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     // ---- pass C: stream the chunks, resolve the tasks of each
     int stage = 0;
     uint32_t phase = 0;
-    int r_cc = 0, r_kh = 0, r_kw = 0;   // convolution: channel block and tap of the chunk being resolved
+    [[maybe_unused]] int r_cc = 0, r_kh = 0, r_kw = 0;   // convolution: channel block and tap of the chunk being resolved
     for (int kc = 0; kc < nk; ++kc) {
         if (tid == 0 && !produce_one()) atomicExch(error, 1);
         if (!mbar_wait_bounded(&full_bar[stage], phase)) {
@@ -551,7 +553,7 @@ mam_resolve_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         // Convolution rows: the chunk is 32 channels of one tap; indices leave in the numbering
         // k = (c*kH + kh)*kW + kw of weight.view(F, -1), i.e. kout = kout0 + e * kH*kW for element e.
         int kout0 = kc * FWD_BK, kout_step = 1;
-        if (conv.c32) {   // (r_cc, r_kh, r_kw) step with the chunks: no divisions in the loop
+        if constexpr (CONV) {   // (r_cc, r_kh, r_kw) step with the chunks: no divisions in the loop
             kout_step = conv.kH * conv.kW;
             kout0 = r_cc * 32 * kout_step + r_kh * conv.kW + r_kw;
             if (++r_cc == conv.c32) {
@@ -604,7 +606,7 @@ mam_resolve_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
             if (p2 == best) e = 2;
             if (p1 == best) e = 1;
             if (p0 == best) e = 0;
-            const int kbest = kout0 + (bq * 4 + e) * kout_step;
+            const int kbest = CONV ? kout0 + (bq * 4 + e) * kout_step : kout0 + bq * 4 + e;
             const long long m = m0 + ra, n = n0 + rw;
             if (code & 1u) argmin[m * N + n] = kbest; else argmax[m * N + n] = kbest;
         }

@@ -293,6 +293,22 @@ at::Tensor conv_im2col(const at::Tensor& x, int64_t kH, int64_t kW, int64_t sh, 
                  "mam_im2col_f32");
     return rows;
 }
+// [B,H,W,C] contiguous from x[B,C,H,W] (returned as is when x already is channels-last in memory)
+at::Tensor conv_channels_last(const at::Tensor& x) {
+    TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kFloat && x.dim() == 4, "x must be a float32 CUDA [B,C,H,W] tensor");
+    auto view = x.permute({0, 2, 3, 1});
+    if (view.is_contiguous()) return view;
+    auto xc = x.contiguous();
+    const int64_t B = xc.size(0), C = xc.size(1), H = xc.size(2), W = xc.size(3);
+    c10::cuda::CUDAGuard guard(x.device());
+    auto out = at::empty({B, H, W, C}, xc.options());
+    if (out.numel() == 0) return out;
+    if (B > 65535 || C > 65535 * 32) return view.contiguous();
+    auto stream = at::cuda::getCurrentCUDAStream();
+    check_status(mam_nchw_to_nhwc_f32(xc.data_ptr<float>(), out.data_ptr<float>(), B, C, H, W, stream.stream()),
+                 "mam_nchw_to_nhwc_f32");
+    return out;
+}
 // Whether conv_forward_implicit can take a convolution of this geometry (no device needed).
 bool conv_implicit_applies(int64_t B, int64_t C, int64_t H, int64_t W, int64_t kH, int64_t kW, int64_t sh, int64_t sw,
                            int64_t ph, int64_t pw) {
@@ -556,6 +572,7 @@ TORCH_LIBRARY(mamtorch_b200, m) {
     m.def("conv_backward(Tensor x, Tensor weight, Tensor grad, Tensor argmax, Tensor argmin, float scale, int kH, int kW, int sh, int sw, int ph, int pw) -> Tensor[]");
     m.def("conv_im2col(Tensor x, int kH, int kW, int sh, int sw, int ph, int pw) -> Tensor");
     m.def("linear_forward_splits(Tensor x, Tensor weight, Tensor? bias, Tensor? dense, float alpha, float beta, int split_width) -> Tensor");
+    m.def("conv_channels_last(Tensor x) -> Tensor");
     m.def("conv_forward_implicit(Tensor x_nhwc, Tensor w_taps, Tensor? bias, Tensor? dense, float alpha, float beta, int kH, int kW, int sh, int sw, int ph, int pw, bool need_indices) -> Tensor[]");
     m.def("conv_implicit_applies(int B, int C, int H, int W, int kH, int kW, int sh, int sw, int ph, int pw) -> bool", &conv_implicit_applies);
     m.def("conv_col2im(Tensor cols_t, int B, int C, int H, int W, int kH, int kW, int sh, int sw, int ph, int pw) -> Tensor");
@@ -574,6 +591,7 @@ TORCH_LIBRARY_IMPL(mamtorch_b200, CUDA, m) {
     m.impl("conv_backward", &conv_backward);
     m.impl("conv_im2col", &conv_im2col);
     m.impl("conv_forward_implicit", &conv_forward_implicit);
+    m.impl("conv_channels_last", &conv_channels_last);
     m.impl("linear_forward_splits", &linear_forward_splits);
     m.impl("conv_col2im", &conv_col2im);
     m.impl("selection_hits", &selection_hits);

@@ -50,6 +50,12 @@ def _(x, weight, bias, dense, alpha, beta, split_width):
     return x.new_empty((x.size(0), weight.size(0)))
 
 
+@torch.library.register_fake("mamtorch_b200::conv_channels_last")
+def _(x):
+    B, C, H, W = x.shape
+    return x.new_empty((B, H, W, C))
+
+
 @torch.library.register_fake("mamtorch_b200::conv_forward_implicit")
 def _(x_nhwc, w_taps, bias, dense, alpha, beta, kH, kW, sh, sw, ph, pw, need_indices):
     B, H, W, C = x_nhwc.shape

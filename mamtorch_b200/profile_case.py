@@ -98,6 +98,8 @@ def conv_case(args):
 
     B, C, H, W, Fo = (int(v) for v in args.shape.lower().split("x"))
     dev = torch.device("cuda:0")
+    if args.variant >= 0:
+        _lib.check(_lib.lib().mam_set_fwd_variant(1, args.variant), "variant")
     g = torch.Generator().manual_seed(0)
     torch.manual_seed(0)
     conv = mamtorch.nn.MAMConv2d(C, Fo, 3, padding=1, bias=False, reduction_order=args.order).to(dev)

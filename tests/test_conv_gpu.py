@@ -232,3 +232,16 @@ def test_conv_module_in_tap_order_matches_the_patch_row_module(channels, cuda):
     flat = lambda t: t.permute(0, 2, 3, 1).reshape(-1, 24).cpu()
     assert torch.equal(flat(y4), y_ref)
     assert torch.equal(flat(imax4).long(), imax_ref) and torch.equal(flat(imin4).long(), imin_ref)
+
+
+@pytest.mark.parametrize("shape", [(3, 64, 14, 9), (2, 5, 7, 33), (1, 96, 1, 1), (4, 32, 56, 56)])
+def test_channels_last_copy(shape, cuda):
+    B, C, H, W = shape
+    x = torch.randn(B, C, H, W, generator=torch.Generator().manual_seed(B * C + H)).to(cuda)
+    out = torch.ops.mamtorch_b200.conv_channels_last(x)
+    assert out.shape == (B, H, W, C) and out.is_contiguous()
+    assert torch.equal(out, x.permute(0, 2, 3, 1))
+    # already channels-last in memory: handed back as a view, no copy
+    xcl = x.contiguous(memory_format=torch.channels_last)
+    view = torch.ops.mamtorch_b200.conv_channels_last(xcl)
+    assert view.data_ptr() == xcl.data_ptr() and torch.equal(view, out)
