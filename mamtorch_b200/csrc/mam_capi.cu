@@ -352,6 +352,7 @@ int run_tiled(const float* a, const float* w, float* y, int32_t* argmax, int32_t
     return MAM_OK;
 }
 
+int g_dense_split = 1;  // 0: the TF32 product runs whole tiles only (cross-check / timing selector)
 int g_bwd_mode = 0;  // 0 auto, 1 force the single-kernel form, 2 force the two-kernel form
 
 template <bool NK>
@@ -440,6 +441,10 @@ int mam_set_fwd_variant(int with_indices, int variant) {
     if (with_indices == 3) {  // selects the backward form: 0 auto, 1 single kernel, 2 two kernels
         if (variant < 0 || variant > 2) return MAM_ERR_INVALID_ARGUMENT;
         g_bwd_mode = variant;
+        return MAM_OK;
+    }
+    if (with_indices == 4) {  // TF32 product: 1 (default) slices the tiles of the last partial wave, 0 does not
+        g_dense_split = variant ? 1 : 0;
         return MAM_OK;
     }
     if (with_indices == 2) {  // selects the index resolver: 0 tiled (default), 1 thread-per-output
@@ -816,6 +821,9 @@ int mam_dense_tf32(const float* a, const float* w, float* out, float c_acc, floa
     if (st != MAM_OK) return st;
     st = encode_rows_k(&tmW, w, N, K, DG_BN);
     if (st != MAM_OK) return st;
+    CUtensorMap tmW64;   // 64-row boxes of W for the column slices of the last partial wave
+    st = encode_rows_k(&tmW64, w, N, K, 64);
+    if (st != MAM_OK) return st;
     const long long tiles = ((M + DG_BM - 1) / DG_BM) * ((N + DG_BN - 1) / DG_BN);
     if (tiles > 2147483647LL) return MAM_ERR_UNSUPPORTED;
     int* flag = nullptr;
@@ -823,9 +831,16 @@ int mam_dense_tf32(const float* a, const float* w, float* out, float c_acc, floa
     MAM_CUDA(cudaFuncSetAttribute(mam_dense_tf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DG_SMEM_BYTES));
     {
         TimedLaunch t(MAM_KERNEL_DENSE_TF32, (cudaStream_t)stream);
-        const unsigned grid = (unsigned)(tiles < d->sms ? tiles : d->sms);  // persistent: one CTA per SM
+        // persistent, one CTA per SM; the tiles of the last partial wave are cut into 2 or 4 column slices
+        // when that many more work items still fit one wave
+        const long long rem = tiles % d->sms;
+        int split = rem == 0 ? 1 : (rem * 4 <= d->sms ? 4 : (rem * 2 <= d->sms ? 2 : 1));
+        if (!g_dense_split) split = 1;
+        const long long full = split > 1 ? tiles - rem : tiles;
+        const long long items = full + (tiles - full) * split;
+        const unsigned grid = (unsigned)(items < d->sms ? items : d->sms);
         mam_dense_tf32_kernel<<<grid, DG_THREADS, DG_SMEM_BYTES, (cudaStream_t)stream>>>(
-            tmA, tmW, out, M, K, N, c_acc, c_out, flag);
+            tmA, tmW, tmW64, out, M, K, N, c_acc, c_out, flag, full, split);
     }
     MAM_CUDA(cudaGetLastError());
     return MAM_OK;

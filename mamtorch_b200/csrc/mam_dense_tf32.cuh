@@ -39,8 +39,8 @@ constexpr int DG_TMEM_COLS = 2 * DG_BN;  // two accumulators of 256 fp32 columns
 
 // Instruction descriptor of tcgen05.mma kind::tf32: fp32 accumulator (bits 4-5 = 1), TF32 A and B
 // (bits 7-9 and 10-12 = 2), both operands K-major (bits 15, 16 = 0), N>>3 at bit 17, M>>4 at bit 24.
-__host__ __device__ constexpr uint32_t dg_idesc() {
-    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(DG_BN >> 3) << 17) | ((uint32_t)(DG_BM >> 4) << 24);
+__host__ __device__ constexpr uint32_t dg_idesc(int n = DG_BN) {
+    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(DG_BM >> 4) << 24);
 }
 
 // Shared-memory matrix descriptor for a K-major operand stored as rows of 128 bytes in the 128-byte
@@ -86,10 +86,33 @@ __device__ __forceinline__ void dg_tile_coords(long long tile, int ntm, int ntn,
     tn = r / rows;
 }
 
+// Work items.  The first `full` tiles (a whole number of waves of the grid) are whole 128x256 tiles; the tiles
+// of the last, partial wave are cut into `split` column slices of 256/split columns each, one item per
+// slice, so that the tail keeps (nearly) every SM busy for 1/split of a tile time instead of a few SMs
+// for a whole one.  A slice loads the same operand boxes as its tile and multiplies against the rows
+// [ncol0, ncol0 + ncols) of the W box (N = ncols in the instruction descriptor).
+struct DgItem {
+    int tm, tn, ncol0, ncols;
+};
+__device__ __forceinline__ DgItem dg_item(long long g, long long full, int split, int ntm, int ntn) {
+    DgItem it;
+    long long tile = g;
+    it.ncol0 = 0;
+    it.ncols = DG_BN;
+    if (g >= full) {
+        const long long s = g - full;
+        tile = full + s / split;
+        it.ncols = DG_BN / split;
+        it.ncol0 = (int)(s % split) * it.ncols;
+    }
+    dg_tile_coords(tile, ntm, ntn, it.tm, it.tn);
+    return it;
+}
+
 __global__ void __launch_bounds__(DG_THREADS, 1)
 mam_dense_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW,
-                      float* __restrict__ out, long long M, long long K, long long N, float c_acc, float c_out,
-                      int* error) {
+                      const __grid_constant__ CUtensorMap tmW64, float* __restrict__ out, long long M, long long K, long long N, float c_acc, float c_out,
+                      int* error, long long full, int split) {
     extern __shared__ unsigned char dg_smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(
         (reinterpret_cast<uintptr_t>(dg_smem_raw) + 1023) & ~uintptr_t(1023));
@@ -103,6 +126,7 @@ mam_dense_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     const int ntn = (int)((N + DG_BN - 1) / DG_BN);
     const int ntm = (int)((M + DG_BM - 1) / DG_BM);
     const long long ntiles = (long long)ntm * ntn;
+    const long long nitems = full + (ntiles - full) * split;
     const int nk = (int)((K + DG_BK - 1) / DG_BK);
 
     if (threadIdx.x == 0) {
@@ -134,19 +158,28 @@ mam_dense_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (long long tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
-                int tm, tn;
-                dg_tile_coords(tile, ntm, ntn, tm, tn);
+            for (long long g = blockIdx.x; g < nitems && ok; g += gridDim.x) {
+                const DgItem item = dg_item(g, full, split, ntm, ntn);
+                const int tm = item.tm, tn = item.tn;
                 for (int kc = 0; kc < nk; ++kc) {
                     if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u)) {
                         atomicExch(error, 1);
                         ok = false;
                         break;
                     }
-                    mbar_expect_tx(&full_bar[stage], DG_STAGE_BYTES);
                     unsigned char* sa = smem + stage * DG_STAGE_BYTES;
-                    tma_load_2d(sa, &tmA, &full_bar[stage], kc * DG_BK, tm * DG_BM);
-                    tma_load_2d(sa + DG_A_BYTES, &tmW, &full_bar[stage], kc * DG_BK, tn * DG_BN);
+                    if (item.ncols == DG_BN) {
+                        mbar_expect_tx(&full_bar[stage], DG_STAGE_BYTES);
+                        tma_load_2d(sa, &tmA, &full_bar[stage], kc * DG_BK, tm * DG_BM);
+                        tma_load_2d(sa + DG_A_BYTES, &tmW, &full_bar[stage], kc * DG_BK, tn * DG_BN);
+                    } else {
+                        // a column slice: only its rows of W, in 64-row boxes, at their place in the stage
+                        mbar_expect_tx(&full_bar[stage], DG_A_BYTES + item.ncols * DG_BK * 4);
+                        tma_load_2d(sa, &tmA, &full_bar[stage], kc * DG_BK, tm * DG_BM);
+                        for (int r = item.ncol0; r < item.ncol0 + item.ncols; r += 64)
+                            tma_load_2d(sa + DG_A_BYTES + r * (DG_BK * 4), &tmW64, &full_bar[stage], kc * DG_BK,
+                                        tn * DG_BN + r);
+                    }
                     if (++stage == DG_STAGES) { stage = 0; phase ^= 1u; }
                 }
             }
@@ -157,7 +190,10 @@ mam_dense_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             uint32_t phase = 0;
             bool ok = true;
             long long it = 0;  // tiles done by this CTA
-            for (long long tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++it) {
+            for (long long g = blockIdx.x; g < nitems && ok; g += gridDim.x, ++it) {
+                const DgItem item = dg_item(g, full, split, ntm, ntn);
+                const uint32_t idesc = dg_idesc(item.ncols);
+                const uint32_t b_rows_off = (uint32_t)item.ncol0 * 128u;   // W rows are 128-byte rows of the box
                 const int buf = (int)(it & 1);
                 // the half must have been drained by the epilogue of the tile two steps back
                 if (!mbar_wait_bounded(&acc_empty[buf], (uint32_t)((it >> 1) & 1) ^ 1u)) {
@@ -174,13 +210,13 @@ mam_dense_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                     }
                     tc_fence_after();
                     const uint32_t a_addr = smem_u32(smem + stage * DG_STAGE_BYTES);
-                    const uint32_t b_addr = a_addr + DG_A_BYTES;
+                    const uint32_t b_addr = a_addr + DG_A_BYTES + b_rows_off;
 #pragma unroll
                     for (int k = 0; k < DG_BK / 8; ++k) {
                         // 8 tf32 = 32 bytes along K inside the 128-byte swizzle span: +2 in the address field
                         const uint64_t adesc = dg_smem_desc(a_addr + k * 32);
                         const uint64_t bdesc = dg_smem_desc(b_addr + k * 32);
-                        tc_mma_tf32(tmem_d, adesc, bdesc, dg_idesc(), (kc | k) ? 1u : 0u);
+                        tc_mma_tf32(tmem_d, adesc, bdesc, idesc, (kc | k) ? 1u : 0u);
                     }
                     tc_commit(&empty_bar[stage]);  // stage is free once these MMAs have read it
                     if (++stage == DG_STAGES) { stage = 0; phase ^= 1u; }
@@ -193,9 +229,9 @@ mam_dense_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         const int quarter = warp & 3;
         float* stage_s = reinterpret_cast<float*>(tmem_slot + 4) + (warp - 2) * (32 * 33);
         long long it = 0;
-        for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++it) {
-            int tm, tn;
-            dg_tile_coords(tile, ntm, ntn, tm, tn);
+        for (long long g = blockIdx.x; g < nitems; g += gridDim.x, ++it) {
+            const DgItem item = dg_item(g, full, split, ntm, ntn);
+            const int tm = item.tm, tn = item.tn;
             const int buf = (int)(it & 1);
             if (!mbar_wait_bounded(&acc_full[buf], (uint32_t)((it >> 1) & 1))) {
                 atomicExch(error, 1);
@@ -203,7 +239,7 @@ mam_dense_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             }
             tc_fence_after();
 #pragma unroll 1
-            for (int cg = 0; cg < DG_BN / 32; ++cg) {
+            for (int cg = 0; cg < item.ncols / 32; ++cg) {
                 uint32_t r[32];
                 const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * DG_BN + cg * 32);
                 asm volatile(
@@ -224,7 +260,7 @@ mam_dense_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
 #pragma unroll
                 for (int i = 0; i < 32; ++i) stage_s[lane * 33 + i] = __uint_as_float(r[i]) * c_acc;
                 __syncwarp();
-                const long long n = (long long)tn * DG_BN + cg * 32 + lane;
+                const long long n = (long long)tn * DG_BN + item.ncol0 + cg * 32 + lane;
                 const long long mrow0 = (long long)tm * DG_BM + quarter * 32;
                 if (n < N) {
 #pragma unroll 8

@@ -28,6 +28,8 @@ def main():
     ap.add_argument("--compare", action="store_true", help="spmm: time torch.sparse.mm on the same operands too")
     ap.add_argument("--reps", type=int, default=3)
     ap.add_argument("--variant", type=int, default=-1, help="tile configuration of the tiled forward (-1 auto)")
+    ap.add_argument("--dense-split", type=int, default=1, choices=[0, 1],
+                    help="dense_tf32: cut the tiles of the last partial wave into column slices (1, default) or not")
     args = ap.parse_args()
     if args.op == "conv":
         return conv_case(args)
@@ -45,6 +47,7 @@ def main():
     if args.variant >= 0:
         _lib.check(_lib.lib().mam_set_fwd_variant(1, args.variant), "variant")
         _lib.check(_lib.lib().mam_set_fwd_variant(0, args.variant), "variant")
+    _lib.check(_lib.lib().mam_set_fwd_variant(4, args.dense_split), "dense split")
     ops = torch.ops.mamtorch_b200
     y, imax, imin = ops.linear_forward(x, w, None, None, 1.0, 0.0, True)
     if args.op in ("csr_fwd", "spmm"):

@@ -54,6 +54,36 @@ def test_tf32_product_exact_on_small_integers(cuda):
     assert torch.equal(out, a @ w.T)
 
 
+@pytest.mark.parametrize("shape", [(1280, 96, 1280),    # 50 tiles: last wave cut in two
+                                   (1000, 512, 700),    # 24 tiles: cut in four
+                                   (4096, 256, 2560),   # 320 tiles = two whole waves + 24 tiles cut in four
+                                   (3000, 64, 5000),    # 480 tiles, ragged edges, 36 tiles cut in four
+                                   (2432, 128, 4096)])  # 304 tiles: two waves + 8 tiles cut in four
+def test_tf32_tail_slices_give_the_same_bits_as_whole_tiles(shape, cuda):
+    """Cutting the tiles of the last partial wave into column slices changes which SM computes an output, not
+    how: every output still sums its K products in the same order, so the two forms agree bit for bit."""
+    M, K, N = shape
+    L = _lib.lib()
+    g = torch.Generator().manual_seed(M + K + N)
+    a = torch.randint(-8, 9, (M, K), generator=g).float().to(cuda)
+    w = torch.randint(-8, 9, (N, K), generator=g).float().to(cuda)
+    try:
+        _lib.check(L.mam_set_fwd_variant(4, 0), "selector")
+        whole = _dense(a, w)
+        _lib.check(L.mam_set_fwd_variant(4, 1), "selector")
+        sliced = _dense(a, w)
+    finally:
+        L.mam_set_fwd_variant(4, 1)
+    torch.cuda.synchronize()
+    assert L.mam_check_device_flag() == 0
+    assert torch.equal(sliced, whole)
+    assert torch.equal(sliced, a @ w.T)      # small integers: exact in TF32, pins rows, columns and k-slices
+    ar = torch.randn(M, K, generator=g).to(cuda)
+    wr = (torch.randn(N, K, generator=g) * K ** -0.5).to(cuda)
+    base = torch.randn(M, N, generator=g).to(cuda)
+    _close(_dense(ar, wr, out=base.clone(), c_acc=0.5, c_out=2.0), 2.0 * base.double() + 0.5 * (ar.double() @ wr.double().T))
+
+
 def test_tf32_product_accumulates_into_output(cuda):
     g = torch.Generator().manual_seed(2)
     a = torch.randn(200, 64, generator=g).to(cuda)
