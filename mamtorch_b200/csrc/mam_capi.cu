@@ -329,16 +329,17 @@ int run_tiled(const float* a, const float* w, float* y, int32_t* argmax, int32_t
         if (st != MAM_OK) return st;
         const long long tiles = ((M + ResolveCfg::RM - 1) / ResolveCfg::RM) * ((N + ResolveCfg::RN - 1) / ResolveCfg::RN);
         if (tiles > 2147483647LL) return MAM_ERR_UNSUPPORTED;
+        const int rsmem = ResolveCfg::smem_bytes(nkc);
         TimedLaunch t(MAM_KERNEL_FWD_RESOLVE, cs);
         if (cv) {
             MAM_CUDA(cudaFuncSetAttribute(mam_resolve_tiled_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          ResolveCfg::SMEM_BYTES));
-            mam_resolve_tiled_kernel<true><<<(unsigned)tiles, ResolveCfg::THREADS, ResolveCfg::SMEM_BYTES, cs>>>(
+                                          rsmem));
+            mam_resolve_tiled_kernel<true><<<(unsigned)tiles, ResolveCfg::THREADS, rsmem, cs>>>(
                 tmA, tmW, argmax, argmin, M, K, N, flag, prm.conv);
         } else {
             MAM_CUDA(cudaFuncSetAttribute(mam_resolve_tiled_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          ResolveCfg::SMEM_BYTES));
-            mam_resolve_tiled_kernel<false><<<(unsigned)tiles, ResolveCfg::THREADS, ResolveCfg::SMEM_BYTES, cs>>>(
+                                          rsmem));
+            mam_resolve_tiled_kernel<false><<<(unsigned)tiles, ResolveCfg::THREADS, rsmem, cs>>>(
                 tmA, tmW, argmax, argmin, M, K, N, flag, prm.conv);
         }
     } else {

@@ -402,13 +402,17 @@ mam_fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
 // recovers the lowest true group index among those equal to the chunk extreme.
 // A min task negates its a-values (exact) and then runs the same max search as a max task.
 struct ResolveCfg {
-    static constexpr int RM = 64, RN = 128, STAGES = 2, THREADS = 256, WARPS = 8;
+    static constexpr int RM = 64, RN = 128, STAGES = 3, THREADS = 256, WARPS = 8;
     static constexpr int NK_MAX = 2048;  // K <= 65536
     static constexpr int A_BYTES = RM * FWD_BK * 4, W_BYTES = RN * FWD_BK * 4;
     static constexpr int STAGE_BYTES = A_BYTES + W_BYTES;
     static constexpr int TASKS = 2 * RM * RN;
-    static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + 2 * STAGES * 8 + 64 + TASKS * 2 +
-                                      (2 * NK_MAX + 8) * 4;
+    // bucket counters are sized by the number of chunks, so that three stages still leave room for two CTAs
+    // per SM at ordinary K (105 KB at K <= 4096; 121 KB and one CTA per SM at the 65536 limit)
+    __host__ __device__ static constexpr int nk_pad(int nk) { return (nk + 3) & ~3; }
+    static constexpr int smem_bytes(int nk) {
+        return 1024 + STAGES * STAGE_BYTES + 2 * STAGES * 8 + 64 + TASKS * 2 + (2 * nk_pad(nk) + 8) * 4;
+    }
     static constexpr int LOOKAHEAD = STAGES - 1;
 };
 
@@ -425,7 +429,8 @@ mam_resolve_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     uint64_t* empty_bar = full_bar + C::STAGES;
     unsigned short* tasks = reinterpret_cast<unsigned short*>(smem + C::STAGES * C::STAGE_BYTES + 2 * C::STAGES * 8 + 64);
     int* cursor = reinterpret_cast<int*>(tasks + C::TASKS);  // [nk]   running insert position
-    int* start = cursor + C::NK_MAX + 4;                      // [nk+1] bucket boundaries
+    const int nk_for_layout = (int)((K + FWD_BK - 1) / FWD_BK);
+    int* start = cursor + C::nk_pad(nk_for_layout) + 4;       // [nk+1] bucket boundaries
     __shared__ int warp_sums[C::WARPS];
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
