@@ -247,6 +247,17 @@ int mam_csr_fwd_f32(const float* a, const int64_t* crow, const int64_t* col, con
  * times faster (rows of a ride on the lanes, the stored weights are broadcast).  No counterpart in
  * the reference beyond the one named at mam_csr_fwd_f32. */
 size_t mam_csr_fwd_workspace_bytes(int64_t M, int64_t K, int64_t N, int64_t nnz);
+/* The same call for a weight that stays put between calls (inference on a pruned layer).  The workspace holds
+ * the regrouped weight first -- mam_csr_fwd_entries_bytes(K, N, nnz) bytes, independent of M -- and the
+ * transposed activations after it.  With entries_ready != 0 the regrouping kernels are skipped: the caller
+ * vouches that this workspace was last written by a call with the same crow / col / val contents, K, N and
+ * nnz (M may differ; the workspace must hold mam_csr_fwd_workspace_bytes for the M of this call).  With
+ * entries_ready == 0 it is mam_csr_fwd_ws_f32. */
+size_t mam_csr_fwd_entries_bytes(int64_t K, int64_t N, int64_t nnz);
+int mam_csr_fwd_ws_ex_f32(const float* a, const int64_t* crow, const int64_t* col, const float* val, int64_t nnz,
+                          const float* bias, float* y, int32_t* argmax, int32_t* argmin,
+                          int64_t M, int64_t K, int64_t N,
+                          void* workspace, size_t workspace_bytes, int entries_ready, void* stream);
 int mam_csr_fwd_ws_f32(const float* a, const int64_t* crow, const int64_t* col, const float* val, int64_t nnz,
                        const float* bias, float* y, int32_t* argmax, int32_t* argmin,
                        int64_t M, int64_t K, int64_t N,

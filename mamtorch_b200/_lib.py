@@ -44,6 +44,8 @@ ABI = {
     "mam_csr_fwd_f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "mam_csr_fwd_workspace_bytes": (ctypes.c_size_t, [_i64, _i64, _i64, _i64]),
     "mam_csr_fwd_ws_f32": (_i32, [_vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, ctypes.c_size_t, _vp]),
+    "mam_csr_fwd_ws_ex_f32": (_i32, [_vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, ctypes.c_size_t, _i32, _vp]),
+    "mam_csr_fwd_entries_bytes": (ctypes.c_size_t, [_i64, _i64, _i64]),
     "mam_spmm_csr_f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "mam_spmm_csr_workspace_bytes": (ctypes.c_size_t, [_i64, _i64, _i64, _i64]),
     "mam_spmm_csr_ws_f32": (_i32, [_vp, _vp, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _vp, ctypes.c_size_t, _vp]),

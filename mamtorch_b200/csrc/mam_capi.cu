@@ -877,13 +877,15 @@ CsrWs csr_ws_layout(int64_t M, int64_t K, int64_t N, int64_t nnz) {
     w.nks = (int)((K + CT_KS - 1) / CT_KS);
     w.pitch = (M + 3) & ~3LL;
     const size_t segs = (size_t)w.nks * (size_t)N;
+    // the regrouped weight first (nothing in it depends on M, so it can be kept from call to call while the
+    // weight stays the same), the transposed activations last
     size_t off = 0;
-    w.at_off = off;     off += round256((size_t)K * (size_t)w.pitch * 4);
     w.counts_off = off; off += round256(segs * 4);
     w.seg_off = off;    off += round256((segs + 1) * 4);
     w.k0_off = off;     off += round256((size_t)N * 4);
     w.list_off = off;   off += round256(((size_t)nnz + segs) * sizeof(CsrEntry));
     w.rlist_off = off;  off += round256(((size_t)nnz + segs) * sizeof(CsrColEntry));
+    w.at_off = off;     off += round256((size_t)K * (size_t)w.pitch * 4);
     w.total = off;
     return w;
 }
@@ -894,6 +896,11 @@ bool csr_tiled_applies(int64_t M, int64_t K, int64_t N, int64_t nnz) {
 }
 }  // namespace
 
+size_t mam_csr_fwd_entries_bytes(int64_t K, int64_t N, int64_t nnz) {
+    if (K <= 0 || N <= 0 || nnz < 0 || !csr_tiled_applies(32, K, N, nnz)) return 0;
+    return csr_ws_layout(32, K, N, nnz).at_off;
+}
+
 size_t mam_csr_fwd_workspace_bytes(int64_t M, int64_t K, int64_t N, int64_t nnz) {
     if (M <= 0 || K <= 0 || N <= 0 || nnz < 0 || !csr_tiled_applies(M, K, N, nnz)) return 0;
     return csr_ws_layout(M, K, N, nnz).total;
@@ -902,6 +909,13 @@ size_t mam_csr_fwd_workspace_bytes(int64_t M, int64_t K, int64_t N, int64_t nnz)
 int mam_csr_fwd_ws_f32(const float* a, const int64_t* crow, const int64_t* col, const float* val, int64_t nnz,
                        const float* bias, float* y, int32_t* argmax, int32_t* argmin, int64_t M, int64_t K,
                        int64_t N, void* workspace, size_t workspace_bytes, void* stream) {
+    return mam_csr_fwd_ws_ex_f32(a, crow, col, val, nnz, bias, y, argmax, argmin, M, K, N, workspace, workspace_bytes,
+                                 0, stream);
+}
+
+int mam_csr_fwd_ws_ex_f32(const float* a, const int64_t* crow, const int64_t* col, const float* val, int64_t nnz,
+                          const float* bias, float* y, int32_t* argmax, int32_t* argmin, int64_t M, int64_t K,
+                          int64_t N, void* workspace, size_t workspace_bytes, int entries_ready, void* stream) {
     if (bad_ptr(a) || bad_ptr(crow) || bad_ptr(y) || M <= 0 || K <= 0 || N <= 0 || nnz < 0)
         return MAM_ERR_INVALID_ARGUMENT;
     if ((argmax == nullptr) != (argmin == nullptr)) return MAM_ERR_INVALID_ARGUMENT;
@@ -929,12 +943,12 @@ int mam_csr_fwd_ws_f32(const float* a, const int64_t* crow, const int64_t* col, 
         if (gy > 65535) return MAM_ERR_UNSUPPORTED;
         mam_transpose_pitch_kernel<<<dim3((unsigned)gx, (unsigned)gy), 256, 0, cs>>>(a, at, M, K, w.pitch);
     }
-    // stored entries regrouped by stage
+    // stored entries regrouped by stage (kept from an earlier call when the caller says so)
     const unsigned seg_blocks = (unsigned)((segs + 255) / 256);
     const long long* crow_ll = reinterpret_cast<const long long*>(crow);
     const long long* col_ll = reinterpret_cast<const long long*>(col);
-    csr_tile_count_kernel<<<seg_blocks, 256, 0, cs>>>(crow_ll, col_ll, counts, k0, N, K, w.nks);
-    {
+    if (!entries_ready) {
+        csr_tile_count_kernel<<<seg_blocks, 256, 0, cs>>>(crow_ll, col_ll, counts, k0, N, K, w.nks);
         // counts -> seg (exclusive scan); the first words of the list area hold the per-block sums
         // until the fill kernel overwrites them
         int* block_sums = reinterpret_cast<int*>(list);
@@ -942,8 +956,8 @@ int mam_csr_fwd_ws_f32(const float* a, const int64_t* crow, const int64_t* col, 
         csr_scan_block_sums_kernel<<<(unsigned)nb, 1024, 0, cs>>>(counts, block_sums, segs);
         csr_scan_sums_kernel<<<1, 1024, 0, cs>>>(block_sums, nb);
         csr_scan_apply_kernel<<<(unsigned)nb, 1024, 0, cs>>>(counts, block_sums, seg, segs);
+        csr_tile_fill_kernel<<<seg_blocks, 256, 0, cs>>>(crow_ll, col_ll, val, seg, list, rlist, N, w.nks, 0);
     }
-    csr_tile_fill_kernel<<<seg_blocks, 256, 0, cs>>>(crow_ll, col_ll, val, seg, list, rlist, N, w.nks, 0);
     MAM_CUDA(cudaGetLastError());
 
     CUtensorMap tmAT;

@@ -490,6 +490,53 @@ std::vector<at::Tensor> csr_linear_forward(const at::Tensor& x, const at::Tensor
     return {y, amax, amin};
 }
 
+// Bytes of scratch the tiled CSR forward wants for [M,K] activations and this weight (0: the tiled kernels do not
+// apply), and how many of them hold the regrouped weight (independent of M).
+std::vector<int64_t> csr_workspace_bytes(int64_t M, int64_t K, int64_t N, int64_t nnz) {
+    return {(int64_t)mam_csr_fwd_workspace_bytes(M, K, N, nnz), (int64_t)mam_csr_fwd_entries_bytes(K, N, nnz)};
+}
+// csr_linear_forward on a scratch buffer the caller keeps: with entries_ready the regrouped weight found in
+// `workspace` (left there by an earlier call on the same CSR contents) is used as is
+std::vector<at::Tensor> csr_linear_forward_ws(const at::Tensor& x, const at::Tensor& crow, const at::Tensor& col,
+                                              const at::Tensor& val, const c10::optional<at::Tensor>& bias,
+                                              bool want_idx, at::Tensor workspace, bool entries_ready) {
+    check_matrix(x, "x");
+    TORCH_CHECK(crow.is_cuda() && col.is_cuda() && val.is_cuda(), "CSR components must be CUDA tensors");
+    TORCH_CHECK(crow.scalar_type() == at::kLong && col.scalar_type() == at::kLong, "CSR indices must be int64");
+    TORCH_CHECK(val.scalar_type() == at::kFloat, "CSR values must be float32");
+    TORCH_CHECK(crow.dim() == 1 && crow.numel() >= 1 && col.numel() == val.numel(), "malformed CSR components");
+    TORCH_CHECK(crow.is_contiguous() && col.is_contiguous() && val.is_contiguous(), "CSR components must be contiguous");
+    TORCH_CHECK(workspace.is_cuda() && workspace.scalar_type() == at::kByte && workspace.is_contiguous(),
+                "workspace must be a contiguous uint8 CUDA tensor");
+    const int64_t M = x.size(0), K = x.size(1), N = crow.numel() - 1, nnz = val.numel();
+    TORCH_CHECK(M > 0 && N > 0 && K > 0 && nnz > 0, "empty problem: use csr_linear_forward");
+    const size_t need = mam_csr_fwd_workspace_bytes(M, K, N, nnz);
+    TORCH_CHECK(need > 0 && (size_t)workspace.numel() >= need, "workspace too small for this call");
+    c10::cuda::CUDAGuard guard(x.device());
+    auto y = at::empty({M, N}, x.options());
+    at::Tensor amax, amin;
+    if (want_idx) {
+        amax = at::empty({M, N}, x.options().dtype(at::kInt));
+        amin = at::empty({M, N}, x.options().dtype(at::kInt));
+    }
+    const float* bias_p = nullptr;
+    at::Tensor bias_c;
+    if (bias.has_value() && bias->defined()) {
+        TORCH_CHECK(bias->numel() == N && bias->scalar_type() == at::kFloat && bias->is_cuda(), "bias");
+        bias_c = bias->contiguous();
+        bias_p = bias_c.data_ptr<float>();
+    }
+    auto stream = at::cuda::getCurrentCUDAStream();
+    check_status(mam_csr_fwd_ws_ex_f32(x.data_ptr<float>(), crow.data_ptr<int64_t>(), col.data_ptr<int64_t>(),
+                                       val.data_ptr<float>(), nnz, bias_p, y.data_ptr<float>(),
+                                       want_idx ? amax.data_ptr<int32_t>() : nullptr,
+                                       want_idx ? amin.data_ptr<int32_t>() : nullptr, M, K, N, workspace.data_ptr(),
+                                       (size_t)workspace.numel(), entries_ready ? 1 : 0, stream.stream()),
+                 "mam_csr_fwd_ws_ex_f32");
+    if (!want_idx) return {y};
+    return {y, amax, amin};
+}
+
 // cusparsemm(a_sparse[N,K], b[K,M]) -> dense [N,M]
 at::Tensor spmm_csr(const at::Tensor& a, const at::Tensor& b) {
     TORCH_CHECK(b.is_cuda() && b.dim() == 2 && b.scalar_type() == at::kFloat, "b must be a 2-D float CUDA tensor");
@@ -582,6 +629,8 @@ TORCH_LIBRARY(mamtorch_b200, m) {
     m.def("set_dense_backend(int backend) -> ()");
     m.def("get_dense_backend() -> int");
     m.def("csr_linear_forward(Tensor x, Tensor crow, Tensor col, Tensor val, Tensor? bias, bool want_idx) -> Tensor[]");
+    m.def("csr_linear_forward_ws(Tensor x, Tensor crow, Tensor col, Tensor val, Tensor? bias, bool want_idx, Tensor(a!) workspace, bool entries_ready) -> Tensor[]");
+    m.def("csr_workspace_bytes(int M, int K, int N, int nnz) -> int[]", &csr_workspace_bytes);
 }
 TORCH_LIBRARY_IMPL(mamtorch_b200, CUDA, m) {
     m.impl("linear_forward", &linear_forward);
@@ -597,6 +646,7 @@ TORCH_LIBRARY_IMPL(mamtorch_b200, CUDA, m) {
     m.impl("selection_hits", &selection_hits);
     m.impl("selection_count_update_", &selection_count_update_);
     m.impl("csr_linear_forward", &csr_linear_forward);
+    m.impl("csr_linear_forward_ws", &csr_linear_forward_ws);
     m.impl("dense_nt", &dense_nt);
 }
 TORCH_LIBRARY_IMPL(mamtorch_b200, CompositeExplicitAutograd, m) {

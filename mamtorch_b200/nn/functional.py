@@ -45,6 +45,14 @@ def _(x, kH, kW, sh, sw, ph, pw):
     return x.new_empty((B * Ho * Wo, C * kH * kW))
 
 
+@torch.library.register_fake("mamtorch_b200::csr_linear_forward_ws")
+def _(x, crow, col, val, bias, want_idx, workspace, entries_ready):
+    y = x.new_empty((x.size(0), crow.numel() - 1))
+    if not want_idx:
+        return [y]
+    return [y, y.new_empty(y.shape, dtype=torch.int32), y.new_empty(y.shape, dtype=torch.int32)]
+
+
 @torch.library.register_fake("mamtorch_b200::linear_forward_splits")
 def _(x, weight, bias, dense, alpha, beta, split_width):
     return x.new_empty((x.size(0), weight.size(0)))

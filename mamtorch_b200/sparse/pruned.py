@@ -71,6 +71,8 @@ class PrunedFullyConnected(nn.Module):
         self.argmax = self.argmin = None
         self._csr = None
         self._csr_key = None
+        self._ws = None          # scratch of the tiled kernels, kept between inference calls
+        self._ws_key = None      # the CSR build whose regrouped entries the scratch holds
         nn.init.kaiming_uniform_(self.weight, a=math.sqrt(5))
         if self.bias is not None:
             bound = 1 / math.sqrt(in_features) if in_features > 0 else 0
@@ -98,6 +100,7 @@ class PrunedFullyConnected(nn.Module):
             threshold = magnitude_threshold(self.weight, fraction)
         self.keep_mask.copy_(magnitude_keep_mask(self.weight, threshold))
         self._csr = None
+        self._ws_key = None
         return self
 
     def sparsity(self) -> float:
@@ -110,10 +113,36 @@ class PrunedFullyConnected(nn.Module):
             self._csr_key = key
         return self._csr
 
+    def _forward_kept_scratch(self, x: Tensor, csr: Tensor):
+        """Inference on a weight that has not changed since the last call: the regrouped entries the tiled
+        kernels work from are still in the scratch buffer, so only the activations are prepared again."""
+        ops = torch.ops.mamtorch_b200
+        crow, col, val = csr.crow_indices(), csr.col_indices(), csr.values()
+        M, K = x.shape
+        if M == 0 or val.numel() == 0:
+            return None
+        need, _ = ops.csr_workspace_bytes(M, K, self.out_features, val.numel())
+        if need == 0:
+            return None                      # the tiled kernels do not apply (few rows): no scratch involved
+        ready = (self._ws is not None and self._ws_key == self._csr_key and self._ws.numel() >= need
+                 and self._ws.device == x.device)
+        if not ready and (self._ws is None or self._ws.numel() < need or self._ws.device != x.device):
+            self._ws = torch.empty(need, dtype=torch.uint8, device=x.device)
+        out = ops.csr_linear_forward_ws(x.contiguous(), crow.contiguous(), col.contiguous(), val.contiguous(),
+                                        self.bias, True, self._ws, ready)
+        self._ws_key = self._csr_key
+        return out
+
     def forward(self, input: Tensor) -> Tensor:
         x = input.reshape(-1, input.size(-1))
-        dense = self.weight * self.keep_mask if torch.is_grad_enabled() and self.weight.requires_grad else None
-        y, self.argmax, self.argmin = mam_linear_csr(x, self._weight_csr(), self.bias, dense_weight=dense)
+        csr = self._weight_csr()
+        wants_grad = torch.is_grad_enabled() and (self.weight.requires_grad or x.requires_grad)
+        out = None if wants_grad else self._forward_kept_scratch(x, csr)
+        if out is not None:
+            y, self.argmax, self.argmin = out
+        else:
+            dense = self.weight * self.keep_mask if torch.is_grad_enabled() and self.weight.requires_grad else None
+            y, self.argmax, self.argmin = mam_linear_csr(x, csr, self.bias, dense_weight=dense)
         return y.view(input.shape[:-1] + (self.out_features,))
 
     def extra_repr(self) -> str:

@@ -182,6 +182,72 @@ def test_magnitude_pruned_layer_equals_dense_layer_on_zeroed_weight(cuda):
     assert torch.equal(thr_g, torch.quantile(both, 0.5))
 
 
+def test_pruned_layer_inference_keeps_the_regrouped_weight_between_calls(cuda):
+    """Inference calls on an unchanged weight reuse the scratch buffer's regrouped entries (only the activations
+    are prepared again); results must not depend on that, whatever the row counts in between, and a changed
+    weight or mask must be picked up."""
+    import mamtorch_b200 as mamtorch
+
+    torch.manual_seed(31)
+    K, N = 320, 150
+    dense = mamtorch.nn.FullyConnected(K, N, store_args=True).to(cuda)
+    pruned = mamtorch.sparse.PrunedFullyConnected.from_dense(dense, fraction=0.85).eval()
+
+    def reference(x):
+        w = (pruned.weight.detach() * pruned.keep_mask)
+        return torch.ops.mamtorch_b200.linear_forward(x, w, pruned.bias.detach(), None, 1.0, 0.0, True)
+
+    g = torch.Generator().manual_seed(32)
+    seen_ready = []
+    for rows in (200, 200, 64, 500, 33, 8, 200):     # same, smaller, larger (scratch regrown), below 32 rows
+        x = torch.relu(torch.randn(rows, K, generator=g)).to(cuda)
+        with torch.no_grad():
+            y = pruned(x)
+        seen_ready.append(pruned._ws_key == pruned._csr_key)
+        yr, imax, imin = reference(x)
+        assert torch.equal(y, yr) and torch.equal(pruned.argmax, imax) and torch.equal(pruned.argmin, imin)
+    assert all(seen_ready)
+    ws_before = pruned._ws
+    with torch.no_grad():
+        pruned.weight.mul_(-1.5)                      # new weight: the kept entries are stale
+        x = torch.randn(200, K, generator=g).to(cuda)
+        y = pruned(x)
+        yr, imax, imin = reference(x)
+    assert torch.equal(y, yr) and torch.equal(pruned.argmax, imax) and torch.equal(pruned.argmin, imin)
+    assert pruned._ws is ws_before                    # same buffer, rebuilt in place
+    pruned.prune_(fraction=0.5)                       # new mask
+    with torch.no_grad():
+        y = pruned(x)
+        yr, imax, imin = reference(x)
+    assert torch.equal(y, yr) and torch.equal(pruned.argmax, imax)
+    # through the C ABI: entries_ready on a workspace written by the plain call
+    import ctypes
+
+    import capi
+    from mamtorch_b200 import _lib
+
+    L = _lib.lib()
+    csr = pruned._weight_csr()
+    crow, col, val = csr.crow_indices().contiguous(), csr.col_indices().contiguous(), csr.values().contiguous()
+    nnz = val.numel()
+    need = L.mam_csr_fwd_workspace_bytes(300, K, N, nnz)
+    ent = L.mam_csr_fwd_entries_bytes(K, N, nnz)
+    assert 0 < ent < need and L.mam_csr_fwd_workspace_bytes(64, K, N, nnz) < need
+    ws = torch.empty(need, dtype=torch.uint8, device=cuda)
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    outs = []
+    for rows, ready in ((300, 0), (300, 1), (100, 1)):
+        xx = torch.randn(rows, K, generator=torch.Generator().manual_seed(rows)).to(cuda)
+        yy = torch.empty(rows, N, device=cuda)
+        ia = torch.empty(rows, N, dtype=torch.int32, device=cuda)
+        ib = torch.empty_like(ia)
+        _lib.check(L.mam_csr_fwd_ws_ex_f32(p(xx), p(crow), p(col), p(val), nnz, None, p(yy), p(ia), p(ib), rows, K, N,
+                                           p(ws), need, ready, capi._stream()), "mam_csr_fwd_ws_ex_f32")
+        w = pruned.weight.detach() * pruned.keep_mask
+        yr, imax, imin = torch.ops.mamtorch_b200.linear_forward(xx, w, None, None, 1.0, 0.0, True)
+        assert torch.equal(yy, yr) and torch.equal(ia, imax) and torch.equal(ib, imin)
+
+
 @pytest.mark.parametrize("shape,keep", [((130, 257, 200), 0.1), ((64, 64, 64), 1.0), ((1000, 700, 132), 0.02),
                                         ((33, 4100, 68), 0.3), ((256, 128, 1024), 0.0), ((9, 40, 20), 0.5)])
 def test_tiled_spmm_matches_fp64_product_and_the_row_kernel(shape, keep, cuda):
