@@ -52,7 +52,9 @@ int mam_check_device_flag(void);
  * with_indices = 0 / 1 addresses the values-only / index-producing forward.  Two more selectors ride on
  * the same call for cross-checks and timing comparisons: with_indices = 2 chooses the index resolver
  * (variant 0 = tiled, the default; 1 = one thread per output), with_indices = 3 the backward form
- * (variant 0 or 1 = single kernel, the default; 2 = separate dX and dW kernels), with_indices = 4 the
+ * (variant 0 = chosen by shape, the default; 1 = single kernel, a CTA's rows of dX shared by its warps;
+ * 2 = separate dX and dW kernels; 3 = single kernel, one row of dX per warp, the row of a parked in shared
+ * memory where it fits; 4 = as 3 with a read through L1), with_indices = 4 the
  * TF32 product's handling of its last partial wave of tiles (1 = cut them into column slices, the default;
  * 0 = whole tiles only). */
 int mam_set_fwd_variant(int with_indices, int variant);

@@ -90,6 +90,106 @@ mam_bwd_kernel(const float* __restrict__ a, const float* __restrict__ w, const f
 }
 
 // ---------------------------------------------------------------------------------------------
+// Row-per-warp form of the same pass.
+//
+// In the form above all warps of a CTA add into the same rows of da, so every addition is a
+// floating-point shared-memory atomic -- a compare-and-swap loop on this hardware, and more than half
+// of the kernel's load/store wavefronts.  Here every warp owns ONE row of a: its da row lives in
+// shared memory and only that warp touches it, so the additions are plain read-modify-writes.  What is
+// left to settle is two lanes of the same instruction naming the same k (about half of the 32-lane
+// groups hold one such pair at K = 768): match.any groups the lanes by k, the lowest lane of a group
+// collects the other lanes' terms by shuffle and adds the sum once.  A_SMEM also parks the warp's row
+// of a in shared memory, so that the two selected activations per output are shared-memory gathers
+// instead of scattered reads of a 3 KB row through L1.  The dW terms still go to L2 as
+// red.global.add.f32 (their addresses are distinct inside a warp by construction: 32 different n).
+constexpr int BWD_RW_UNROLL = 4;   // outputs in flight per lane
+
+__device__ __forceinline__ void warp_row_add(float* row, int k, bool ok, float v, int lane) {
+    // lanes with nothing to add get keys of their own so that they join no group
+    const unsigned key = ok ? (unsigned)k : (0x80000000u | (unsigned)lane);
+    const unsigned peers = __match_any_sync(0xffffffffu, key);
+    const bool leader = (__ffs(peers) - 1) == lane;
+    unsigned todo = leader ? (peers & (peers - 1)) : 0u;   // the group's other lanes
+    float s = v;
+    while (__any_sync(0xffffffffu, todo != 0u)) {
+        const int src = todo ? __ffs(todo) - 1 : lane;
+        const float t = __shfl_sync(0xffffffffu, v, src);
+        if (todo) {
+            s += t;
+            todo &= todo - 1;
+        }
+    }
+    if (ok && leader) row[k] += s;
+    __syncwarp();
+}
+
+template <bool B_NK, bool A_SMEM>
+__global__ void __launch_bounds__(BWD_THREADS)
+mam_bwd_rowwarp_kernel(const float* __restrict__ a, const float* __restrict__ w, const float* __restrict__ g,
+                       const int* __restrict__ argmax, const int* __restrict__ argmin,
+                       float* __restrict__ da, float* __restrict__ dw,
+                       long long M, long long K, long long N, float scale) {
+    extern __shared__ float rw_s[];   // per warp: da row [K] (+ a row [K])
+    constexpr int WARPS = BWD_THREADS / 32, U = BWD_RW_UNROLL;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long m = (long long)blockIdx.x * WARPS + warp;
+    if (m >= M) return;   // a whole warp leaves; nothing below synchronises across warps
+    float* dar = rw_s + (size_t)warp * (size_t)K * (A_SMEM ? 2 : 1);
+    float* as = dar + K;
+    const float* arow = a + m * K;
+    for (long long k = lane; k < K; k += 32) {
+        dar[k] = 0.f;
+        if constexpr (A_SMEM) as[k] = arow[k];
+    }
+    __syncwarp();
+    const float* grow = g + m * N;
+    const int* r1 = argmax + m * N;
+    const int* r2 = argmin + m * N;
+    for (long long nb = 0; nb < N; nb += 32 * U) {
+        float gv[U], t1[U], t2[U];
+        int k1[U], k2[U];
+        bool ok1[U], ok2[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const long long n = nb + u * 32 + lane;
+            gv[u] = 0.f;
+            k1[u] = -1;
+            k2[u] = -1;
+            if (n < N) {
+                gv[u] = __fmul_rn(grow[n], scale);
+                k1[u] = r1[n];
+                k2[u] = r2[n];
+            }
+            // an index outside [0,K) cannot come from the forward; skip it rather than fault
+            ok1[u] = (unsigned)k1[u] < (unsigned long long)K;
+            ok2[u] = (unsigned)k2[u] < (unsigned long long)K;
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const long long n = nb + u * 32 + lane;
+            t1[u] = 0.f;
+            t2[u] = 0.f;
+            if (ok1[u]) {
+                const long long wi = B_NK ? n * K + k1[u] : (long long)k1[u] * N + n;
+                t1[u] = __fmul_rn(w[wi], gv[u]);
+                atomicAdd(&dw[wi], __fmul_rn(A_SMEM ? as[k1[u]] : arow[k1[u]], gv[u]));
+            }
+            if (ok2[u]) {
+                const long long wi = B_NK ? n * K + k2[u] : (long long)k2[u] * N + n;
+                t2[u] = __fmul_rn(w[wi], gv[u]);
+                atomicAdd(&dw[wi], __fmul_rn(A_SMEM ? as[k2[u]] : arow[k2[u]], gv[u]));
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            warp_row_add(dar, k1[u], ok1[u], t1[u], lane);
+            warp_row_add(dar, k2[u], ok2[u], t2[u], lane);
+        }
+    }
+    for (long long k = lane; k < K; k += 32) da[m * K + k] = dar[k];
+}
+
+// ---------------------------------------------------------------------------------------------
 // Two-kernel form of the backward used when both operands fit the shared-memory budgets.
 //
 // fp32 atomics are the cost of this pass (shared memory ~1.7 lane-ops/clk/SM, L2 reductions ~0.8),

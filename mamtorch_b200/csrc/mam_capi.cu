@@ -354,7 +354,7 @@ int run_tiled(const float* a, const float* w, float* y, int32_t* argmax, int32_t
 }
 
 int g_dense_split = 1;  // 0: the TF32 product runs whole tiles only (cross-check / timing selector)
-int g_bwd_mode = 0;  // 0 auto, 1 force the single-kernel form, 2 force the two-kernel form
+int g_bwd_mode = 0;  // 0 auto, 1 CTA-shared rows, 2 two kernels, 3 row per warp (a parked in shared memory where it fits), 4 row per warp (a read from L1)
 
 template <bool NK>
 int launch_bwd_split(const float* a, const float* b, const float* grad, const int32_t* argmax, const int32_t* argmin,
@@ -439,8 +439,8 @@ int mam_timer_disarm(void) {
 }
 
 int mam_set_fwd_variant(int with_indices, int variant) {
-    if (with_indices == 3) {  // selects the backward form: 0 auto, 1 single kernel, 2 two kernels
-        if (variant < 0 || variant > 2) return MAM_ERR_INVALID_ARGUMENT;
+    if (with_indices == 3) {  // selects the backward form: 0 auto, 1 CTA-shared rows, 2 two kernels, 3 / 4 row per warp
+        if (variant < 0 || variant > 4) return MAM_ERR_INVALID_ARGUMENT;
         g_bwd_mode = variant;
         return MAM_OK;
     }
@@ -623,6 +623,36 @@ int mam_bwd_count_ex_f32(const float* a, const float* b, int b_layout, const flo
                                           cols, cs);
         return launch_bwd_split<false>(a, b, grad, argmax, argmin, da, db, hit_max, hit_min, scale, M, K, N, rows, cols,
                                        cs);
+    }
+    // Row-per-warp form: every warp keeps its own row of da (and, where 8 rows of each still leave room for
+    // two CTAs per SM, of a) in shared memory and needs no floating-point shared-memory atomics.
+    constexpr int RW_ROWS = BWD_THREADS / 32;
+    const size_t rw_row = (size_t)K * 4;
+    const bool rw_fits = da_layout == MAM_DA_MK && RW_ROWS * rw_row <= (size_t)d->max_smem - 1024;
+    // Measured on B200 (12608x768x3072): 0.76 ms against 0.88 ms for the CTA-shared form, which is what 154 M
+    // fp32 reductions into L2 cost at the rate the probe measures (2.0e11/s).  With K in the thousands a warp's
+    // rows leave room for too few warps per SM (0.42 against 0.23 ms at 12608x3072x768), so the automatic
+    // choice takes this form only while four CTAs still fit an SM.
+    const bool rw_auto = g_bwd_mode == 0 && 2 * RW_ROWS * rw_row <= 56 * 1024;
+    if (rw_fits && (rw_auto || g_bwd_mode == 3 || g_bwd_mode == 4)) {
+        const bool a_smem = g_bwd_mode != 4 && 2 * RW_ROWS * rw_row <= ((size_t)d->max_smem - 2048) / 2;
+        const size_t smem_rw = RW_ROWS * rw_row * (a_smem ? 2 : 1);
+        const long long grid_rw = (M + RW_ROWS - 1) / RW_ROWS;
+        if (grid_rw > 2147483647LL) return MAM_ERR_UNSUPPORTED;
+        MAM_CUDA(cudaMemsetAsync(db, 0, (size_t)K * (size_t)N * 4, cs));
+        auto launch = [&](auto kern) -> int {
+            MAM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_rw));
+            TimedLaunch t(MAM_KERNEL_BWD, cs);
+            kern<<<(unsigned)grid_rw, BWD_THREADS, smem_rw, cs>>>(a, b, grad, argmax, argmin, da, db, M, K, N, scale);
+            return MAM_OK;
+        };
+        const bool nk = b_layout == MAM_B_NK;
+        st = nk ? (a_smem ? launch(mam_bwd_rowwarp_kernel<true, true>) : launch(mam_bwd_rowwarp_kernel<true, false>))
+                : (a_smem ? launch(mam_bwd_rowwarp_kernel<false, true>) : launch(mam_bwd_rowwarp_kernel<false, false>));
+        if (st != MAM_OK) return st;
+        MAM_CUDA(cudaGetLastError());
+        if (count) return mam_selcount_i32(argmax, argmin, hit_max, hit_min, M, K, N, stream);
+        return MAM_OK;
     }
     const size_t smem = (size_t)rows * (size_t)K * 4;
     const long long grid = (M + rows - 1) / rows;

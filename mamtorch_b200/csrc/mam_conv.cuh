@@ -107,4 +107,104 @@ mam_col2im_kernel(const float* __restrict__ colsT, float* __restrict__ dx, ConvG
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Convolution backward without row gradients: dx accumulated where it lives.
+//
+// The patch-row form above hands every output pixel's K row gradients to the fold kernel through
+// memory ([K][M] floats, nine times the size of dx for a 3x3 kernel).  Here a CTA owns `th` consecutive
+// output rows of one image and keeps, in shared memory, the part of dx those rows can reach: all C
+// channels x ((th-1)*sh + kH) input rows x W columns.  Every selected pair adds its term g*w there
+// (shared-memory atomics: different outputs reach the same input pixel) and its term g*x to dW in L2;
+// at the end the region is added into dx, four floats per reduction where the rows allow it --
+// neighbouring CTAs overlap by kH - sh input rows, so dx is zero-filled first and every CTA adds.
+// Per selected k the channel / tap arithmetic comes from a table built once per CTA.
+struct ConvDirectEntry {
+    int roff;   // (c*RH + kh)*W + kw : offset inside the region, before the pixel's own (row, column) shift
+    int goff;   // (c*H + kh)*W + kw  : the same inside the image
+    int khkw;   // kh | kw << 16
+    int pad;
+};
+constexpr int CONV_DIRECT_THREADS = 512;
+
+__global__ void __launch_bounds__(CONV_DIRECT_THREADS)
+mam_conv_bwd_direct_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ g,
+                           const int* __restrict__ argmax, const int* __restrict__ argmin,
+                           float* __restrict__ dx, float* __restrict__ dw, ConvGeom cg, long long N, int th,
+                           float scale) {
+    extern __shared__ __align__(16) unsigned char cd_smem[];
+    const int K = cg.C * cg.kH * cg.kW, taps = cg.kH * cg.kW;
+    const int RH = (th - 1) * cg.sh + cg.kH;
+    const int region = cg.C * RH * cg.W;
+    float* reg = reinterpret_cast<float*>(cd_smem);
+    ConvDirectEntry* tab = reinterpret_cast<ConvDirectEntry*>(cd_smem + (((size_t)region * 4 + 15) & ~(size_t)15));
+    const int hblocks = (cg.Ho + th - 1) / th;
+    const int ho0 = (blockIdx.x % hblocks) * th;
+    const long long b = blockIdx.x / hblocks;
+    const int nrows = min(th, cg.Ho - ho0);
+    const int h_lo = ho0 * cg.sh - cg.ph;               // image row of region row 0 (may be negative)
+    for (int i = threadIdx.x; i < region; i += CONV_DIRECT_THREADS) reg[i] = 0.f;
+    for (int k = threadIdx.x; k < K; k += CONV_DIRECT_THREADS) {
+        const int c = k / taps, r = k - c * taps;
+        const int kh = r / cg.kW, kw = r - kh * cg.kW;
+        tab[k] = ConvDirectEntry{(c * RH + kh) * cg.W + kw, (c * cg.H + kh) * cg.W + kw, kh | (kw << 16), 0};
+    }
+    __syncthreads();
+    const float* xb = x + b * (long long)cg.C * cg.H * cg.W;
+    const long long m0 = (b * cg.Ho + ho0) * (long long)cg.Wo;
+    const long long outputs = (long long)nrows * cg.Wo * N;   // the tile's outputs are one contiguous run
+    const float* gt = g + m0 * N;
+    const int* r1 = argmax + m0 * N;
+    const int* r2 = argmin + m0 * N;
+    for (long long o = threadIdx.x; o < outputs; o += CONV_DIRECT_THREADS) {
+        const int p = (int)(o / N);                     // pixel inside the tile
+        const long long n = o - (long long)p * N;
+        const int hl = p / cg.Wo, wo = p - hl * cg.Wo;
+        const int hs = hl * cg.sh;                      // region row of the patch's first row
+        const int w0 = wo * cg.sw - cg.pw;              // image column of the patch's first column
+        const float gv = g ? gt[o] * scale : 0.f;
+        const int k1 = r1[o], k2 = r2[o];
+        // an index outside [0,K) cannot come from the forward; skip it rather than fault
+#pragma unroll
+        for (int side = 0; side < 2; ++side) {
+            const int k = side ? k2 : k1;
+            if ((unsigned)k >= (unsigned)K) continue;
+            const ConvDirectEntry e = tab[k];
+            const int kh = e.khkw & 0xffff, kw = e.khkw >> 16;
+            const int h = h_lo + hs + kh, ww = w0 + kw;
+            // a selected padding position multiplied a zero: it has no pixel to send a gradient to
+            if ((unsigned)h >= (unsigned)cg.H || (unsigned)ww >= (unsigned)cg.W) continue;
+            const long long wi = n * K + k;
+            atomicAdd(&reg[e.roff + hs * cg.W + w0], __fmul_rn(w[wi], gv));
+            atomicAdd(&dw[wi], __fmul_rn(xb[e.goff + (h_lo + hs) * cg.W + w0], gv));
+        }
+    }
+    __syncthreads();
+    // region -> dx: rows of the region that lie inside the image, all channels
+    float* dxb = dx + b * (long long)cg.C * cg.H * cg.W;
+    const int rh_first = max(0, -h_lo), rh_last = min(RH, cg.H - h_lo);   // [first, last)
+    const int live = rh_last - rh_first;
+    if (live <= 0) return;
+    if ((cg.W & 3) == 0) {
+        const int w4 = cg.W >> 2, per_c = live * w4;
+        for (int i = threadIdx.x; i < cg.C * per_c; i += CONV_DIRECT_THREADS) {
+            const int c = i / per_c, r = i - c * per_c;
+            const int rh = rh_first + r / w4, q = r - (r / w4) * w4;
+            const float4 v = *reinterpret_cast<const float4*>(reg + (c * RH + rh) * cg.W + q * 4);
+            if (v.x == 0.f && v.y == 0.f && v.z == 0.f && v.w == 0.f) continue;
+            float* dst = dxb + ((long long)c * cg.H + (h_lo + rh)) * cg.W + q * 4;
+            asm volatile("red.global.v4.f32.add [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(v.x), "f"(v.y), "f"(v.z),
+                         "f"(v.w)
+                         : "memory");
+        }
+    } else {
+        const int per_c = live * cg.W;
+        for (int i = threadIdx.x; i < cg.C * per_c; i += CONV_DIRECT_THREADS) {
+            const int c = i / per_c, r = i - c * per_c;
+            const int rh = rh_first + r / cg.W, ww = r - (r / cg.W) * cg.W;
+            const float v = reg[(c * RH + rh) * cg.W + ww];
+            if (v != 0.f) atomicAdd(dxb + ((long long)c * cg.H + (h_lo + rh)) * cg.W + ww, v);
+        }
+    }
+}
+
 }  // namespace mamb200

@@ -55,7 +55,9 @@ def cases():
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("MAMTORCH_REFERENCE_DIR")
+    if not ref_root:
+        raise SystemExit("usage: make_golden.py /path/to/mamtorch   (or set MAMTORCH_REFERENCE_DIR)")
     sys.path.insert(0, os.path.join(ref_root, "test"))
     from reference import fullyconnected_backward_reference, fullyconnected_reference
 

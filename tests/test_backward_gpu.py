@@ -38,11 +38,13 @@ def test_blend_scale(cuda):
     assert_grad_close(db.cpu().numpy(), g["bgrad"])
 
 
-@pytest.mark.parametrize("mode", [1, 2])
-@pytest.mark.parametrize("shape", [(700, 768, 520), (33, 3000, 40), (2048, 64, 96)])
+@pytest.mark.parametrize("mode", [0, 1, 2, 3, 4])
+@pytest.mark.parametrize("shape", [(700, 768, 520), (33, 3000, 40), (2048, 64, 96), (300, 5, 257), (67, 1, 70)])
 def test_random_backward_against_c_oracle(shape, mode, cuda):
-    """mode 1 = single kernel (da in shared memory, dW by L2 reductions); mode 2 = two kernels
-    (row-owned da, column-owned dW), the form used for large M."""
+    """mode 0 = the library's own choice; 1 = single kernel, the rows of da shared by a CTA (shared-memory
+    atomics), dW by L2 reductions; 2 = two kernels (row-owned da, column-owned dW); 3 / 4 = one row of da per
+    warp, lanes that name the same k merged by match + shuffle (3 also parks the row of a in shared memory).
+    The shapes with K = 5 and K = 1 put many lanes of a warp on the same k."""
     M, K, N = shape
     gen = torch.Generator().manual_seed(M + K + N)
     a = torch.randn(M, K, generator=gen)
