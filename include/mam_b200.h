@@ -56,7 +56,8 @@ int mam_check_device_flag(void);
  * 2 = separate dX and dW kernels; 3 = single kernel, one row of dX per warp, the row of a parked in shared
  * memory where it fits; 4 = as 3 with a read through L1), with_indices = 4 the
  * TF32 product's handling of its last partial wave of tiles (1 = cut them into column slices, the default;
- * 0 = whole tiles only). */
+ * 0 = whole tiles only), with_indices = 5 the output rows per CTA of mam_conv_bwd_direct_f32 (0 = chosen by
+ * shared-memory size, the default). */
 int mam_set_fwd_variant(int with_indices, int variant);
 const char* mam_fwd_variant_name(int with_indices, int variant);
 
@@ -185,6 +186,22 @@ int mam_conv_bwd_f32(const float* x, const float* w, const float* grad,
                      float* cols_t, float* dw, float scale,
                      int64_t B, int64_t C, int64_t H, int64_t W,
                      int kH, int kW, int sh, int sw, int ph, int pw, int64_t N, void* stream);
+
+/* The same backward WITHOUT the transposed row gradients: dx[B,C,H,W] and dw[N, C*kH*kW] in one kernel.  A CTA
+ * owns a few consecutive output rows of one image, sums in shared memory the part of dx they reach (all
+ * channels x the input rows under those output rows x W) and adds it into dx with reductions (dx and dw are
+ * zero-filled by the call; sums are formed in another order than mam_conv_bwd_f32 + mam_col2im_f32, so the
+ * two agree to rounding).  mam_conv_bwd_direct_applies() answers without a device whether the geometry fits:
+ * C * kH * W * 4 bytes plus the 16-byte-per-k table must fit one CTA's shared memory (226 KiB); otherwise
+ * MAM_ERR_UNSUPPORTED and the caller takes the two-step form.  Stands in for the same reference text as
+ * mam_conv_bwd_f32 (mamtorch/kernel/backup/mamconv2d_backward.txt:21-124). */
+int mam_conv_bwd_direct_applies(int64_t B, int64_t C, int64_t H, int64_t W, int kH, int kW, int sh, int sw,
+                                int ph, int pw);
+int mam_conv_bwd_direct_f32(const float* x, const float* w, const float* grad,
+                            const int32_t* argmax, const int32_t* argmin,
+                            float* dx, float* dw, float scale,
+                            int64_t B, int64_t C, int64_t H, int64_t W,
+                            int kH, int kW, int sh, int sw, int ph, int pw, int64_t N, void* stream);
 
 /* Forward of the MAM convolution WITHOUT materialised patch rows: the tiled kernels fetch every 32-channel
  * chunk of the patch rows from the channels-last input x_nhwc[B,H,W,C] by im2col-mode TMA

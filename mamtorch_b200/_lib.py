@@ -32,6 +32,8 @@ ABI = {
     "mam_bwd_count_f32": (_i32, [_vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f32, _i64, _i64, _i64, _vp]),
     "mam_bwd_count_ex_f32": (_i32, [_vp, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _f32, _i64, _i64, _i64, _vp]),
     "mam_conv_bwd_f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _f32, _i64, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _i64, _vp]),
+    "mam_conv_bwd_direct_f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _f32, _i64, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _i64, _vp]),
+    "mam_conv_bwd_direct_applies": (_i32, [_i64, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _i32, _i32]),
     "mam_fwd_splits_f32": (_i32, [_vp, _vp, _vp, _vp, _i32, _f32, _f32, _vp, _i64, _i64, _i64, _i64, _vp]),
     "mam_nchw_to_nhwc_f32": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _vp]),
     "mam_conv_fwd_applies": (_i32, [_i64, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _i32, _i32]),

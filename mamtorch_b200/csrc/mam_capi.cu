@@ -354,6 +354,7 @@ int run_tiled(const float* a, const float* w, float* y, int32_t* argmax, int32_t
 }
 
 int g_dense_split = 1;  // 0: the TF32 product runs whole tiles only (cross-check / timing selector)
+int g_conv_direct_rows = 0;  // 0 auto, else output rows per CTA of mam_conv_bwd_direct_kernel (if they fit)
 int g_bwd_mode = 0;  // 0 auto, 1 CTA-shared rows, 2 two kernels, 3 row per warp (a parked in shared memory where it fits), 4 row per warp (a read from L1)
 
 template <bool NK>
@@ -442,6 +443,11 @@ int mam_set_fwd_variant(int with_indices, int variant) {
     if (with_indices == 3) {  // selects the backward form: 0 auto, 1 CTA-shared rows, 2 two kernels, 3 / 4 row per warp
         if (variant < 0 || variant > 4) return MAM_ERR_INVALID_ARGUMENT;
         g_bwd_mode = variant;
+        return MAM_OK;
+    }
+    if (with_indices == 5) {  // one-kernel convolution backward: output rows per CTA (0 = chosen by shared-memory size)
+        if (variant < 0 || variant > 64) return MAM_ERR_INVALID_ARGUMENT;
+        g_conv_direct_rows = variant;
         return MAM_OK;
     }
     if (with_indices == 4) {  // TF32 product: 1 (default) slices the tiles of the last partial wave, 0 does not
@@ -693,6 +699,25 @@ int conv_geom(ConvGeom* g, int64_t B, int64_t C, int64_t H, int64_t W, int kH, i
     *g = ConvGeom{(int)B, (int)C, (int)H, (int)W, kH, kW, sh, sw, ph, pw, (int)Ho, (int)Wo};
     return MAM_OK;
 }
+// Shared memory of mam_conv_bwd_direct_kernel for `th` output rows per CTA: the region of dx they reach plus
+// the per-k table.
+size_t conv_direct_smem(const ConvGeom& g, int th) {
+    const size_t region = (size_t)g.C * (size_t)((th - 1) * g.sh + g.kH) * (size_t)g.W * 4;
+    return ((region + 15) & ~size_t(15)) + (size_t)g.C * g.kH * g.kW * sizeof(ConvDirectEntry);
+}
+// Output rows per CTA: as many as keep the CTA under 84 KB (two CTAs per SM with room to spare, so that one
+// CTA's flush overlaps the other's sweep; measured at [128,64,56,56] 3x3 -> 128: 1 to 3 rows 1.54-1.55 ms,
+// 4 rows 1.63, 8 rows 1.83), at most 8; a single row may use the whole SM; 0 = the region does not fit.
+int conv_direct_rows(const ConvGeom& g) {
+    if ((long long)g.C * g.H * g.W >= (1LL << 31) || (long long)g.kW >= 32768 || (long long)g.kH >= 65536) return 0;
+    if (g_conv_direct_rows > 0 && conv_direct_smem(g, g_conv_direct_rows) <= 226 * 1024)
+        return g_conv_direct_rows < g.Ho ? g_conv_direct_rows : g.Ho;
+    int th = 0;
+    for (int t = 1; t <= 8 && t <= g.Ho; ++t)
+        if (conv_direct_smem(g, t) <= 84 * 1024) th = t;
+    if (th == 0 && conv_direct_smem(g, 1) <= 226 * 1024) th = 1;
+    return th;
+}
 }  // namespace
 
 int mam_conv_bwd_f32(const float* x, const float* w, const float* grad, const int32_t* argmax, const int32_t* argmin,
@@ -767,6 +792,42 @@ int mam_im2col_f32(const float* x, float* rows, int64_t B, int64_t C, int64_t H,
     const long long blocks = (long long)g.B * g.Ho;
     if (blocks > 2147483647LL) return MAM_ERR_UNSUPPORTED;
     mam_im2col_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(x, rows, g);
+    MAM_CUDA(cudaGetLastError());
+    return MAM_OK;
+}
+
+int mam_conv_bwd_direct_applies(int64_t B, int64_t C, int64_t H, int64_t W, int kH, int kW, int sh, int sw, int ph,
+                                int pw) {
+    ConvGeom g;
+    if (conv_geom(&g, B, C, H, W, kH, kW, sh, sw, ph, pw) != MAM_OK) return 0;
+    return conv_direct_rows(g) > 0 ? 1 : 0;
+}
+
+int mam_conv_bwd_direct_f32(const float* x, const float* w, const float* grad, const int32_t* argmax,
+                            const int32_t* argmin, float* dx, float* dw, float scale, int64_t B, int64_t C, int64_t H,
+                            int64_t W, int kH, int kW, int sh, int sw, int ph, int pw, int64_t N, void* stream) {
+    if (bad_ptr(x) || bad_ptr(w) || bad_ptr(grad) || bad_ptr(argmax) || bad_ptr(argmin) || bad_ptr(dx) ||
+        bad_ptr(dw) || N <= 0)
+        return MAM_ERR_INVALID_ARGUMENT;
+    ConvGeom g;
+    int st = conv_geom(&g, B, C, H, W, kH, kW, sh, sw, ph, pw);
+    if (st != MAM_OK) return st;
+    const long long K = (long long)g.C * g.kH * g.kW;
+    if (N >= (1LL << 31) / K) return MAM_ERR_UNSUPPORTED;
+    const int th = conv_direct_rows(g);
+    if (th <= 0) return MAM_ERR_UNSUPPORTED;
+    const long long grid = (long long)g.B * ((g.Ho + th - 1) / th);
+    if (grid > 2147483647LL) return MAM_ERR_UNSUPPORTED;
+    const size_t smem = conv_direct_smem(g, th);
+    cudaStream_t cs = (cudaStream_t)stream;
+    MAM_CUDA(cudaMemsetAsync(dw, 0, (size_t)K * (size_t)N * 4, cs));
+    MAM_CUDA(cudaMemsetAsync(dx, 0, (size_t)g.B * g.C * g.H * g.W * 4, cs));
+    MAM_CUDA(cudaFuncSetAttribute(mam_conv_bwd_direct_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    {
+        TimedLaunch t(MAM_KERNEL_BWD, cs);
+        mam_conv_bwd_direct_kernel<<<(unsigned)grid, CONV_DIRECT_THREADS, smem, cs>>>(
+            x, w, grad, argmax, argmin, dx, dw, g, N, th, scale, (g.W % 4 == 0 && aligned16(dx)) ? 1 : 0);
+    }
     MAM_CUDA(cudaGetLastError());
     return MAM_OK;
 }

@@ -125,12 +125,13 @@ struct ConvDirectEntry {
     int pad;
 };
 constexpr int CONV_DIRECT_THREADS = 512;
+constexpr int CONV_DIRECT_UNROLL = 2;   // outputs in flight per lane
 
-__global__ void __launch_bounds__(CONV_DIRECT_THREADS)
+__global__ void __launch_bounds__(CONV_DIRECT_THREADS, 2)
 mam_conv_bwd_direct_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ g,
                            const int* __restrict__ argmax, const int* __restrict__ argmin,
                            float* __restrict__ dx, float* __restrict__ dw, ConvGeom cg, long long N, int th,
-                           float scale) {
+                           float scale, int vec4) {
     extern __shared__ __align__(16) unsigned char cd_smem[];
     const int K = cg.C * cg.kH * cg.kW, taps = cg.kH * cg.kW;
     const int RH = (th - 1) * cg.sh + cg.kH;
@@ -151,31 +152,71 @@ mam_conv_bwd_direct_kernel(const float* __restrict__ x, const float* __restrict_
     __syncthreads();
     const float* xb = x + b * (long long)cg.C * cg.H * cg.W;
     const long long m0 = (b * cg.Ho + ho0) * (long long)cg.Wo;
-    const long long outputs = (long long)nrows * cg.Wo * N;   // the tile's outputs are one contiguous run
     const float* gt = g + m0 * N;
     const int* r1 = argmax + m0 * N;
     const int* r2 = argmin + m0 * N;
-    for (long long o = threadIdx.x; o < outputs; o += CONV_DIRECT_THREADS) {
-        const int p = (int)(o / N);                     // pixel inside the tile
-        const long long n = o - (long long)p * N;
+    // a warp takes one output pixel at a time and its lanes walk the pixel's N outputs (one coalesced run)
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int npix = nrows * cg.Wo;
+    for (int p = warp; p < npix; p += CONV_DIRECT_THREADS / 32) {
         const int hl = p / cg.Wo, wo = p - hl * cg.Wo;
         const int hs = hl * cg.sh;                      // region row of the patch's first row
         const int w0 = wo * cg.sw - cg.pw;              // image column of the patch's first column
-        const float gv = g ? gt[o] * scale : 0.f;
-        const int k1 = r1[o], k2 = r2[o];
-        // an index outside [0,K) cannot come from the forward; skip it rather than fault
+        const int rshift = hs * cg.W + w0;              // the pixel's shift inside the region ...
+        const int gshift = (h_lo + hs) * cg.W + w0;     // ... and inside the image
+        const long long row = (long long)p * N;
+        // CONV_DIRECT_UNROLL outputs per lane at a time, in three phases -- the streamed reads, the four
+        // gathers per output, the additions -- so that the loads of a phase are in flight together
+        // (atomics in between would keep the compiler from hoisting them)
+        constexpr int U = CONV_DIRECT_UNROLL;
+        const int Ni = (int)N;   // N * K < 2^31 (checked by the host): 32-bit offsets into w / dw
+        for (int nb = 0; nb < Ni; nb += 32 * U) {
+            float gv[U];
+            int ks[2 * U];
 #pragma unroll
-        for (int side = 0; side < 2; ++side) {
-            const int k = side ? k2 : k1;
-            if ((unsigned)k >= (unsigned)K) continue;
-            const ConvDirectEntry e = tab[k];
-            const int kh = e.khkw & 0xffff, kw = e.khkw >> 16;
-            const int h = h_lo + hs + kh, ww = w0 + kw;
-            // a selected padding position multiplied a zero: it has no pixel to send a gradient to
-            if ((unsigned)h >= (unsigned)cg.H || (unsigned)ww >= (unsigned)cg.W) continue;
-            const long long wi = n * K + k;
-            atomicAdd(&reg[e.roff + hs * cg.W + w0], __fmul_rn(w[wi], gv));
-            atomicAdd(&dw[wi], __fmul_rn(xb[e.goff + (h_lo + hs) * cg.W + w0], gv));
+            for (int u = 0; u < U; ++u) {
+                const int n = nb + u * 32 + lane;
+                gv[u] = 0.f;
+                ks[2 * u] = -1;
+                ks[2 * u + 1] = -1;
+                if (n < Ni) {
+                    gv[u] = __fmul_rn(gt[row + n], scale);
+                    ks[2 * u] = r1[row + n];
+                    ks[2 * u + 1] = r2[row + n];
+                }
+            }
+            int ra[2 * U];          // index inside the region, -1 = nothing to add
+            int wi[2 * U];
+            float wv[2 * U], xv[2 * U];
+#pragma unroll
+            for (int j = 0; j < 2 * U; ++j) {
+                const int k = ks[j];
+                const int n = nb + (j >> 1) * 32 + lane;
+                ra[j] = -1;
+                wi[j] = 0;
+                wv[j] = 0.f;
+                xv[j] = 0.f;
+                // an index outside [0,K) cannot come from the forward; skip it rather than fault
+                if ((unsigned)k < (unsigned)K) {
+                    const ConvDirectEntry e = tab[k];
+                    const int kh = e.khkw & 0xffff, kw = e.khkw >> 16;
+                    const int h = h_lo + hs + kh, ww = w0 + kw;
+                    // a selected padding position multiplied a zero: it has no pixel to send a gradient to
+                    if ((unsigned)h < (unsigned)cg.H && (unsigned)ww < (unsigned)cg.W) {
+                        ra[j] = e.roff + rshift;
+                        wi[j] = n * K + k;
+                        wv[j] = w[wi[j]];
+                        xv[j] = xb[e.goff + gshift];
+                    }
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 2 * U; ++j) {
+                if (ra[j] >= 0) {
+                    atomicAdd(&reg[ra[j]], __fmul_rn(wv[j], gv[j >> 1]));
+                    atomicAdd(&dw[wi[j]], __fmul_rn(xv[j], gv[j >> 1]));
+                }
+            }
         }
     }
     __syncthreads();
@@ -184,7 +225,7 @@ mam_conv_bwd_direct_kernel(const float* __restrict__ x, const float* __restrict_
     const int rh_first = max(0, -h_lo), rh_last = min(RH, cg.H - h_lo);   // [first, last)
     const int live = rh_last - rh_first;
     if (live <= 0) return;
-    if ((cg.W & 3) == 0) {
+    if (vec4) {   // W % 4 == 0 and dx 16-byte aligned: every row of the region starts on a 16-byte boundary
         const int w4 = cg.W >> 2, per_c = live * w4;
         for (int i = threadIdx.x; i < cg.C * per_c; i += CONV_DIRECT_THREADS) {
             const int c = i / per_c, r = i - c * per_c;

@@ -408,6 +408,43 @@ std::vector<at::Tensor> conv_backward(const at::Tensor& x, const at::Tensor& w2d
                  "mam_conv_bwd_f32");
     return {cols_t, dw};
 }
+// Whether conv_backward_direct can take a convolution of this geometry (no device needed).
+bool conv_direct_applies(int64_t B, int64_t C, int64_t H, int64_t W, int64_t kH, int64_t kW, int64_t sh, int64_t sw,
+                         int64_t ph, int64_t pw) {
+    return mam_conv_bwd_direct_applies(B, C, H, W, (int)kH, (int)kW, (int)sh, (int)sw, (int)ph, (int)pw) != 0;
+}
+// {dx [B,C,H,W], dw [N, C*kH*kW]}: convolution backward in one kernel, dx summed per tile of output rows
+std::vector<at::Tensor> conv_backward_direct(const at::Tensor& x, const at::Tensor& w2d, const at::Tensor& grad,
+                                             const at::Tensor& argmax, const at::Tensor& argmin, double scale,
+                                             int64_t kH, int64_t kW, int64_t sh, int64_t sw, int64_t ph, int64_t pw) {
+    TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kFloat && x.dim() == 4, "x must be a float32 CUDA [B,C,H,W] tensor");
+    check_matrix(w2d, "weight");
+    check_matrix(grad, "grad");
+    check_matrix(argmax, "argmax", at::kInt);
+    check_matrix(argmin, "argmin", at::kInt);
+    auto xc = x.contiguous();
+    const int64_t B = xc.size(0), C = xc.size(1), H = xc.size(2), W = xc.size(3);
+    const int64_t Ho = (H + 2 * ph - kH) / sh + 1, Wo = (W + 2 * pw - kW) / sw + 1;
+    const int64_t M = B * Ho * Wo, K = C * kH * kW, N = w2d.size(0);
+    TORCH_CHECK(w2d.size(1) == K, "weight must be [N, C*kH*kW]");
+    TORCH_CHECK(grad.size(0) == M && grad.size(1) == N, "grad must be [B*Ho*Wo, N]");
+    TORCH_CHECK(argmax.sizes() == grad.sizes() && argmin.sizes() == grad.sizes(), "index shapes must match grad");
+    c10::cuda::CUDAGuard guard(x.device());
+    auto dx = at::empty_like(xc);
+    auto dw = at::empty_like(w2d);
+    if (M == 0 || N == 0 || K == 0) {
+        dx.zero_();
+        dw.zero_();
+        return {dx, dw};
+    }
+    auto stream = at::cuda::getCurrentCUDAStream();
+    check_status(mam_conv_bwd_direct_f32(xc.data_ptr<float>(), w2d.data_ptr<float>(), grad.data_ptr<float>(),
+                                         argmax.data_ptr<int32_t>(), argmin.data_ptr<int32_t>(), dx.data_ptr<float>(),
+                                         dw.data_ptr<float>(), (float)scale, B, C, H, W, (int)kH, (int)kW, (int)sh,
+                                         (int)sw, (int)ph, (int)pw, N, stream.stream()),
+                 "mam_conv_bwd_direct_f32");
+    return {dx, dw};
+}
 // {dx transposed [K,M], dw}: the backward of linear_forward with the row gradients laid out for conv_col2im
 std::vector<at::Tensor> linear_backward_km(const at::Tensor& x, const at::Tensor& weight, const at::Tensor& grad,
                                            const at::Tensor& argmax, const at::Tensor& argmin, double scale) {
@@ -618,6 +655,8 @@ TORCH_LIBRARY(mamtorch_b200, m) {
     m.def("linear_backward_km(Tensor x, Tensor weight, Tensor grad, Tensor argmax, Tensor argmin, float scale) -> Tensor[]");
     m.def("conv_backward(Tensor x, Tensor weight, Tensor grad, Tensor argmax, Tensor argmin, float scale, int kH, int kW, int sh, int sw, int ph, int pw) -> Tensor[]");
     m.def("conv_im2col(Tensor x, int kH, int kW, int sh, int sw, int ph, int pw) -> Tensor");
+    m.def("conv_backward_direct(Tensor x, Tensor weight, Tensor grad, Tensor argmax, Tensor argmin, float scale, int kH, int kW, int sh, int sw, int ph, int pw) -> Tensor[]");
+    m.def("conv_direct_applies(int B, int C, int H, int W, int kH, int kW, int sh, int sw, int ph, int pw) -> bool", &conv_direct_applies);
     m.def("linear_forward_splits(Tensor x, Tensor weight, Tensor? bias, Tensor? dense, float alpha, float beta, int split_width) -> Tensor");
     m.def("conv_channels_last(Tensor x) -> Tensor");
     m.def("conv_forward_implicit(Tensor x_nhwc, Tensor w_taps, Tensor? bias, Tensor? dense, float alpha, float beta, int kH, int kW, int sh, int sw, int ph, int pw, bool need_indices) -> Tensor[]");
@@ -638,6 +677,7 @@ TORCH_LIBRARY_IMPL(mamtorch_b200, CUDA, m) {
     m.impl("linear_backward_count", &linear_backward_count);
     m.impl("linear_backward_km", &linear_backward_km);
     m.impl("conv_backward", &conv_backward);
+    m.impl("conv_backward_direct", &conv_backward_direct);
     m.impl("conv_im2col", &conv_im2col);
     m.impl("conv_forward_implicit", &conv_forward_implicit);
     m.impl("conv_channels_last", &conv_channels_last);

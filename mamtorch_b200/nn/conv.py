@@ -37,7 +37,20 @@ from . import functional as MF
 
 _ops = torch.ops.mamtorch_b200
 
-__all__ = ["MAMConv1d", "MAMConv2d", "mam_conv2d", "tap_order_permutation", "to_legacy_index"]
+__all__ = ["MAMConv1d", "MAMConv2d", "mam_conv2d", "tap_order_permutation", "to_legacy_index",
+           "set_conv_backward_form"]
+
+
+# "auto": the one-kernel backward where its tile of dx fits shared memory, else transposed row gradients +
+# fold; "fold": always the latter (kept for cross-checks and timing comparisons).
+_backward_form = "auto"
+
+
+def set_conv_backward_form(form: str) -> None:
+    global _backward_form
+    if form not in ("auto", "fold"):
+        raise ValueError("form must be 'auto' or 'fold'")
+    _backward_form = form
 
 
 def _pair(v):
@@ -77,9 +90,13 @@ class _MamConv2d(torch.autograd.Function):
         g2d = gy.permute(0, 2, 3, 1).reshape(B * Ho * Wo, Fo).contiguous()
         dx = dw = dbias = ddense = None
         if ctx.needs_input_grad[0] or ctx.needs_input_grad[1]:
-            cols_t, dw2d = _ops.conv_backward(x, w2d, g2d, amax, amin, ctx.alpha, kH, kW, sh, sw, ph, pw)
-            if ctx.needs_input_grad[0]:
-                dx = _ops.conv_col2im(cols_t, B, C, H, W, kH, kW, sh, sw, ph, pw)
+            if _backward_form != "fold" and _ops.conv_direct_applies(B, C, H, W, kH, kW, sh, sw, ph, pw):
+                # one kernel: dx summed in shared memory per tile of output rows, no row gradients in memory
+                dx, dw2d = _ops.conv_backward_direct(x, w2d, g2d, amax, amin, ctx.alpha, kH, kW, sh, sw, ph, pw)
+            else:
+                cols_t, dw2d = _ops.conv_backward(x, w2d, g2d, amax, amin, ctx.alpha, kH, kW, sh, sw, ph, pw)
+                if ctx.needs_input_grad[0]:
+                    dx = _ops.conv_col2im(cols_t, B, C, H, W, kH, kW, sh, sw, ph, pw)
             dw = dw2d.view(Fo, C, kH, kW)
         if ctx.has_bias and ctx.needs_input_grad[2]:
             dbias = g2d.sum(0)

@@ -74,6 +74,11 @@ def _(x_nhwc, w_taps, bias, dense, alpha, beta, kH, kW, sh, sw, ph, pw, need_ind
     return [y, y.new_empty(y.shape, dtype=torch.int32), y.new_empty(y.shape, dtype=torch.int32)]
 
 
+@torch.library.register_fake("mamtorch_b200::conv_backward_direct")
+def _(x, weight, grad, argmax, argmin, scale, kH, kW, sh, sw, ph, pw):
+    return [torch.empty_like(x, memory_format=torch.contiguous_format), torch.empty_like(weight)]
+
+
 @torch.library.register_fake("mamtorch_b200::conv_col2im")
 def _(cols_t, B, C, H, W, kH, kW, sh, sw, ph, pw):
     return cols_t.new_empty((B, C, H, W))

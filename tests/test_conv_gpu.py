@@ -98,9 +98,73 @@ def test_conv_backward_from_the_input_equals_backward_on_patch_rows(geom, cuda):
     assert_grad_close(dw_b.cpu().numpy(), dw_a.cpu().numpy())
 
 
-def test_strided_padded_conv_module_gradients(cuda):
-    import mamtorch_b200 as mamtorch
+DIRECT_GEOMS = GEOMS + [
+    (2, 8, 12, 16, 3, 3, 1, 1, 1, 1),      # W % 4 == 0: the tile goes out four floats per reduction
+    (2, 4, 13, 12, 3, 3, 2, 2, 1, 1),      # stride 2, several tiles of output rows per image
+    (1, 3, 40, 8, 5, 1, 1, 1, 2, 0),       # more output rows than one tile holds, tall kernel
+    (3, 2, 6, 5, 2, 2, 1, 1, 3, 3),        # padding wider than the kernel: whole patches in the padding
+]
 
+
+@pytest.mark.parametrize("geom", DIRECT_GEOMS)
+def test_one_kernel_conv_backward_equals_row_gradients_plus_fold(geom, cuda):
+    """mam_conv_bwd_direct_f32 sums dx per tile of output rows in shared memory and adds the tiles into dx;
+    mam_conv_bwd_f32 + mam_col2im_f32 go through the transposed row gradients.  Same sums in another order:
+    dx and dW agree to rounding.  A few outputs get the same index on both sides (counted twice) and one row of
+    outputs gets indices outside [0, K), which both forms skip."""
+    B, C, H, W, kH, kW, sh, sw, ph, pw = geom
+    L = _lib.lib()
+    assert L.mam_conv_bwd_direct_applies(B, C, H, W, kH, kW, sh, sw, ph, pw) == 1
+    g = torch.Generator().manual_seed(3 + sum(geom))
+    x = torch.randn(B, C, H, W, generator=g).to(cuda)
+    Ho, Wo = (H + 2 * ph - kH) // sh + 1, (W + 2 * pw - kW) // sw + 1
+    M, K, N = B * Ho * Wo, C * kH * kW, 37
+    w = (torch.randn(N, K, generator=g) * K ** -0.5).to(cuda)
+    gy = torch.randn(M, N, generator=g).to(cuda)
+    rows = torch.empty(M, K, device=cuda)
+    _lib.check(L.mam_im2col_f32(_p(x), _p(rows), B, C, H, W, kH, kW, sh, sw, ph, pw, capi._stream()), "mam_im2col_f32")
+    _, imax, imin = capi.forward(rows, w, capi.NK)
+    imin[0, :] = imax[0, :]
+    imax[M - 1, :] = K + 5
+    imin[M - 1, :] = -1
+    ct, dw_a = torch.empty(K, M, device=cuda), torch.empty_like(w)
+    dx_a = torch.empty_like(x)
+    _lib.check(L.mam_conv_bwd_f32(_p(x), _p(w), _p(gy), _p(imax), _p(imin), _p(ct), _p(dw_a), 0.5, B, C, H, W, kH, kW,
+                                  sh, sw, ph, pw, N, capi._stream()), "mam_conv_bwd_f32")
+    _lib.check(L.mam_col2im_f32(_p(ct), _p(dx_a), B, C, H, W, kH, kW, sh, sw, ph, pw, capi._stream()), "mam_col2im_f32")
+    for _ in range(2):   # twice: the call zero-fills what it accumulates into
+        dx_b, dw_b = torch.full_like(x, 7.0), torch.full_like(w, 7.0)
+        _lib.check(L.mam_conv_bwd_direct_f32(_p(x), _p(w), _p(gy), _p(imax), _p(imin), _p(dx_b), _p(dw_b), 0.5, B, C, H,
+                                             W, kH, kW, sh, sw, ph, pw, N, capi._stream()), "mam_conv_bwd_direct_f32")
+        assert_grad_close(dx_b.cpu().numpy(), dx_a.cpu().numpy())
+        assert_grad_close(dw_b.cpu().numpy(), dw_a.cpu().numpy())
+
+
+def test_one_kernel_conv_backward_declines_what_does_not_fit(cuda):
+    L = _lib.lib()
+    # 4096 channels x 3 input rows x 64 columns of fp32 = 3 MiB: no tile of dx fits a CTA's shared memory
+    assert L.mam_conv_bwd_direct_applies(1, 4096, 64, 64, 3, 3, 1, 1, 1, 1) == 0
+    assert L.mam_conv_bwd_direct_applies(128, 64, 56, 56, 3, 3, 1, 1, 1, 1) == 1
+    t = torch.zeros(16, device=cuda)
+    i = torch.zeros(16, dtype=torch.int32, device=cuda)
+    st = L.mam_conv_bwd_direct_f32(_p(t), _p(t), _p(t), _p(i), _p(i), _p(t), _p(t), 1.0, 1, 4096, 64, 64, 3, 3, 1, 1, 1,
+                                   1, 8, capi._stream())
+    assert st == 2   # MAM_ERR_UNSUPPORTED
+
+
+@pytest.mark.parametrize("form", ["auto", "fold"])
+def test_strided_padded_conv_module_gradients(form, cuda):
+    import mamtorch_b200 as mamtorch
+    from mamtorch_b200.nn.conv import set_conv_backward_form
+
+    set_conv_backward_form(form)
+    try:
+        _strided_padded_conv_module_gradients(mamtorch, cuda)
+    finally:
+        set_conv_backward_form("auto")
+
+
+def _strided_padded_conv_module_gradients(mamtorch, cuda):
     torch.manual_seed(11)
     conv = mamtorch.nn.MAMConv2d(6, 5, (3, 2), stride=(2, 1), padding=(1, 0)).to(cuda)
     x = torch.randn(3, 6, 9, 7, generator=torch.Generator().manual_seed(12)).to(cuda).requires_grad_()
