@@ -90,7 +90,8 @@ class _MamConv2d(torch.autograd.Function):
         g2d = gy.permute(0, 2, 3, 1).reshape(B * Ho * Wo, Fo).contiguous()
         dx = dw = dbias = ddense = None
         if ctx.needs_input_grad[0] or ctx.needs_input_grad[1]:
-            if _backward_form != "fold" and _ops.conv_direct_applies(B, C, H, W, kH, kW, sh, sw, ph, pw):
+            if (_backward_form != "fold" and Fo * C * kH * kW < 2 ** 31
+                    and _ops.conv_direct_applies(B, C, H, W, kH, kW, sh, sw, ph, pw)):
                 # one kernel: dx summed in shared memory per tile of output rows, no row gradients in memory
                 dx, dw2d = _ops.conv_backward_direct(x, w2d, g2d, amax, amin, ctx.alpha, kH, kW, sh, sw, ph, pw)
             else:
