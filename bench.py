@@ -565,10 +565,10 @@ def main():
     sel_bytes = 8 * mn + 8 * 2 * D_MODEL * D_FF
     line["kernels_ms_per_step"] = {"forward_main_loop": 2 * kavg, **other_ms}
     line["roofline_other_kernels"] = [
-        {"kernel": "mam_bwd_kernel", "bound": "hbm", "achieved": bwd_bytes / (other_ms["backward_scatter"] * 1e-3) / 1e9,
+        {"kernel": "mam_bwd_rowwarp_kernel (768 -> 3072) + mam_bwd_kernel (3072 -> 768)", "bound": "hbm", "achieved": bwd_bytes / (other_ms["backward_scatter"] * 1e-3) / 1e9,
          "peak": hbm_peak, "unit": "GB/s", "frac": bwd_bytes / (other_ms["backward_scatter"] * 1e-3) / 1e9 / hbm_peak,
-         "note": "12*M*N + 8*(M*K + N*K) bytes per layer; in practice bound by the LSU data pipe (uncoalesced gathers, "
-                 "fp32 atomics), see profiles/step_kernels_4736x768x3072.md"},
+         "note": "12*M*N + 8*(M*K + N*K) bytes per layer; in practice bound by the rate of scattered fp32 reductions "
+                 "into L2 (2*M*N per layer) and the LSU data pipe, see profiles/step_kernels_4736x768x3072.md"},
         {"kernel": "mam_selcount_kernel", "bound": "hbm", "achieved": sel_bytes / (other_ms["selection_hits"] * 1e-3) / 1e9,
          "peak": hbm_peak, "unit": "GB/s", "frac": sel_bytes / (other_ms["selection_hits"] * 1e-3) / 1e9 / hbm_peak,
          "note": "8*M*N + 8*N*K bytes per layer"}]
