@@ -635,8 +635,8 @@ int mam_bwd_count_ex_f32(const float* a, const float* b, int b_layout, const flo
     constexpr int RW_ROWS = BWD_THREADS / 32;
     const size_t rw_row = (size_t)K * 4;
     const bool rw_fits = da_layout == MAM_DA_MK && RW_ROWS * rw_row <= (size_t)d->max_smem - 1024;
-    // Measured on B200 (12608x768x3072): 0.76 ms against 0.88 ms for the CTA-shared form, which is what 154 M
-    // fp32 reductions into L2 cost at the rate the probe measures (2.0e11/s).  With K in the thousands a warp's
+    // Measured on B200 (12608x768x3072): 0.76 ms against 0.88 ms for the CTA-shared form, which is what its 155 M
+    // scattered L2 sector operations (weight gathers + fp32 reductions) cost at the 2.0e11/s the probe measures.  With K in the thousands a warp's
     // rows leave room for too few warps per SM (0.42 against 0.23 ms at 12608x3072x768), so the automatic
     // choice takes this form only while four CTAs still fit an SM.
     const bool rw_auto = g_bwd_mode == 0 && 2 * RW_ROWS * rw_row <= 56 * 1024;
