@@ -635,11 +635,12 @@ int mam_bwd_count_ex_f32(const float* a, const float* b, int b_layout, const flo
     constexpr int RW_ROWS = BWD_THREADS / 32;
     const size_t rw_row = (size_t)K * 4;
     const bool rw_fits = da_layout == MAM_DA_MK && RW_ROWS * rw_row <= (size_t)d->max_smem - 1024;
-    // Measured on B200 (12608x768x3072): 0.76 ms against 0.88 ms for the CTA-shared form, which is what its 155 M
-    // scattered L2 sector operations (weight gathers + fp32 reductions) cost at the 2.0e11/s the probe measures.  With K in the thousands a warp's
-    // rows leave room for too few warps per SM (0.42 against 0.23 ms at 12608x3072x768), so the automatic
-    // choice takes this form only while four CTAs still fit an SM.
-    const bool rw_auto = g_bwd_mode == 0 && 2 * RW_ROWS * rw_row <= 56 * 1024;
+    // Measured on B200 against the CTA-shared form (NK layout, 12608 rows): K x N = 768 x 3072 0.76 vs 0.88 ms
+    // (its 155 M scattered L2 sector operations -- weight gathers + fp32 reductions -- at the 2.0e11/s the probe
+    // measures), 1024 x 4096 1.12 vs 1.22; but 512 x 2048 0.62 vs 0.58 (per row the zero / stage / write-out of K
+    // floats weighs more), 896 x 3584 1.10 vs 1.03, 1280 x 5120 1.95 vs 1.30, 3072 x 768 0.42 vs 0.23 (a warp's rows
+    // leave room for too few warps per SM).  The automatic choice takes this form only in the band where it won.
+    const bool rw_auto = g_bwd_mode == 0 && K >= 640 && K <= 832;
     if (rw_fits && (rw_auto || g_bwd_mode == 3 || g_bwd_mode == 4)) {
         const bool a_smem = g_bwd_mode != 4 && 2 * RW_ROWS * rw_row <= ((size_t)d->max_smem - 2048) / 2;
         const size_t smem_rw = RW_ROWS * rw_row * (a_smem ? 2 : 1);
