@@ -148,6 +148,24 @@ def test_implicit_convolution_applicability_needs_no_device():
     assert L.mam_conv_fwd_f32(one, one, null, null, 0, 1.0, 0.0, one, one, null, 8, 64, 56, 56, 3, 3, 1, 1, 1, 1, 8, null) == 1
 
 
+def test_one_kernel_conv_backward_applicability_and_argument_checks_need_no_device():
+    L = _lib.lib()
+    ok = L.mam_conv_bwd_direct_applies
+    assert ok(128, 64, 56, 56, 3, 3, 1, 1, 1, 1) == 1          # the benchmark convolution
+    assert ok(1, 1, 1, 1, 1, 1, 1, 1, 0, 0) == 1
+    assert ok(8, 512, 14, 14, 3, 3, 1, 1, 1, 1) == 1           # 512 channels x 3 rows x 14 columns = 86 KB
+    assert ok(1, 4096, 64, 64, 3, 3, 1, 1, 1, 1) == 0          # one output row's tile of dx exceeds a CTA's shared memory
+    assert ok(1, 3, 2, 2, 5, 5, 1, 1, 0, 0) == 0               # kernel larger than the padded input: no geometry
+    assert ok(0, 3, 8, 8, 3, 3, 1, 1, 1, 1) == 0
+    # null pointers are refused before any device work
+    st = L.mam_conv_bwd_direct_f32(None, None, None, None, None, None, None, 1.0, 1, 3, 8, 8, 3, 3, 1, 1, 1, 1, 4, None)
+    assert st == 1   # MAM_ERR_INVALID_ARGUMENT
+    from mamtorch_b200.nn.conv import set_conv_backward_form
+    with pytest.raises(ValueError):
+        set_conv_backward_form("scatter")
+    set_conv_backward_form("auto")
+
+
 def test_tap_order_permutation_and_legacy_index():
     from mamtorch_b200.nn.conv import tap_order_permutation, to_legacy_index
 
