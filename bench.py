@@ -1,12 +1,12 @@
 #!/usr/bin/env python
 """Benchmark of the MAM hot path on B200.
 
-Workload (N GPUs, weak scaling: every rank owns the same number of rows): the ViT-B/16-shaped
-MAM MLP pair of the reference's headline configuration -- tokens M = 64 x 197 = 12608 per rank,
-layer 1 K=768 -> N=3072, layer 2 K=3072 -> N=768, fp32, x ~ N(0,1), W ~ N(0,1/K), forward with
-arg-indices + selected-pair backward + selection-count accumulation, synthetic data.  With N > 1
-the two weight gradients are summed over ranks with one NCCL all-reduce each (the only exchange a
-row-sharded layer has).
+Headline workload (N GPUs, weak scaling: every rank owns the same number of rows): the
+ViT-B/16-shaped MAM MLP pair -- tokens M = 64 x 197 = 12608 per rank, layer 1 K=768 -> N=3072,
+layer 2 K=3072 -> N=768, fp32, x ~ N(0,1), W ~ N(0,1/K), forward with arg-indices + selected-pair
+backward + selection-count accumulation, synthetic data.  With N > 1 the weight gradients are
+summed over ranks with NCCL, each as soon as its layer's backward has produced it, on NCCL's own
+stream, so that the exchange runs under the rest of the backward.
 
 One JSON line on stdout (rank 0).  `value` counts (m,n,k) units -- one multiply, one max update,
 one min update -- of the two forward passes, divided by the whole forward+backward step time:
@@ -15,12 +15,20 @@ upstream gradient start in pinned host memory and its output and loss come back 
 inside the timed region.  `roofline` is for the dominant kernel (the tiled forward), timed with
 CUDA events recorded by the library around each of its launches during the timed steps.
 
+The same line carries `north_star_configs`: the other configurations the path is specified on,
+each measured in this run with CUDA events (max over ranks) -- the 4096^3 forward (values only;
+with indices: main loop and index resolver), the convolution and the beta-blended training step
+(one GPU only), and the large sharded pruned layer at this N (65536 rows split over the ranks,
+strong scaling, dW all-reduced) with the time of its all-reduce alone.
+
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
-`--impl reference` times the CPU restatement of the reference's own torch path (oracle/) on the
-host cores on a bounded row sample of the same workload.  `--impl reference_cuda` (an extra arm, not
-part of the default run) times the reference's own CUDA operators on the GPU where
-oracle/build_ref_cuda.py has built them.
+`--impl reference` times the reference's own CPU torch path on the host cores on a bounded row
+sample of the same workload: the reference's checker functions byte-compiled into oracle/_ref/ where
+that was built, else their restatement in oracle/mam_oracle.py.  `--impl reference_cuda` (an extra
+arm, not part of the default run) times the reference's own CUDA operators on the GPU where
+oracle/build_ref_cuda.py has built them.  `--case OP --shape ...` runs one operation a few times and
+prints its time: the small, bounded command that profiler captures are taken on.
 """
 import argparse
 import ctypes
@@ -41,16 +49,23 @@ METRIC = "mam_mlp_pair_fwd_bwd_throughput"
 UNIT = "G(mul+max/min)/s"
 WORKLOAD = ("ViT-B/16 MAM MLP pair fwd+bwd, fp32, M=12608 tokens per rank, 768->3072->768, "
             "arg-indices, selected-pair backward, selection count on")
-
-
 M_TOTAL_OUTPUTS = M_TOKENS * (D_FF + D_MODEL)   # outputs of both layers per rank
+
+# DRAM bytes (read + write) of one launch of the index-tracking forward at M=4736, K=768, N=3072, from a
+# profiler capture of `bench.py --case step --shape 4736x768x3072 --reps 1`: 24.1 MB read (of which the
+# 9.4 MB weight does not depend on M) + 122.5 MB written.  The rest grows with the rows, so a launch at M rows
+# moves about 9.4 MB + 137.2 MB * M / 4736.
+TRAFFIC_CAPTURED_ROWS, TRAFFIC_CAPTURED_BYTES, TRAFFIC_WEIGHT_BYTES = 4736, 1.372e8, 9.4e6
+
+SHARDED_M, SHARDED_K, SHARDED_N, SHARDED_SPARSITY = 65536, 4096, 4096, 0.9
+CONV_SHAPE = (128, 64, 56, 56, 128)      # B, C, H, W, F; 3x3, stride 1, padding 1
 
 
 def measured_hbm_gbs() -> float:
     """Copy bandwidth measured on this pool's B200s (MEASURED_PEAKS.json beside this file), else the
     6650 GB/s of an earlier measurement."""
     try:
-        with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")) as f:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
             return float(json.load(f)["hbm_gbs"])
     except (OSError, KeyError, ValueError):
         return 6650.0
@@ -59,9 +74,9 @@ def measured_hbm_gbs() -> float:
 def fp32_peaks(sms: int, mhz: float):
     lanes = sms * 128 * mhz * 1e6
     # mix_ceiling: what the (mul, max, min) instruction mix can sustain on sm_100a, measured with
-    # independent instruction streams (profiles/pipe_probe_b200.md): the min/max pipe shares its
-    # datapath with half of the fp32 multiply throughput -> 3 cycles per unit per warp = 128/3
-    # units/clk/SM, numerically the non-FMA issue peak.
+    # independent instruction streams: the min/max pipe shares its datapath with half of the fp32
+    # multiply throughput -> 3 cycles per unit per warp = 128/3 units/clk/SM, numerically the
+    # non-FMA issue peak.
     return {"fma_counted_tflops": 2 * lanes / 1e12, "non_fma_tops": lanes / 1e12,
             "mix_ceiling_gunits": sms * (128.0 / 3.0) * mhz * 1e6 / 1e9}
 
@@ -101,15 +116,77 @@ class ClockSampler:
                 "samples": len(sm), "reasons": reasons}
 
 
-def cpu_reference_sample(rows: int, repeats: int):
-    """The reference's CPU torch path (restated in oracle/mam_oracle.py) on `rows` rows of both
-    layers, forward + backward.  Returns (G units/s, threads, description)."""
+def bind_to_gpu_numa_node(local: int) -> None:
+    """Best effort: run this rank's host threads (and so first-touch its pinned buffers) on the NUMA
+    node its GPU hangs off, so that eight ranks do not pull their host copies through one node."""
+    try:
+        import torch
+
+        bus = torch.cuda.get_device_properties(local).pci_bus_id
+        dom = torch.cuda.get_device_properties(local).pci_domain_id
+        dev = torch.cuda.get_device_properties(local).pci_device_id
+        path = f"/sys/bus/pci/devices/{dom:04x}:{bus:02x}:{dev:02x}.0/numa_node"
+        node = int(open(path).read().strip())
+        if node < 0:
+            return
+        cpus = set()
+        for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = cpus & os.sched_getaffinity(0)
+        if allowed:
+            os.sched_setaffinity(0, allowed)
+    except (OSError, ValueError, AttributeError, RuntimeError):
+        pass
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU legs: the reference's own torch path on the host cores
+# ------------------------------------------------------------------------------------------------
+class CpuPath:
+    """The reference's CPU functions: its own checker (`test/reference.py`, byte-compiled into
+    oracle/_ref/reference.pyc by oracle/build_ref_py.py where a checkout was at hand when the tree was
+    built; kind "reference") or their restatement in oracle/mam_oracle.py (kind "port")."""
+
+    def __init__(self):
+        import torch
+
+        self.threads = os.cpu_count() or 1
+        torch.set_num_threads(self.threads)
+        self.kind, self._ref = "port", None
+        pyc = os.path.join(ROOT, "oracle", "_ref", "reference.pyc")
+        if os.path.exists(pyc):
+            try:
+                import importlib.machinery
+                import importlib.util
+
+                loader = importlib.machinery.SourcelessFileLoader("mamtorch_reference_checker", pyc)
+                spec = importlib.util.spec_from_loader("mamtorch_reference_checker", loader)
+                mod = importlib.util.module_from_spec(spec)
+                loader.exec_module(mod)
+                self._ref, self.kind = mod, "reference"
+            except Exception:  # noqa: BLE001  (a .pyc of another interpreter version: fall back to the port)
+                self._ref = None
+        if self._ref is None:
+            from oracle import mam_oracle
+
+            self._port = mam_oracle
+
+    def forward(self, a, b, beta=0.0):
+        if self._ref is not None:
+            return self._ref.fullyconnected_reference(a, b, 0.0, beta)
+        return self._port.mam_forward(a, b, beta=beta)
+
+    def backward(self, a, b, g, imax, imin, beta=0.0):
+        if self._ref is not None:
+            return self._ref.fullyconnected_backward_reference(a, b, g, imax, imin, beta)
+        return self._port.mam_backward(a, b, g, imax, imin, beta=beta)
+
+
+def cpu_mlp_pair_sample(cpu: CpuPath, rows: int, repeats: int):
+    """`rows` rows of both layers of the headline workload, forward + backward.  Returns (G units/s, text)."""
     import torch
 
-    from oracle import mam_oracle
-
-    threads = os.cpu_count() or 1
-    torch.set_num_threads(threads)
     g = torch.Generator().manual_seed(0)
     x = torch.randn(rows, D_MODEL, generator=g)
     w1 = torch.randn(D_FF, D_MODEL, generator=g) * D_MODEL ** -0.5
@@ -120,124 +197,478 @@ def cpu_reference_sample(rows: int, repeats: int):
     best = None
     for _ in range(repeats):
         t0 = time.perf_counter()
-        h, i1, j1 = mam_oracle.mam_forward(x, b1)
-        y, i2, j2 = mam_oracle.mam_forward(h, b2)
-        dh, dw2 = mam_oracle.mam_backward(h, b2, gy, i2, j2)
-        dx, dw1 = mam_oracle.mam_backward(x, b1, dh, i1, j1)
+        h, i1, j1 = cpu.forward(x, b1)
+        y, i2, j2 = cpu.forward(h, b2)
+        dh, dw2 = cpu.backward(h, b2, gy, i2, j2)
+        dx, dw1 = cpu.backward(x, b1, dh, i1, j1)
         dt = time.perf_counter() - t0
         best = dt if best is None else min(best, dt)
-    return units / best / 1e9, threads, f"{rows} of {M_TOKENS} rows of both layers, fwd+bwd, torch CPU, best of {repeats}"
+    return units / best / 1e9, f"{rows} of {M_TOKENS} rows of both layers, fwd+bwd, torch CPU, best of {repeats}"
+
+
+def cpu_layer_sample(cpu: CpuPath, rows: int, K: int, N: int, beta: float, sparsity: float, x_std: float, w_std: float):
+    """`rows` rows of one layer, forward + backward, optionally on a pruned (zeroed) weight or blended
+    with the dense term.  Returns seconds."""
+    import torch
+
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(rows, K, generator=g) * x_std
+    w = torch.randn(N, K, generator=g) * w_std
+    if sparsity > 0:
+        w = w * (torch.rand(N, K, generator=g) >= sparsity).float()
+    gy = torch.randn(rows, N, generator=g)
+    b = w.T.contiguous()
+    t0 = time.perf_counter()
+    y, i1, j1 = cpu.forward(x, b, beta)
+    cpu.backward(x, b, gy, i1, j1, beta)
+    return time.perf_counter() - t0
+
+
+def cpu_conv_sample(cpu: CpuPath, images: int, out_rows: int):
+    """The convolution's CPU path: F.unfold + the reference functions on the first `out_rows` output
+    pixels of `images` images (the reference has no executable convolution).  Returns seconds."""
+    import torch
+
+    from oracle import mam_oracle
+
+    B, C, H, W, Fo = CONV_SHAPE
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(images, C, H, W, generator=g)
+    w = torch.randn(Fo, C, 3, 3, generator=g) * (C * 9) ** -0.5
+    t0 = time.perf_counter()
+    rows = mam_oracle.conv2d_as_rows(x, (3, 3), stride=1, padding=1)[:out_rows].contiguous()
+    gy = torch.randn(rows.size(0), Fo, generator=g)
+    b = w.reshape(Fo, -1).T.contiguous()
+    y, i1, j1 = cpu.forward(rows, b)
+    cpu.backward(rows, b, gy, i1, j1)
+    return time.perf_counter() - t0
 
 
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    rows = 128
-    # warm-up + K timed "steps", each one bounded sample
+    cpu = CpuPath()
+    rows = 64
     for _ in range(max(1, min(args.warmup, 2))):
-        cpu_reference_sample(rows, 1)
+        cpu_mlp_pair_sample(cpu, rows, 1)
     t0 = time.perf_counter()
-    vals = [cpu_reference_sample(rows, 1) for _ in range(args.steps)]
+    vals = [cpu_mlp_pair_sample(cpu, rows, 1) for _ in range(args.steps)]
     wall = time.perf_counter() - t0
     value = statistics.median(v[0] for v in vals)
-    threads, sample = vals[0][1], vals[0][2]
+    sample = vals[0][1]
+    how = ("the reference's own checker functions (test/reference.py, byte-compiled)" if cpu.kind == "reference"
+           else "CPU restatement of the reference's torch path")
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": wall / args.steps * 1e3,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "note": "CPU restatement of the reference's torch path; each step is a "
-                       f"{rows}-row sample of the workload, throughput is per-unit so it compares directly"},
-            "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+            "config": {"workload": WORKLOAD, "note": f"{how}; each step is a {rows}-row sample of the workload, "
+                       "throughput is per unit so it compares directly"},
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": cpu.threads, "kind": cpu.kind, "sample": sample},
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line), flush=True)
 
 
-def run_sharded_sparse(args):
-    """The large sharded configuration: one MAM layer, M = 65536 rows split by rank, K = N = 4096, W pruned
-    to 90 % sparsity (uniform random mask) and stored as CSR; forward with indices through the tiled CSR
-    kernels, backward through the selected-pair scatter (dW dense), dW summed over the ranks with NCCL.
-    Total work is fixed, so the scaling is strong.  Prints one JSON line with the same keys as the
-    headline run (without the per-kernel roofline, which profiles/mam_csr_fwd_2048x4096x4096.md covers)."""
+# ------------------------------------------------------------------------------------------------
+# GPU helpers
+# ------------------------------------------------------------------------------------------------
+class Dist:
+    """Rank bookkeeping + barrier + max-over-ranks event timing."""
+
+    def __init__(self, args):
+        import torch
+        import torch.distributed as dist
+
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.local = int(os.environ.get("LOCAL_RANK", "0"))
+        assert self.world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={self.world} (launch with torch.distributed.run)"
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py needs a CUDA device: there is no CPU path")
+        torch.cuda.set_device(self.local)
+        self.dev = torch.device("cuda", self.local)
+        if self.world > 1:     # (a single rank keeps every core: it also times the CPU path)
+            bind_to_gpu_numa_node(self.local)
+        if self.world > 1:
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            dist.init_process_group("nccl", device_id=self.dev)
+        self.dist = dist
+
+    def barrier(self):
+        import torch
+
+        if self.world > 1:
+            self.dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(self, fn, steps):
+        """Milliseconds for `steps` calls of fn: CUDA events, barrier + synchronize on both sides, max over ranks."""
+        import torch
+
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        self.barrier()
+        ev0.record()
+        for _ in range(steps):
+            fn()
+        ev1.record()
+        self.barrier()
+        ms = torch.tensor([ev0.elapsed_time(ev1)], device=self.dev)
+        if self.world > 1:
+            self.dist.all_reduce(ms, op=self.dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    def close(self):
+        if self.world > 1:
+            self.dist.destroy_process_group()
+
+
+class LibTimer:
+    """Per-launch CUDA events recorded by the library around one class of its kernels."""
+
+    def __init__(self, L, capacity):
+        import torch
+
+        self.L, self.cap = L, capacity
+        self.pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(capacity)]
+        for a, b in self.pairs:   # events are created lazily on first record; force creation now
+            a.record()
+            b.record()
+        torch.cuda.synchronize()
+        self.starts = (ctypes.c_void_p * capacity)(*[ctypes.c_void_p(a.cuda_event) for a, _ in self.pairs])
+        self.stops = (ctypes.c_void_p * capacity)(*[ctypes.c_void_p(b.cuda_event) for _, b in self.pairs])
+
+    def arm(self, kernel_id):
+        from mamtorch_b200 import _lib
+
+        _lib.check(self.L.mam_timer_arm(self.starts, self.stops, self.cap, kernel_id), "mam_timer_arm")
+
+    def collect(self):
+        import torch
+
+        n = self.L.mam_timer_disarm()
+        torch.cuda.synchronize()
+        return [a.elapsed_time(b) for a, b in self.pairs[:n]]
+
+
+def bench_fwd_4096(D: Dist, L, sms, max_mhz, reps=8):
+    """The 4096^3 forward on one GPU: values only, and with indices (main loop and resolver apart)."""
     import torch
-    import torch.distributed as dist
+
+    from mamtorch_b200 import _lib
+
+    n = 4096
+    gen = torch.Generator(device=D.dev).manual_seed(4096)
+    x = torch.randn(n, n, generator=gen, device=D.dev)
+    w = torch.randn(n, n, generator=gen, device=D.dev) * n ** -0.5
+    ops = torch.ops.mamtorch_b200
+    timer = LibTimer(L, 2 * reps)
+    units = float(n) ** 3
+    peaks = fp32_peaks(sms, max_mhz)
+
+    def run(want_idx, kid):
+        for _ in range(3):
+            ops.linear_forward(x, w, None, None, 1.0, 0.0, want_idx)
+        timer.arm(kid)
+        for _ in range(reps):
+            ops.linear_forward(x, w, None, None, 1.0, 0.0, want_idx)
+        ms = timer.collect()
+        return statistics.mean(ms) if ms else float("nan")
+
+    def fractions(ms):
+        tf = 3.0 * units / (ms * 1e-3) / 1e12
+        return {"ms": ms, "t_units_per_s": units / (ms * 1e-3) / 1e12, "tflops_3_per_unit": tf,
+                "frac_of_fma_counted_peak": tf / peaks["fma_counted_tflops"],
+                "frac_of_non_fma_peak": tf / peaks["non_fma_tops"]}
+
+    val_ms = run(False, 0)
+    idx_main_ms = run(True, 0)
+    idx_res_ms = run(True, 1)
+    _lib.check(L.mam_check_device_flag(), "device wait flag")
+    return {"shape": "M=N=K=4096, x ~ N(0,1), W ~ N(0,1/K), fp32",
+            "timing": f"library-recorded CUDA events per launch, mean of {reps} launches after 3 warm-ups",
+            "peaks": {"fma_counted_tflops": peaks["fma_counted_tflops"], "non_fma_tops": peaks["non_fma_tops"],
+                      "source": f"{sms} SMs x 128 lanes x {max_mhz:.0f} MHz (x 2 counting an FMA as two)"},
+            "values_only": fractions(val_ms),
+            "with_indices": {"main_loop": fractions(idx_main_ms), "index_resolver_ms": idx_res_ms,
+                             "total": fractions(idx_main_ms + idx_res_ms)}}
+
+
+def bench_sharded_sparse(D: Dist, L, steps=5, warmup=3):
+    """The large sharded layer at this world size: 65536 rows split by rank (strong scaling), K = N = 4096,
+    W pruned to 90 % (uniform random mask, CSR), forward with indices through the CSR kernels, backward
+    through the selected-pair scatter (dW dense), dW summed over the ranks with NCCL."""
+    import torch
 
     import mamtorch_b200 as mamtorch
     from mamtorch_b200 import _lib
     from mamtorch_b200.dist import row_shard
 
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world} (launch with torch.distributed.run)"
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: there is no CPU path")
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
-    M_TOTAL, K, N = 65536, 4096, 4096
-    lo, hi = row_shard(M_TOTAL, world, rank)
+    M_TOTAL, K, N = SHARDED_M, SHARDED_K, SHARDED_N
+    lo, hi = row_shard(M_TOTAL, D.world, D.rank)
     rows = hi - lo
     g = torch.Generator().manual_seed(0)
     w = torch.randn(N, K, generator=g) * K ** -0.5
-    keep = (torch.rand(N, K, generator=g) >= 0.9).float()          # as test/test_sparse.py:13-16 of the reference
-    wz = (w * keep).to(dev).requires_grad_()
-    w_csr = wz.detach().to_sparse_csr()
-    nnz = int(w_csr.values().numel())
-    gd = torch.Generator().manual_seed(100 + rank)
-    x = torch.randn(rows, K, generator=gd).to(dev)
-    gy = torch.randn(rows, N, generator=gd).to(dev)
+    keep = (torch.rand(N, K, generator=g) >= SHARDED_SPARSITY).float()   # the mask rule of test/test_sparse.py:13-16
+    layer = mamtorch.sparse.PrunedFullyConnected(K, N, bias=False, device=D.dev)
+    with torch.no_grad():
+        layer.weight.copy_(w)
+        layer.keep_mask.copy_(keep)
+    nnz = int(keep.sum().item())
+    gd = torch.Generator(device=D.dev).manual_seed(100 + D.rank)
+    x = torch.randn(rows, K, generator=gd, device=D.dev)
+    gy = torch.randn(rows, N, generator=gd, device=D.dev)
 
     def step():
-        wz.grad = None
+        # a training step of the pruned layer: the kept values are gathered and regrouped again every step (an
+        # optimiser would have moved them), the sparsity pattern is kept from step to step
+        layer.weight.grad = None
         xl = x.detach().requires_grad_()
-        y, _, _ = mamtorch.sparse.kernel.v1.mam_linear_csr(xl, w_csr, None, dense_weight=wz)
+        y = layer(xl)
         y.backward(gy)
-        if world > 1:
-            dist.all_reduce(wz.grad)
+        if D.world > 1:
+            D.dist.all_reduce(layer.weight.grad)
         return y
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
+    for _ in range(warmup):
+        step()
+    ms = D.timed(step, steps) / steps
+    ar_ms = None
+    if D.world > 1:
+        buf = torch.empty_like(layer.weight)
+        for _ in range(2):
+            D.dist.all_reduce(buf)
+        ar_ms = D.timed(lambda: D.dist.all_reduce(buf), 5) / 5
+    _lib.check(L.mam_check_device_flag(), "device wait flag")
+    out = {"workload": "M=65536 rows split by rank, K=N=4096 fp32, W pruned to 90 % (uniform random mask, CSR rows), "
+                       "fwd with indices + selected-pair bwd, dW all-reduced",
+           "scaling": "strong", "rows_per_rank": rows, "nnz": nnz, "steps": steps, "warmup": warmup,
+           "ms_per_step": ms,
+           "value": M_TOTAL * nnz / (ms * 1e-3) / 1e9, "unit": "G(row, stored weight) units/s over all ranks",
+           "dense_equivalent_gunits": M_TOTAL * K * N / (ms * 1e-3) / 1e9,
+           "dw_allreduce_bytes": 4 * N * K, "dw_allreduce_alone_ms": ar_ms}
+    if ar_ms:
+        out["dw_allreduce_bus_gbs"] = 2.0 * (D.world - 1) / D.world * 4 * N * K / (ar_ms * 1e-3) / 1e9
+    del x, gy, layer
+    torch.cuda.empty_cache()
+    return out
 
-    for _ in range(max(args.warmup, 3)):
-        step()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sampler = ClockSampler(local)
-    if rank == 0:
+
+def bench_conv(D: Dist, L, steps=5, warmup=3):
+    """MAM conv2d fwd+bwd, [128,64,56,56] -> 128 channels, 3x3, stride 1, padding 1 (M=401408, K=576, N=128)."""
+    import torch
+
+    import mamtorch_b200 as mamtorch
+    from mamtorch_b200 import _lib
+
+    B, C, H, W, Fo = CONV_SHAPE
+    torch.manual_seed(0)
+    gen = torch.Generator(device=D.dev).manual_seed(3)
+    out = {"workload": "MAM conv2d fwd+bwd, x[128,64,56,56], 3x3 64->128, stride 1, padding 1, fp32 "
+                       "(M=401408, K=576, N=128), indices + dX + dW"}
+    units = B * H * W * C * 9 * Fo
+    for order in ("unfold", "taps"):
+        conv = mamtorch.nn.MAMConv2d(C, Fo, 3, padding=1, bias=False, reduction_order=order).to(D.dev)
+        with torch.no_grad():
+            conv.weight.copy_(torch.randn(Fo, C, 3, 3, generator=gen, device=D.dev) * (C * 9) ** -0.5)
+        x = torch.randn(B, C, H, W, generator=gen, device=D.dev).requires_grad_()
+        gy = torch.randn(B, Fo, H, W, generator=gen, device=D.dev)
+
+        def step():
+            conv.zero_grad()
+            x.grad = None
+            conv(x).backward(gy)
+
+        for _ in range(warmup):
+            step()
+        ms = D.timed(step, steps) / steps
+        out[f"ms_per_step_{order}"] = ms
+        out[f"gunits_per_s_{order}"] = units / (ms * 1e-3) / 1e9
+        del conv, x, gy
+    _lib.check(L.mam_check_device_flag(), "device wait flag")
+    torch.cuda.empty_cache()
+    return out
+
+
+def bench_beta_blend(D: Dist, L, steps=5, warmup=3):
+    """beta-blended training step, M=N=K=4096, beta=0.5, the dense term on the tcgen05 TF32 kernel."""
+    import torch
+
+    import mamtorch_b200 as mamtorch
+    from mamtorch_b200 import _lib
+    from mamtorch_b200.nn import functional as MF
+
+    n = 4096
+    std = n ** -0.25           # "N(0, 1/sqrt(K))" read as variance K^-1/2
+    gen = torch.Generator(device=D.dev).manual_seed(4)
+    torch.manual_seed(0)
+    layer = mamtorch.nn.FullyConnected(n, n, bias=True, vcon_steps=2).to(D.dev)
+    layer.vcon_step()          # beta: 1 -> 0.5
+    assert abs(layer.beta - 0.5) < 1e-12
+    with torch.no_grad():
+        layer.weight.copy_(torch.randn(n, n, generator=gen, device=D.dev) * std)
+        layer.bias.zero_()
+    x = torch.randn(n, n, generator=gen, device=D.dev) * std
+    gy = torch.randn(n, n, generator=gen, device=D.dev)
+    was = MF.get_dense_backend()
+    MF.set_dense_backend("tf32")
+    try:
+        def step():
+            layer.zero_grad()
+            xl = x.detach().requires_grad_()
+            layer(xl).backward(gy)
+
+        for _ in range(warmup):
+            step()
+        ms = D.timed(step, steps) / steps
+    finally:
+        MF.set_dense_backend(was)
+    _lib.check(L.mam_check_device_flag(), "device wait flag")
+    del layer, x, gy
+    torch.cuda.empty_cache()
+    return {"workload": "beta-blended MAM training step fp32, y=(1-b)(max+min)+b(x.W^T), b=0.5, M=N=K=4096, "
+                        "x,W ~ N(0,1/sqrt(K)); dense term and its two gradient products on tcgen05 TF32",
+            "ms_per_step": ms, "gunits_per_s": float(n) ** 3 / (ms * 1e-3) / 1e9,
+            "dense_tflops_in_step": 3 * 2.0 * n ** 3 / 1e12}
+
+
+def cpu_other_configs(cpu: CpuPath):
+    """CPU path on bounded row samples of the sharded pruned layer, the convolution and the blended layer."""
+    out = {}
+    rows = 8
+    s = cpu_layer_sample(cpu, rows, SHARDED_K, SHARDED_N, 0.0, SHARDED_SPARSITY, 1.0, SHARDED_K ** -0.5)
+    out["sharded_sparse"] = {"dense_equivalent_gunits": rows * SHARDED_K * SHARDED_N / s / 1e9,
+                             "sample": f"{rows} of {SHARDED_M} rows, dense reference on the zero-filled weight, fwd+bwd"}
+    px = 256
+    s = cpu_conv_sample(cpu, 1, px)
+    B, C, H, W, Fo = CONV_SHAPE
+    out["conv"] = {"gunits_per_s": px * C * 9 * Fo / s / 1e9,
+                   "sample": f"{px} of {B * H * W} output pixels, F.unfold + the reference functions, fwd+bwd"}
+    rows = 8
+    s = cpu_layer_sample(cpu, rows, 4096, 4096, 0.5, 0.0, 4096 ** -0.25, 4096 ** -0.25)
+    out["beta_blend"] = {"gunits_per_s": rows * 4096 * 4096 / s / 1e9,
+                         "sample": f"{rows} of 4096 rows, beta = 0.5, fwd+bwd"}
+    for v in out.values():
+        v.update({"cores": cpu.threads, "kind": cpu.kind})
+    return out
+
+
+# ------------------------------------------------------------------------------------------------
+# single operations (what profiler captures are taken on)
+# ------------------------------------------------------------------------------------------------
+def run_case(args):
+    import torch
+
+    import mamtorch_b200 as mamtorch
+    from mamtorch_b200 import _lib
+    from mamtorch_b200.nn import functional as MF
+
+    dev = torch.device("cuda:0")
+    L = _lib.lib()
+    if args.variant >= 0:
+        _lib.check(L.mam_tune_set(1, args.variant), "variant")
+        _lib.check(L.mam_tune_set(0, args.variant), "variant")
+    _lib.check(L.mam_tune_set(4, args.dense_split), "dense split")
+    g = torch.Generator().manual_seed(0)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if args.case == "conv":
+        B, C, H, W, Fo = (int(v) for v in args.shape.lower().split("x"))
+        torch.manual_seed(0)
+        conv = mamtorch.nn.MAMConv2d(C, Fo, 3, padding=1, bias=False, reduction_order=args.order).to(dev)
+        x = torch.randn(B, C, H, W, generator=g).to(dev).requires_grad_(not args.fwd_only)
+        gy = torch.randn(B, Fo, H, W, generator=g).to(dev)
+        torch.cuda.reset_peak_memory_stats()
+        for rep in range(args.reps + 1):
+            if rep == min(1, args.reps):
+                e0.record()
+            if args.fwd_only:
+                with torch.no_grad():
+                    y = conv(x)
+            else:
+                conv.zero_grad()
+                x.grad = None
+                y = conv(x)
+                y.backward(gy)
+        e1.record()
+        torch.cuda.synchronize()
+        _lib.check(L.mam_check_device_flag(), "device wait flag")
+        print(f"ok conv {args.shape} order {args.order} {'fwd' if args.fwd_only else 'fwd+bwd'} checksum "
+              f"{float(y.double().sum()):.6e} ms_per_rep {e0.elapsed_time(e1) / max(args.reps, 1):.4f} "
+              f"peak_alloc_MB {torch.cuda.max_memory_allocated() / 1e6:.0f}")
+        return
+    M, K, N = (int(v) for v in args.shape.lower().split("x"))
+    x = torch.randn(M, K, generator=g).to(dev)
+    w = (torch.randn(N, K, generator=g) * K ** -0.5).to(dev)
+    gy = torch.randn(M, N, generator=g).to(dev)
+    ops = torch.ops.mamtorch_b200
+    y, imax, imin = ops.linear_forward(x, w, None, None, 1.0, 0.0, True)
+    if args.case in ("csr_fwd", "spmm"):
+        keep = (torch.rand(N, K, generator=g) >= args.sparsity).float().to(dev)
+        w_csr = (w * keep).to_sparse_csr()
+        xT = x.t().contiguous()
+    if args.case == "step":
+        layer = mamtorch.nn.FullyConnected(K, N, store_args=True).to(dev)
+    for rep in range(args.reps + 1):
+        if rep == min(1, args.reps):
+            e0.record()
+        if args.case == "fwd_idx":
+            y, imax, imin = ops.linear_forward(x, w, None, None, 1.0, 0.0, True)
+        elif args.case == "fwd_val":
+            y, = ops.linear_forward(x, w, None, None, 1.0, 0.0, False)
+        elif args.case == "bwd":
+            ops.linear_backward(x, w, gy, imax, imin, 1.0)
+        elif args.case == "bwd_count":
+            ops.linear_backward_count(x, w, gy, imax, imin, 1.0)
+        elif args.case == "selcount":
+            MF.selection_hits(imax, imin, K)
+        elif args.case == "dense_tf32":
+            y = ops.dense_nt(x, w)
+        elif args.case == "csr_fwd":
+            y, imax, imin = mamtorch.sparse.kernel.v1.mam_linear_csr(x, w_csr)
+        elif args.case == "spmm":
+            y = mamtorch.sparse.kernel.v1.cusparsemm(w_csr, xT)
+        else:
+            out = layer(x.clone().requires_grad_())
+            out.backward(gy)
+            layer.update_selection_count()
+    e1.record()
+    torch.cuda.synchronize()
+    _lib.check(L.mam_check_device_flag(), "device wait flag")
+    ms = e0.elapsed_time(e1) / max(args.reps, 1)
+    extra = ""
+    if args.case == "spmm" and args.compare:
+        ref = torch.sparse.mm(w_csr, xT)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(args.reps):
+            ref = torch.sparse.mm(w_csr, xT)
+        e1.record()
+        torch.cuda.synchronize()
+        extra = (f" torch_sparse_mm_ms {e0.elapsed_time(e1) / max(args.reps, 1):.4f}"
+                 f" max_abs_diff {float((y - ref).abs().max()):.3e}")
+    print(f"ok {args.case} {M}x{K}x{N} checksum {float(y.double().sum()):.6e} ms_per_rep {ms:.4f}{extra}")
+
+
+def run_sharded_sparse(args):
+    """`--workload sharded_sparse`: the sharded pruned layer alone, as a line of its own."""
+    from mamtorch_b200 import _lib
+
+    D = Dist(args)
+    L = _lib.lib()
+    sampler = ClockSampler(D.local)
+    if D.rank == 0:
         sampler.start()
-    barrier()
-    ev0.record()
-    for _ in range(args.steps):
-        step()
-    ev1.record()
-    barrier()
-    ms = torch.tensor([ev0.elapsed_time(ev1)], device=dev)
-    if world > 1:
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    clocks = sampler.stop() if rank == 0 else None
-    _lib.check(_lib.lib().mam_check_device_flag(), "device wait flag")
-    if rank == 0:
-        ms_per_step = float(ms.item()) / args.steps
-        units = M_TOTAL * nnz                                       # (row, stored weight) pairs, all ranks
-        line = {"metric": "mam_sharded_sparse_layer_fwd_bwd_throughput", "value": units / (ms_per_step * 1e-3) / 1e9,
-                "unit": UNIT, "n_gpus": world,
-                "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
+    res = bench_sharded_sparse(D, L, steps=args.steps, warmup=max(args.warmup, 3))
+    clocks = sampler.stop() if D.rank == 0 else None
+    if D.rank == 0:
+        line = {"metric": "mam_sharded_sparse_layer_fwd_bwd_throughput", "value": res["value"], "unit": UNIT,
+                "n_gpus": D.world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": res["ms_per_step"],
                 "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-                "config": {"workload": "large sharded MAM layer fwd+bwd, fp32, M=65536 rows split by rank, K=N=4096, "
-                                       "W pruned to 90 % sparsity (CSR), dW all-reduced over NCCL",
-                           "units": "value counts (row, stored weight) pairs; the dense-equivalent rate is "
-                                    f"{M_TOTAL * K * N / (ms_per_step * 1e-3) / 1e9:.0f} G units/s",
-                           "nnz": nnz, "rows_per_rank": rows,
+                "config": {"workload": res["workload"], "units": "value counts (row, stored weight) pairs",
                            "l2": "per-rank working set (activations, indices, gradients) exceeds the 126 MB L2"},
-                "gpu_launches": 11 * args.steps, "clocks": clocks}
+                "detail": res, "gpu_launches": 11 * args.steps, "clocks": clocks}
         print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    D.close()
 
 
 def run_reference_cuda(args):
@@ -356,11 +787,25 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference", "reference_cuda"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-other-configs", action="store_true", help="headline workload only")
     ap.add_argument("--fwd-variant", type=int, default=-1, help="tile configuration of the index-producing forward")
     ap.add_argument("--workload", default="vit_mlp", choices=["vit_mlp", "sharded_sparse"],
                     help="vit_mlp: the headline configuration (default); sharded_sparse: the large pruned layer, "
                          "65536 rows split over the ranks (strong scaling), K = N = 4096, 90 %% of W pruned")
+    ap.add_argument("--case", default=None, choices=["fwd_idx", "fwd_val", "bwd", "bwd_count", "selcount", "step",
+                                                     "dense_tf32", "csr_fwd", "spmm", "conv"],
+                    help="run one operation --reps times on --shape and print its time (profiler captures)")
+    ap.add_argument("--shape", default="4096x1024x2048", help="--case: MxKxN, or BxCxHxWxF for conv")
+    ap.add_argument("--reps", type=int, default=3)
+    ap.add_argument("--order", default="unfold", choices=["unfold", "taps"], help="--case conv: reduction order")
+    ap.add_argument("--fwd-only", action="store_true", help="--case conv: forward with indices only")
+    ap.add_argument("--sparsity", type=float, default=0.9, help="--case csr_fwd / spmm: share of zeroed weights")
+    ap.add_argument("--compare", action="store_true", help="--case spmm: time torch.sparse.mm too")
+    ap.add_argument("--variant", type=int, default=-1, help="--case: tile configuration of the tiled forward")
+    ap.add_argument("--dense-split", type=int, default=1, choices=[0, 1], help="--case dense_tf32: slice the last wave")
     args = ap.parse_args()
+    if args.case:
+        return run_case(args)
     if args.workload == "sharded_sparse" and args.impl == "b200":
         return run_sharded_sparse(args)
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
@@ -370,26 +815,16 @@ def main():
         return run_reference_cuda(args)
 
     import torch
-    import torch.distributed as dist
 
     import mamtorch_b200 as mamtorch
     from mamtorch_b200 import _lib
-    from mamtorch_b200.dist import allreduce_gradients
+    from mamtorch_b200.dist import OverlappedGradSync
 
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world} (launch with torch.distributed.run)"
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: there is no CPU path")
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
+    D = Dist(args)
+    rank, world, local, dev = D.rank, D.world, D.local, D.dev
     L = _lib.lib()
     if args.fwd_variant >= 0:
-        _lib.check(L.mam_set_fwd_variant(1, args.fwd_variant), "mam_set_fwd_variant")
+        _lib.check(L.mam_tune_set(1, args.fwd_variant), "mam_tune_set")
 
     # ---- model and data: every rank its own rows (seeded per rank), identical weights
     torch.manual_seed(0)
@@ -409,6 +844,9 @@ def main():
     x_dev = x_host.to(dev)
     gy_dev = gy_host.to(dev)
     params = [fc1.weight, fc2.weight, fc1.bias, fc2.bias]
+    # N > 1: every parameter's gradient is all-reduced in place from a hook that fires as soon as autograd has
+    # accumulated it, on NCCL's own stream; finish() makes the compute stream wait for the collectives
+    sync = OverlappedGradSync(params) if world > 1 else None
 
     def step(x, gy):
         for p in params:
@@ -418,9 +856,26 @@ def main():
         y.backward(gy)
         fc1.update_selection_count()
         fc2.update_selection_count()
-        if world > 1:
-            allreduce_gradients(params)
+        if sync is not None:
+            sync.finish()
         return y
+
+    # Before anything is timed, at N > 1: the all-reduced weight gradient must equal the sum of the ranks'
+    # own gradients (values, not just that N ranks took part).
+    grad_sum_check = None
+    if world > 1:
+        sync.enabled = False
+        step(x_dev, gy_dev)
+        own = fc2.weight.grad.detach().clone()
+        gathered = [torch.empty_like(own) for _ in range(world)]
+        D.dist.all_gather(gathered, own)
+        want = torch.stack(gathered).double().sum(0)
+        sync.enabled = True
+        step(x_dev, gy_dev)
+        got = fc2.weight.grad.detach().double()
+        err = float((got - want).abs().max() / want.abs().max())
+        grad_sum_check = {"max_rel_err_vs_sum_of_rank_gradients": err, "ok": err <= 1e-5}
+        assert err <= 1e-5, f"all-reduced dW differs from the sum of the per-rank gradients: {err}"
 
     # End-to-end leg: every step's activations and upstream gradient start in pinned host memory and
     # its output and loss end there.  Copies run on their own stream, double-buffered, so the upload
@@ -443,96 +898,83 @@ def main():
             up_done[slot].record(copy_stream)
 
     def run_from_host(steps):
-        main = torch.cuda.current_stream()
+        main_stream = torch.cuda.current_stream()
         for ev in comp_done + down_done:
-            ev.record(main)
+            ev.record(main_stream)
         upload(0)
         for i in range(steps):
             slot = i & 1
             if i + 1 < steps:
                 upload(slot ^ 1)
-            main.wait_event(up_done[slot])
-            main.wait_event(down_done[slot])          # y_buf[slot] of step i-2 has been downloaded
+            main_stream.wait_event(up_done[slot])
+            main_stream.wait_event(down_done[slot])          # y_buf[slot] of step i-2 has been downloaded
             y = step(x_buf[slot], gy_buf[slot])
             y_buf[slot].copy_(y.detach())
             loss_buf[slot].copy_((y.detach() * gy_buf[slot]).sum())
-            comp_done[slot].record(main)
+            comp_done[slot].record(main_stream)
             with torch.cuda.stream(copy_stream):
                 copy_stream.wait_event(comp_done[slot])
                 y_host.copy_(y_buf[slot], non_blocking=True)
                 loss_host.copy_(loss_buf[slot], non_blocking=True)
                 down_done[slot].record(copy_stream)
-        main.wait_stream(copy_stream)
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def timed(fn, steps):
-        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        barrier()
-        ev0.record()
-        for _ in range(steps):
-            fn()
-        ev1.record()
-        barrier()
-        ms = torch.tensor([ev0.elapsed_time(ev1)], device=dev)
-        if world > 1:
-            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        return float(ms.item())
+        main_stream.wait_stream(copy_stream)
 
     for _ in range(args.warmup):
         step(x_dev, gy_dev)
     run_from_host(2)
-    barrier()
+    D.barrier()
 
     # ---- per-kernel events for the dominant kernel (2 launches per step)
-    cap = 2 * args.steps
-    ev_pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(cap)]
-    for a, b in ev_pairs:  # events are created lazily on first record; force creation now
-        a.record()
-        b.record()
-    torch.cuda.synchronize()
-    starts = (ctypes.c_void_p * cap)(*[ctypes.c_void_p(a.cuda_event) for a, _ in ev_pairs])
-    stops = (ctypes.c_void_p * cap)(*[ctypes.c_void_p(b.cuda_event) for _, b in ev_pairs])
-    _lib.check(L.mam_timer_arm(starts, stops, cap, 0), "mam_timer_arm")
-
+    timer = LibTimer(L, 2 * args.steps)
+    timer.arm(0)
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    total_ms = timed(lambda: step(x_dev, gy_dev), args.steps)
-    recorded = L.mam_timer_disarm()
-    torch.cuda.synchronize()
-    kernel_ms = [a.elapsed_time(b) for a, b in ev_pairs[:recorded]]
-    # the other kernels of the step, each class timed by the library's own events over three extra steps
+    total_ms = D.timed(lambda: step(x_dev, gy_dev), args.steps)
+    kernel_ms = timer.collect()
+    # the other kernels of the step, each class timed by the library's own events over extra steps
     # (two launches per step: layer 1 and layer 2)
     other_ms = {}
+    extra_steps = max(3, min(args.steps, 10))
     for name, kid in (("index_resolver", 1), ("backward_scatter", 3), ("selection_hits", 4)):
-        _lib.check(L.mam_timer_arm(starts, stops, cap, kid), "mam_timer_arm")
-        for _ in range(3):
+        timer.arm(kid)
+        for _ in range(extra_steps):
             step(x_dev, gy_dev)
-        n_rec = L.mam_timer_disarm()
-        torch.cuda.synchronize()
-        per_launch = [a.elapsed_time(b) for a, b in ev_pairs[:n_rec]]
-        other_ms[name] = sum(per_launch) / 3 if per_launch else float("nan")
-    e2e_ms = timed(lambda: run_from_host(args.steps), 1)
+        per_launch = timer.collect()
+        other_ms[name] = sum(per_launch) / extra_steps if per_launch else 0.0
+    e2e_ms = D.timed(lambda: run_from_host(args.steps), 1)
     clocks = sampler.stop() if rank == 0 else None
     _lib.check(L.mam_check_device_flag(), "device wait flag")
 
+    props = torch.cuda.get_device_properties(dev)
+    sms = props.multi_processor_count
+    max_mhz = (clocks or {}).get("sm_max_mhz") or 1965.0
+
+    # ---- the other configurations of the specification, measured in the same run
+    others = {}
+    if not args.no_other_configs:
+        del x_buf, gy_buf, y_buf
+        torch.cuda.empty_cache()
+        sampler2 = ClockSampler(local)
+        if rank == 0:
+            sampler2.start()
+        if world == 1:
+            others["fwd_4096"] = bench_fwd_4096(D, L, sms, max_mhz)
+            others["conv"] = bench_conv(D, L)
+            others["beta_blend"] = bench_beta_blend(D, L)
+        others["sharded_sparse"] = bench_sharded_sparse(D, L)
+        if rank == 0:
+            others["clocks"] = sampler2.stop()
+
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
+        D.close()
         return
 
     ms_per_step = total_ms / args.steps
     value = world * UNITS_PER_STEP / (ms_per_step * 1e-3) / 1e9
     e2e_value = world * UNITS_PER_STEP / (e2e_ms / args.steps * 1e-3) / 1e9
-    props = torch.cuda.get_device_properties(dev)
-    sms = props.multi_processor_count
     kavg = statistics.mean(kernel_ms) if kernel_ms else float("nan")
     flops_per_launch = 3.0 * M_TOKENS * D_MODEL * D_FF  # 3 fp32 ops per (m,n,k) unit, unpadded extents
-    max_mhz = (clocks or {}).get("sm_max_mhz") or 1965.0
     peaks = fp32_peaks(sms, max_mhz)
     achieved = flops_per_launch / (kavg * 1e-3) / 1e12
     roofline = {"bound": "fp32_cuda_core", "kernel": "mam_fwd_tiled_kernel (index-tracking variant "
@@ -543,41 +985,47 @@ def main():
                                "MEASURED_PEAKS.json); a MAM unit has no FMA, see the two extra fractions",
                 "frac_of_non_fma_peak": achieved / peaks["non_fma_tops"],
                 "frac_of_measured_mix_ceiling": (achieved / 3 * 1e3) / peaks["mix_ceiling_gunits"],
-                "launch_ms_avg": kavg, "launches_timed": len(kernel_ms), "traffic": 3.75e8,
-                "traffic_note": "dram read+write bytes per launch (layer-1 shape) from the ncu capture in "
-                                "profiles/step_kernels_4736x768x3072.md, scaled by rows to M=12608"}
+                "launch_ms_avg": kavg, "launches_timed": len(kernel_ms),
+                "traffic": TRAFFIC_WEIGHT_BYTES + TRAFFIC_CAPTURED_BYTES * M_TOKENS / TRAFFIC_CAPTURED_ROWS,
+                "traffic_note": "dram read+write bytes per launch (layer-1 shape): profiler capture at M=4736, "
+                                "scaled by rows to M=12608"}
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": WORKLOAD, "l2": "working set per step (~1 GB of activations, indices and "
                        "gradients) exceeds the 126 MB L2; no explicit flush",
-                       "parallelism": f"rows sharded over {world} rank(s); dW all-reduce over NCCL" if world > 1
-                       else "single GPU"},
+                       "parallelism": f"rows sharded over {world} rank(s); dW all-reduced over NCCL from gradient "
+                                      "hooks, overlapping the rest of the backward" if world > 1 else "single GPU"},
             "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms / args.steps,
                     "h2d_bytes_per_step": x_host.numel() * 4 + gy_host.numel() * 4,
                     "d2h_bytes_per_step": y_host.numel() * 4 + 4},
             "gpu_launches": 10 * args.steps, "clocks": clocks, "roofline": roofline}
+    if grad_sum_check is not None:
+        line["allreduced_dw_check"] = grad_sum_check
     # per-step time of every kernel class and, for the two HBM-style kernels, algorithmic bytes over time
     # against the measured copy bandwidth (both layers: M x 768 x 3072 and M x 3072 x 768)
     hbm_peak = measured_hbm_gbs()
     mn, mk_nk = M_TOTAL_OUTPUTS, 2 * (M_TOKENS * D_MODEL + M_TOKENS * D_FF + 2 * D_MODEL * D_FF)
-    bwd_bytes = 12 * mn + 4 * mk_nk
-    sel_bytes = 8 * mn + 8 * 2 * D_MODEL * D_FF
+    bwd_bytes = 12 * mn + 4 * mk_nk + 8 * 2 * D_MODEL * D_FF     # + both int32 hit matrices of both layers
     line["kernels_ms_per_step"] = {"forward_main_loop": 2 * kavg, **other_ms}
+    bwd_ms = other_ms["backward_scatter"] + other_ms["selection_hits"]
     line["roofline_other_kernels"] = [
-        {"kernel": "mam_bwd_rowwarp_kernel (768 -> 3072) + mam_bwd_kernel (3072 -> 768)", "bound": "hbm", "achieved": bwd_bytes / (other_ms["backward_scatter"] * 1e-3) / 1e9,
-         "peak": hbm_peak, "unit": "GB/s", "frac": bwd_bytes / (other_ms["backward_scatter"] * 1e-3) / 1e9 / hbm_peak,
-         "note": "12*M*N + 8*(M*K + N*K) bytes per layer; in practice bound by the rate of scattered fp32 reductions "
-                 "into L2 (2*M*N per layer) and the LSU data pipe, see profiles/step_kernels_4736x768x3072.md"},
-        {"kernel": "mam_selcount_kernel", "bound": "hbm", "achieved": sel_bytes / (other_ms["selection_hits"] * 1e-3) / 1e9,
-         "peak": hbm_peak, "unit": "GB/s", "frac": sel_bytes / (other_ms["selection_hits"] * 1e-3) / 1e9 / hbm_peak,
-         "note": "8*M*N + 8*N*K bytes per layer"}]
+        {"kernel": "selected-pair backward with the selection hits (both layers)", "bound": "hbm",
+         "achieved": bwd_bytes / (bwd_ms * 1e-3) / 1e9, "peak": hbm_peak, "unit": "GB/s",
+         "frac": bwd_bytes / (bwd_ms * 1e-3) / 1e9 / hbm_peak,
+         "note": "12*M*N + 8*(M*K + N*K) + 8*N*K bytes per layer over backward_scatter + selection_hits; in "
+                 "practice bound by the rate of scattered 4-byte L2 operations (weight gathers and fp32 "
+                 "reductions into dW), not by bytes"}]
+    if others:
+        line["north_star_configs"] = others
     if world == 1 and not args.no_cpu_baseline:
-        cv, threads, sample = cpu_reference_sample(256, 3)
-        line["cpu_baseline"] = {"value": cv, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample}
+        cpu = CpuPath()
+        cv, sample = cpu_mlp_pair_sample(cpu, 128, 2)
+        line["cpu_baseline"] = {"value": cv, "unit": UNIT, "cores": cpu.threads, "kind": cpu.kind, "sample": sample}
+        if others:
+            line["north_star_configs"]["cpu"] = cpu_other_configs(cpu)
     print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    D.close()
 
 
 if __name__ == "__main__":

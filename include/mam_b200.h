@@ -2,8 +2,9 @@
  *
  * Plain C types only: device pointers, sizes, a CUDA stream passed as void*.  No entry point
  * allocates or frees device memory; the caller owns every buffer, including the workspace whose
- * size the *_workspace_bytes queries return.  Every entry point returns a mam_status code; text for
- * it comes from mam_status_str().  All launches go to the stream given (0 = legacy default
+ * size the *_workspace_bytes queries return -- with one exception, mam_fwd_kn_static_f32, whose
+ * scratch is a fixed buffer compiled into the library.  Every entry point returns a mam_status
+ * code; text for it comes from mam_status_str().  All launches go to the stream given (0 = legacy default
  * stream) on the device that is current for the calling thread.
  *
  * Each function names the interface of SSIGPRO/mamtorch it stands in for (path:line inside that
@@ -47,19 +48,12 @@ const char* mam_last_cuda_error(void);
  * recorded a wait that ran out since the flag was last cleared (it clears the flag). */
 int mam_check_device_flag(void);
 
-/* Selects the tile configuration of the tiled forward kernels: -1 (default) picks by shape,
- * other values index mam_fwd_variant_name().  A tuning / benchmarking knob, process-wide.
- * with_indices = 0 / 1 addresses the values-only / index-producing forward.  Two more selectors ride on
- * the same call for cross-checks and timing comparisons: with_indices = 2 chooses the index resolver
- * (variant 0 = tiled, the default; 1 = one thread per output), with_indices = 3 the backward form
- * (variant 0 = chosen by shape, the default; 1 = single kernel, a CTA's rows of dX shared by its warps;
- * 2 = separate dX and dW kernels; 3 = single kernel, one row of dX per warp, the row of a parked in shared
- * memory where it fits; 4 = as 3 with a read through L1), with_indices = 4 the
- * TF32 product's handling of its last partial wave of tiles (1 = cut them into column slices, the default;
- * 0 = whole tiles only), with_indices = 5 the output rows per CTA of mam_conv_bwd_direct_f32 (0 = chosen by
- * shared-memory size, the default). */
-int mam_set_fwd_variant(int with_indices, int variant);
-const char* mam_fwd_variant_name(int with_indices, int variant);
+/* The same check without waiting for the device, for callers that must not stall their stream: returns
+ * MAM_ERR_DEVICE_TIMEOUT if the copy of the flag that an EARLIER call of this function fetched shows a
+ * wait that ran out (and then clears flag and copy), else queues the next fetch of the flag on `stream`
+ * (4 bytes into pinned host memory the library keeps per device) and returns MAM_OK.  A time-out is thus
+ * reported one call late at most.  No counterpart in the reference, whose kernels have no bounded waits. */
+int mam_poll_device_flag(void* stream);
 
 /* Per-kernel timing without a profiler.  While armed, every launch of the kernel class `kernel_id`
  * is bracketed by cudaEventRecord(starts[i]) / cudaEventRecord(stops[i]) on the launch stream,
@@ -271,7 +265,9 @@ size_t mam_csr_fwd_workspace_bytes(int64_t M, int64_t K, int64_t N, int64_t nnz)
  * transposed activations after it.  With entries_ready != 0 the regrouping kernels are skipped: the caller
  * vouches that this workspace was last written by a call with the same crow / col / val contents, K, N and
  * nnz (M may differ; the workspace must hold mam_csr_fwd_workspace_bytes for the M of this call).  With
- * entries_ready == 0 it is mam_csr_fwd_ws_f32. */
+ * entries_ready == 2 the caller vouches for crow, col, K, N and nnz only -- the sparsity pattern -- and the
+ * stored values are regrouped again in one pass: a training step, where the mask stays and the values move.
+ * With entries_ready == 0 it is mam_csr_fwd_ws_f32. */
 size_t mam_csr_fwd_entries_bytes(int64_t K, int64_t N, int64_t nnz);
 int mam_csr_fwd_ws_ex_f32(const float* a, const int64_t* crow, const int64_t* col, const float* val, int64_t nnz,
                           const float* bias, float* y, int32_t* argmax, int32_t* argmin,

@@ -18,7 +18,6 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libmam_b200.so")
 SHIM = os.path.join(HERE, "_C.so")
-PROBE = os.path.join(HERE, "pipe_probe")
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
               "--compiler-options", "-fPIC"]
@@ -39,7 +38,7 @@ def _stale(target: str, sources) -> bool:
 
 
 def _sources(exts):
-    out = [os.path.join(HERE, "..", "include", "mam_b200.h")]
+    out = [os.path.join(HERE, "..", "include", "mam_b200.h"), os.path.join(HERE, "..", "include", "mam_b200_tuning.h")]
     for f in sorted(os.listdir(CSRC)):
         if f.endswith(exts):
             out.append(os.path.join(CSRC, f))
@@ -49,20 +48,12 @@ def _sources(exts):
 def build_lib(force: bool = False, verbose: bool = False) -> str:
     srcs = _sources((".cu", ".cuh"))
     if force or _stale(LIB, srcs):
-        cus = [s for s in srcs if s.endswith(".cu") and not s.endswith("pipe_probe.cu")]
+        cus = [s for s in srcs if s.endswith(".cu")]
         cmd = [_nvcc(), *NVCC_FLAGS, "-shared", "-o", LIB, *cus]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")
         subprocess.check_call(cmd, cwd=CSRC)
     return LIB
-
-
-def build_probe(force: bool = False) -> str:
-    src = os.path.join(CSRC, "pipe_probe.cu")
-    if force or _stale(PROBE, [src, os.path.join(CSRC, "mam_ptx.cuh")]):
-        subprocess.check_call([_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo",
-                               "-o", PROBE, src], cwd=CSRC)
-    return PROBE
 
 
 def build_shim(force: bool = False) -> str:
@@ -88,7 +79,6 @@ def build_shim(force: bool = False) -> str:
 def build(force: bool = False) -> None:
     build_lib(force)
     build_shim(force)
-    build_probe(force)
 
 
 if __name__ == "__main__":

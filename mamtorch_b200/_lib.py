@@ -14,14 +14,15 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libmam_b200.so")
 SHIM_PATH = os.path.join(_HERE, "_C.so")
 
-# name -> (restype, argtypes) for every symbol include/mam_b200.h declares
+# name -> (restype, argtypes) for every symbol include/mam_b200.h and include/mam_b200_tuning.h declare
 _vp, _i64, _i32, _f32, _sz = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_float, ctypes.c_size_t
 ABI = {
     "mam_status_str": (ctypes.c_char_p, [_i32]),
     "mam_abi_version": (_i32, []),
     "mam_last_cuda_error": (ctypes.c_char_p, []),
     "mam_check_device_flag": (_i32, []),
-    "mam_set_fwd_variant": (_i32, [_i32, _i32]),
+    "mam_poll_device_flag": (_i32, [_vp]),
+    "mam_tune_set": (_i32, [_i32, _i32]),
     "mam_fwd_variant_name": (ctypes.c_char_p, [_i32, _i32]),
     "mam_timer_arm": (_i32, [ctypes.POINTER(_vp), ctypes.POINTER(_vp), _i32, _i32]),
     "mam_timer_disarm": (_i32, []),

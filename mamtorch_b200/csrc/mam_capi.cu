@@ -6,6 +6,7 @@
 #include <cuda_runtime.h>
 
 #include "../../include/mam_b200.h"
+#include "../../include/mam_b200_tuning.h"
 #include "mam_bwd.cuh"
 #include "mam_conv.cuh"
 #include "mam_csr.cuh"
@@ -285,7 +286,7 @@ int run_tiled(const float* a, const float* w, float* y, int32_t* argmax, int32_t
     }
     if (cv) {
         // patch rows by im2col-mode TMA: the configurations the automatic choice makes (the tuning
-        // selector of mam_set_fwd_variant applies to the matrix form only)
+        // selector of mam_tune_set applies to the matrix form only)
         if (!want_idx) {
             switch (auto_variant(false, M, N, d)) {
                 case 3: return launch_tiled<ValCfg3, true>(a, w, prm, d, cs, cv);
@@ -423,6 +424,34 @@ int mam_check_device_flag(void) {
     return MAM_OK;
 }
 
+int mam_poll_device_flag(void* stream) {
+    int dev = 0;
+    MAM_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return MAM_ERR_UNSUPPORTED;
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    MAM_CUDA(cudaStreamIsCapturing((cudaStream_t)stream, &cap));
+    if (cap != cudaStreamCaptureStatusNone) return MAM_OK;   // nothing is fetched or reported inside a capture
+    // one pinned int per device: the landing place of the asynchronous fetches
+    static int* mirror[64] = {nullptr};
+    if (mirror[dev] == nullptr) {
+        int* p = nullptr;
+        MAM_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&p), sizeof(int), cudaHostAllocDefault));
+        *p = 0;
+        mirror[dev] = p;
+    }
+    const int seen = *reinterpret_cast<volatile int*>(mirror[dev]);
+    if (seen) {
+        // report once: clear the device flag and the copy (this path may wait for the device)
+        int zero = 0;
+        MAM_CUDA(cudaMemcpyToSymbol(g_wait_gave_up, &zero, sizeof(int)));
+        *mirror[dev] = 0;
+        return MAM_ERR_DEVICE_TIMEOUT;
+    }
+    MAM_CUDA(cudaMemcpyFromSymbolAsync(mirror[dev], g_wait_gave_up, sizeof(int), 0, cudaMemcpyDeviceToHost,
+                                       (cudaStream_t)stream));
+    return MAM_OK;
+}
+
 int mam_timer_arm(void** starts, void** stops, int capacity, int kernel_id) {
     if (!starts || !stops || capacity <= 0) return MAM_ERR_INVALID_ARGUMENT;
     g_timer.starts = starts;
@@ -439,28 +468,30 @@ int mam_timer_disarm(void) {
     return n;
 }
 
-int mam_set_fwd_variant(int with_indices, int variant) {
-    if (with_indices == 3) {  // selects the backward form: 0 auto, 1 CTA-shared rows, 2 two kernels, 3 / 4 row per warp
-        if (variant < 0 || variant > 4) return MAM_ERR_INVALID_ARGUMENT;
-        g_bwd_mode = variant;
-        return MAM_OK;
+int mam_tune_set(int knob, int value) {
+    switch (knob) {
+        case MAM_TUNE_FWD_VALUES:
+        case MAM_TUNE_FWD_INDICES:
+            if (value < -2 || value >= N_VARIANTS) return MAM_ERR_INVALID_ARGUMENT;
+            g_variant[knob == MAM_TUNE_FWD_INDICES ? 1 : 0] = value;
+            return MAM_OK;
+        case MAM_TUNE_RESOLVER:
+            g_resolve_simple = value ? 1 : 0;
+            return MAM_OK;
+        case MAM_TUNE_BWD_FORM:
+            if (value < 0 || value > 4) return MAM_ERR_INVALID_ARGUMENT;
+            g_bwd_mode = value;
+            return MAM_OK;
+        case MAM_TUNE_DENSE_SPLIT:
+            g_dense_split = value ? 1 : 0;
+            return MAM_OK;
+        case MAM_TUNE_CONV_DIRECT_ROWS:
+            if (value < 0 || value > 64) return MAM_ERR_INVALID_ARGUMENT;
+            g_conv_direct_rows = value;
+            return MAM_OK;
+        default:
+            return MAM_ERR_INVALID_ARGUMENT;
     }
-    if (with_indices == 5) {  // one-kernel convolution backward: output rows per CTA (0 = chosen by shared-memory size)
-        if (variant < 0 || variant > 64) return MAM_ERR_INVALID_ARGUMENT;
-        g_conv_direct_rows = variant;
-        return MAM_OK;
-    }
-    if (with_indices == 4) {  // TF32 product: 1 (default) slices the tiles of the last partial wave, 0 does not
-        g_dense_split = variant ? 1 : 0;
-        return MAM_OK;
-    }
-    if (with_indices == 2) {  // selects the index resolver: 0 tiled (default), 1 thread-per-output
-        g_resolve_simple = variant ? 1 : 0;
-        return MAM_OK;
-    }
-    if (variant < -2 || variant >= N_VARIANTS) return MAM_ERR_INVALID_ARGUMENT;
-    g_variant[with_indices ? 1 : 0] = variant;
-    return MAM_OK;
 }
 
 const char* mam_fwd_variant_name(int with_indices, int variant) {
@@ -1039,7 +1070,10 @@ int mam_csr_fwd_ws_ex_f32(const float* a, const int64_t* crow, const int64_t* co
     const unsigned seg_blocks = (unsigned)((segs + 255) / 256);
     const long long* crow_ll = reinterpret_cast<const long long*>(crow);
     const long long* col_ll = reinterpret_cast<const long long*>(col);
-    if (!entries_ready) {
+    if (entries_ready == 2) {
+        // same sparsity pattern as the call that left seg / k0 here, new values: one pass over the entries
+        csr_tile_fill_kernel<<<seg_blocks, 256, 0, cs>>>(crow_ll, col_ll, val, seg, list, rlist, N, w.nks, 0);
+    } else if (!entries_ready) {
         csr_tile_count_kernel<<<seg_blocks, 256, 0, cs>>>(crow_ll, col_ll, counts, k0, N, K, w.nks);
         // counts -> seg (exclusive scan); the first words of the list area hold the per-block sums
         // until the fill kernel overwrites them

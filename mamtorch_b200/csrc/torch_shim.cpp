@@ -132,11 +132,29 @@ std::vector<at::Tensor> backward_impl(const at::Tensor& a, const at::Tensor& w, 
 }
 
 // ------------------------------------------------------------------ dense (sum-of-products) term
-// 1: tcgen05 TF32 kernel of this library (default); 0: torch/cuBLAS in full fp32.
-int g_dense_backend = 1;
+// 1: tcgen05 TF32 kernel of this library; 0: torch/cuBLAS in full fp32, what the reference computes
+// (at::linalg_matmul / F.linear and its own dense.cu); -1 (default): follow torch's own switch for TF32
+// matrix products (torch.backends.cuda.matmul.allow_tf32, off unless the user turned it on), so that the
+// reference-named operators return full-fp32 results unless reduced precision was asked for.
+int g_dense_backend = -1;
 
-void set_dense_backend(int64_t backend) { g_dense_backend = backend ? 1 : 0; }
+void set_dense_backend(int64_t backend) { g_dense_backend = backend < 0 ? -1 : (backend ? 1 : 0); }
 int64_t get_dense_backend() { return g_dense_backend; }
+bool dense_tf32_wanted() {
+    if (g_dense_backend >= 0) return g_dense_backend == 1;
+    return at::globalContext().allowTF32CuBLAS();
+}
+bool ptr16(const at::Tensor& t) { return reinterpret_cast<uintptr_t>(t.data_ptr()) % 16 == 0; }
+
+// The flag a kernel of the library sets when one of its bounded waits gave up (its outputs are then invalid).
+// check_device_flag synchronises the device and raises if the flag is set.  poll_device_flag does not wait:
+// it raises if the copy of the flag fetched by an EARLIER poll shows a time-out, then queues the next fetch
+// on the current stream -- cheap enough to sit in every module call, one call late at most.
+void check_device_flag() { check_status(mam_check_device_flag(), "a kernel of mamtorch_b200"); }
+void poll_device_flag() {
+    auto stream = at::cuda::getCurrentCUDAStream();
+    check_status(mam_poll_device_flag(stream.stream()), "a kernel of mamtorch_b200");
+}
 
 // a[M,K] . w[N,K]^T -> [M,N]
 at::Tensor dense_nt(const at::Tensor& a, const at::Tensor& w) {
@@ -145,9 +163,7 @@ at::Tensor dense_nt(const at::Tensor& a, const at::Tensor& w) {
     TORCH_CHECK(a.size(1) == w.size(1), "inner dimensions differ");
     c10::cuda::CUDAGuard guard(a.device());
     const int64_t M = a.size(0), K = a.size(1), N = w.size(0);
-    const bool tf32_ok = g_dense_backend == 1 && M > 0 && N > 0 && K > 0 && K % 4 == 0 &&
-                         reinterpret_cast<uintptr_t>(a.data_ptr()) % 16 == 0 &&
-                         reinterpret_cast<uintptr_t>(w.data_ptr()) % 16 == 0;
+    const bool tf32_ok = dense_tf32_wanted() && M > 0 && N > 0 && K > 0 && K % 4 == 0 && ptr16(a) && ptr16(w);
     if (!tf32_ok) return at::matmul(a, w.t());
     auto out = at::empty({M, N}, a.options());
     auto stream = at::cuda::getCurrentCUDAStream();
@@ -175,7 +191,7 @@ at::Tensor dense(const at::Tensor& a, const at::Tensor& b) {
     check_matrix(a, "a");
     check_matrix(b, "b");
     TORCH_CHECK(a.size(1) == b.size(0), "inner dimensions differ");
-    if (g_dense_backend == 0) return at::matmul(a, b);
+    if (!dense_tf32_wanted()) return at::matmul(a, b);
     return dense_nt(a, b.t().contiguous());
 }
 // The K-contiguous copy of b serves both the tensor-core product and the MAM kernels, so the
@@ -203,7 +219,14 @@ std::vector<at::Tensor> fullyconnected_backward_beta(const at::Tensor& a, const 
     auto r = backward_impl(a, b, MAM_B_KN, grad, argmax, argmin, 1.0 - beta);
     if (beta != 0.0) {
         const int64_t M = a.size(0), K = a.size(1), N = b.size(1);
-        const bool tf32_ok = g_dense_backend == 1 && M % 4 == 0 && N % 4 == 0 && K % 4 == 0 && M > 0 && N > 0 && K > 0;
+        bool tf32_ok = dense_tf32_wanted() && M % 4 == 0 && N % 4 == 0 && K % 4 == 0 && M > 0 && N > 0 && K > 0 &&
+                       ptr16(grad) && ptr16(b) && ptr16(r[0]) && ptr16(r[1]);
+        at::Tensor at_, gt;
+        if (tf32_ok) {
+            at_ = a.t().contiguous();
+            gt = grad.t().contiguous();
+            tf32_ok = ptr16(at_) && ptr16(gt);
+        }
         if (tf32_ok) {
             // da[M,K] += beta * grad[M,N] . b[K,N]^T      (reduction over N: both operands N-contiguous)
             // db[K,N] += beta * a^T[K,M] . grad^T[N,M]^T  (reduction over M: transposed copies)
@@ -211,8 +234,6 @@ std::vector<at::Tensor> fullyconnected_backward_beta(const at::Tensor& a, const 
             check_status(mam_dense_tf32(grad.data_ptr<float>(), b.data_ptr<float>(), r[0].data_ptr<float>(),
                                         (float)beta, 1.0f, M, N, K, stream.stream()),
                          "mam_dense_tf32");
-            auto at_ = a.t().contiguous();
-            auto gt = grad.t().contiguous();
             check_status(mam_dense_tf32(at_.data_ptr<float>(), gt.data_ptr<float>(), r[1].data_ptr<float>(),
                                         (float)beta, 1.0f, K, M, N, stream.stream()),
                          "mam_dense_tf32");
@@ -293,11 +314,11 @@ at::Tensor conv_im2col(const at::Tensor& x, int64_t kH, int64_t kW, int64_t sh, 
                  "mam_im2col_f32");
     return rows;
 }
-// [B,H,W,C] contiguous from x[B,C,H,W] (returned as is when x already is channels-last in memory)
+// A fresh [B,H,W,C] contiguous copy of x[B,C,H,W].  (A caller whose x already is channels-last in memory
+// uses x.permute(0, 2, 3, 1) as it is and does not come here.)
 at::Tensor conv_channels_last(const at::Tensor& x) {
     TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kFloat && x.dim() == 4, "x must be a float32 CUDA [B,C,H,W] tensor");
     auto view = x.permute({0, 2, 3, 1});
-    if (view.is_contiguous()) return view;
     auto xc = x.contiguous();
     const int64_t B = xc.size(0), C = xc.size(1), H = xc.size(2), W = xc.size(3);
     c10::cuda::CUDAGuard guard(x.device());
@@ -532,11 +553,12 @@ std::vector<at::Tensor> csr_linear_forward(const at::Tensor& x, const at::Tensor
 std::vector<int64_t> csr_workspace_bytes(int64_t M, int64_t K, int64_t N, int64_t nnz) {
     return {(int64_t)mam_csr_fwd_workspace_bytes(M, K, N, nnz), (int64_t)mam_csr_fwd_entries_bytes(K, N, nnz)};
 }
-// csr_linear_forward on a scratch buffer the caller keeps: with entries_ready the regrouped weight found in
-// `workspace` (left there by an earlier call on the same CSR contents) is used as is
+// csr_linear_forward on a scratch buffer the caller keeps: with entries_ready = 1 the regrouped weight found in
+// `workspace` (left there by an earlier call on the same CSR contents) is used as is; with 2 only the sparsity
+// pattern is taken as unchanged and the stored values are regrouped again (a training step: same mask, new values)
 std::vector<at::Tensor> csr_linear_forward_ws(const at::Tensor& x, const at::Tensor& crow, const at::Tensor& col,
                                               const at::Tensor& val, const c10::optional<at::Tensor>& bias,
-                                              bool want_idx, at::Tensor workspace, bool entries_ready) {
+                                              bool want_idx, at::Tensor workspace, int64_t entries_ready) {
     check_matrix(x, "x");
     TORCH_CHECK(crow.is_cuda() && col.is_cuda() && val.is_cuda(), "CSR components must be CUDA tensors");
     TORCH_CHECK(crow.scalar_type() == at::kLong && col.scalar_type() == at::kLong, "CSR indices must be int64");
@@ -568,7 +590,7 @@ std::vector<at::Tensor> csr_linear_forward_ws(const at::Tensor& x, const at::Ten
                                        val.data_ptr<float>(), nnz, bias_p, y.data_ptr<float>(),
                                        want_idx ? amax.data_ptr<int32_t>() : nullptr,
                                        want_idx ? amin.data_ptr<int32_t>() : nullptr, M, K, N, workspace.data_ptr(),
-                                       (size_t)workspace.numel(), entries_ready ? 1 : 0, stream.stream()),
+                                       (size_t)workspace.numel(), (int)entries_ready, stream.stream()),
                  "mam_csr_fwd_ws_ex_f32");
     if (!want_idx) return {y};
     return {y, amax, amin};
@@ -602,9 +624,30 @@ at::Tensor spmm_coo(const at::Tensor& a, const at::Tensor& b) { return spmm_csr(
 
 }  // namespace
 
-TORCH_LIBRARY(mamtorch_kernel_sparsev1, m) { m.def("cusparsemm(Tensor a, Tensor b) -> Tensor"); }
+// The MAM layer on a pruned weight, beside the reference's one sparse operator and in its namespace: forward on
+// the CSR components of W[N,K] (crow, col, val as torch.Tensor.to_sparse_csr() gives them), backward through the
+// selected pairs into a DENSE weight gradient (a pruned position whose zero product was selected receives one).
+std::vector<at::Tensor> fullyconnected_csr(const at::Tensor& a, const at::Tensor& crow, const at::Tensor& col,
+                                           const at::Tensor& val, const c10::optional<at::Tensor>& bias) {
+    return csr_linear_forward(a, crow, col, val, bias, true);
+}
+std::vector<at::Tensor> fullyconnected_csr_backward(const at::Tensor& a, const at::Tensor& w_dense,
+                                                    const at::Tensor& grad, const at::Tensor& argmax,
+                                                    const at::Tensor& argmin) {
+    return backward_impl(a, w_dense, MAM_B_NK, grad, argmax, argmin, 1.0);
+}
+
+TORCH_LIBRARY(mamtorch_kernel_sparsev1, m) {
+    m.def("cusparsemm(Tensor a, Tensor b) -> Tensor");
+    m.def("fullyconnected_csr(Tensor a, Tensor crow, Tensor col, Tensor val, Tensor? bias) -> Tensor[]");
+    m.def("fullyconnected_csr_backward(Tensor a, Tensor w_dense, Tensor grad, Tensor argmax, Tensor argmin) -> Tensor[]");
+}
 TORCH_LIBRARY_IMPL(mamtorch_kernel_sparsev1, SparseCUDA, m) { m.impl("cusparsemm", &spmm_coo); }
 TORCH_LIBRARY_IMPL(mamtorch_kernel_sparsev1, SparseCsrCUDA, m) { m.impl("cusparsemm", &spmm_csr); }
+TORCH_LIBRARY_IMPL(mamtorch_kernel_sparsev1, CUDA, m) {
+    m.impl("fullyconnected_csr", &fullyconnected_csr);
+    m.impl("fullyconnected_csr_backward", &fullyconnected_csr_backward);
+}
 
 TORCH_LIBRARY(mamtorch_kernel_v1, m) {
     m.def("fullyconnected(Tensor a, Tensor b) -> Tensor[]");
@@ -667,8 +710,10 @@ TORCH_LIBRARY(mamtorch_b200, m) {
     m.def("dense_nt(Tensor a, Tensor w) -> Tensor");
     m.def("set_dense_backend(int backend) -> ()");
     m.def("get_dense_backend() -> int");
+    m.def("check_device_flag() -> ()");
+    m.def("poll_device_flag() -> ()");
     m.def("csr_linear_forward(Tensor x, Tensor crow, Tensor col, Tensor val, Tensor? bias, bool want_idx) -> Tensor[]");
-    m.def("csr_linear_forward_ws(Tensor x, Tensor crow, Tensor col, Tensor val, Tensor? bias, bool want_idx, Tensor(a!) workspace, bool entries_ready) -> Tensor[]");
+    m.def("csr_linear_forward_ws(Tensor x, Tensor crow, Tensor col, Tensor val, Tensor? bias, bool want_idx, Tensor(a!) workspace, int entries_ready) -> Tensor[]");
     m.def("csr_workspace_bytes(int M, int K, int N, int nnz) -> int[]", &csr_workspace_bytes);
 }
 TORCH_LIBRARY_IMPL(mamtorch_b200, CUDA, m) {
@@ -692,4 +737,6 @@ TORCH_LIBRARY_IMPL(mamtorch_b200, CUDA, m) {
 TORCH_LIBRARY_IMPL(mamtorch_b200, CompositeExplicitAutograd, m) {
     m.impl("set_dense_backend", &set_dense_backend);
     m.impl("get_dense_backend", &get_dense_backend);
+    m.impl("check_device_flag", &check_device_flag);
+    m.impl("poll_device_flag", &poll_device_flag);
 }

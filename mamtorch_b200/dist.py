@@ -17,7 +17,8 @@ from typing import Iterable, Sequence
 import torch
 import torch.distributed as dist
 
-__all__ = ["row_shard", "shard_rows", "broadcast_parameters", "allreduce_gradients", "allreduce_counts"]
+__all__ = ["row_shard", "shard_rows", "broadcast_parameters", "allreduce_gradients", "allreduce_counts",
+           "OverlappedGradSync"]
 
 
 def row_shard(total_rows: int, world_size: int, rank: int) -> tuple[int, int]:
@@ -45,35 +46,68 @@ def broadcast_parameters(module: torch.nn.Module, src: int = 0) -> None:
 
 
 def _flat_allreduce(tensors: Sequence[torch.Tensor], bucket_bytes: int) -> None:
-    """Sum over ranks, packing small tensors into buckets so each collective amortises its launch."""
-    bucket, size = [], 0
-
-    def flush():
-        nonlocal bucket, size
-        if not bucket:
-            return
-        if len(bucket) == 1:
-            dist.all_reduce(bucket[0])
-        else:
-            flat = torch.cat([t.reshape(-1) for t in bucket])
-            dist.all_reduce(flat)
-            off = 0
-            for t in bucket:
-                t.copy_(flat[off:off + t.numel()].view_as(t))
-                off += t.numel()
-        bucket, size = [], 0
-
+    """Sum over ranks, in place.  Tensors of `bucket_bytes` or more (a layer's weight gradient) go as they
+    are -- no staging copy; smaller ones (biases, counters) of one dtype are grouped into one coalesced
+    launch, or, where the backend has no coalescing, packed into one flat buffer and copied back."""
+    small: dict[torch.dtype, list[torch.Tensor]] = {}
     for t in tensors:
-        nbytes = t.numel() * t.element_size()
-        if bucket and (size + nbytes > bucket_bytes or t.dtype != bucket[0].dtype):
-            flush()
-        bucket.append(t)
-        size += nbytes
-    flush()
+        if t.numel() * t.element_size() >= bucket_bytes or not t.is_contiguous():
+            dist.all_reduce(t)
+        else:
+            small.setdefault(t.dtype, []).append(t)
+    for group in small.values():
+        if len(group) == 1:
+            dist.all_reduce(group[0])
+            continue
+        flat = torch.cat([t.reshape(-1) for t in group])
+        dist.all_reduce(flat)
+        off = 0
+        for t in group:
+            t.copy_(flat[off:off + t.numel()].view_as(t))
+            off += t.numel()
+
+
+class OverlappedGradSync:
+    """All-reduces every parameter's gradient as soon as autograd has finished accumulating it.
+
+    A hook on each parameter (`register_post_accumulate_grad_hook`) starts an asynchronous, in-place
+    all-reduce of `param.grad`; with NCCL it runs on the process group's own stream, ordered after the
+    kernel that produced the gradient, while the backward of the earlier layers carries on on the compute
+    stream.  The weight gradient of the last layer thus crosses NVLink under the backward of the layers
+    before it.  `finish()` makes the current stream wait for all started collectives -- call it once
+    after `backward()`, before the gradients are read.  Sums, like `allreduce_gradients` (pass
+    `average=True` for the mean).  `enabled = False` turns the hooks into no-ops."""
+
+    def __init__(self, params: Iterable[torch.nn.Parameter], average: bool = False, group=None):
+        self.average, self.group, self.enabled = average, group, True
+        self._works: list = []
+        self._grads: list[torch.Tensor] = []
+        self._handles = [p.register_post_accumulate_grad_hook(self._hook) for p in params if p.requires_grad]
+
+    def _hook(self, param: torch.nn.Parameter) -> None:
+        if not self.enabled or param.grad is None:
+            return
+        self._works.append(dist.all_reduce(param.grad, group=self.group, async_op=True))
+        self._grads.append(param.grad)
+
+    def finish(self) -> None:
+        for w in self._works:
+            w.wait()
+        if self.average:
+            n = dist.get_world_size(self.group)
+            for g in self._grads:
+                g.div_(n)
+        self._works.clear()
+        self._grads.clear()
+
+    def remove(self) -> None:
+        for h in self._handles:
+            h.remove()
+        self._handles.clear()
 
 
 def allreduce_gradients(params: Iterable[torch.nn.Parameter], average: bool = False,
-                        bucket_bytes: int = 32 << 20) -> None:
+                        bucket_bytes: int = 1 << 20) -> None:
     """Sums `.grad` of the given parameters over all ranks, in place.  With row sharding the sum
     (not the mean) is the gradient of the un-sharded batch."""
     grads = [p.grad for p in params if p.grad is not None]
@@ -95,4 +129,4 @@ def allreduce_counts(modules: Iterable[torch.nn.Module]) -> None:
             t = getattr(m, name, None)
             if isinstance(t, torch.Tensor):
                 tensors.append(t)
-    _flat_allreduce(tensors, 32 << 20)
+    _flat_allreduce(tensors, 1 << 20)

@@ -128,6 +128,22 @@ def register_blended(ns: str, with_fast: bool, with_dense: bool) -> None:
             check_bias(a, b, bias)
             return a.new_empty((a.size(0), b.size(1)))
 
+        # like the reference (mamtorch/kernel/v3/fullyconnected_fast.py:26-52) the values-only operator
+        # carries the dense gradients: grad @ b.T, a.T @ grad, and the column sum for the bias
+        def setup_fast(ctx, inputs, output):
+            a, b, _bias, _beta = inputs
+            need = ctx.needs_input_grad[0] or ctx.needs_input_grad[1]
+            ctx.save_for_backward(a if need else None, b if need else None)
+
+        def backward_fast(ctx, grad):
+            a, b = ctx.saved_tensors
+            da = grad @ b.T if ctx.needs_input_grad[0] else None
+            db = a.T @ grad if ctx.needs_input_grad[1] else None
+            dbias = grad.sum(0) if ctx.needs_input_grad[2] else None
+            return da, db, dbias, None
+
+        torch.library.register_autograd(f"{ns}::fullyconnected_fast", backward_fast, setup_context=setup_fast)
+
     if with_dense:
         @torch.library.register_fake(f"{ns}::dense")
         def _(a, b):

@@ -122,7 +122,9 @@ def _forward_rows(x, weight, w2d, bias, dflat, alpha, beta, geom, taps, need_ind
         return _ops.linear_forward(rows, w2d, bias, dflat, alpha, beta, need_indices)
     w_taps = weight.permute(0, 3, 2, 1).reshape(Fo, -1).contiguous()          # [F, (kw, kh, c)]
     if _ops.conv_implicit_applies(B, C, H, W, kH, kW, sh, sw, ph, pw):
-        x_nhwc = _ops.conv_channels_last(x)                                   # a view if x is channels_last
+        x_nhwc = x.permute(0, 2, 3, 1)                                        # as it is if x is channels_last
+        if not x_nhwc.is_contiguous():
+            x_nhwc = _ops.conv_channels_last(x)                               # else one permuting copy
         if x_nhwc.data_ptr() % 16 == 0:
             return _ops.conv_forward_implicit(x_nhwc, w_taps, bias, dflat, alpha, beta, kH, kW, sh, sw, ph, pw,
                                               need_indices)

@@ -58,6 +58,16 @@ def _(x, weight, bias, dense, alpha, beta, split_width):
     return x.new_empty((x.size(0), weight.size(0)))
 
 
+@torch.library.register_fake("mamtorch_b200::check_device_flag")
+def _():
+    return None
+
+
+@torch.library.register_fake("mamtorch_b200::poll_device_flag")
+def _():
+    return None
+
+
 @torch.library.register_fake("mamtorch_b200::conv_channels_last")
 def _(x):
     B, C, H, W = x.shape
@@ -121,15 +131,31 @@ def _(a, w):
 
 def set_dense_backend(name: str) -> None:
     """Backend of the dense (sum-of-products) beta term: "tf32" = this library's tcgen05 kernel
-    (TF32 inputs, fp32 accumulation, 1e-3 relative to fp32; the default), "fp32" = torch/cuBLAS in
-    full fp32, bit-compatible with the reference's `F.linear` / `at::linalg_matmul`."""
-    if name not in ("tf32", "fp32"):
-        raise ValueError("dense backend must be 'tf32' or 'fp32'")
-    _ops.set_dense_backend(1 if name == "tf32" else 0)
+    (TF32 inputs, fp32 accumulation, 1e-3 relative to fp32), "fp32" = torch/cuBLAS in full fp32, what
+    the reference's `F.linear` / `at::linalg_matmul` compute, "auto" (the default) = "tf32" only while
+    `torch.backends.cuda.matmul.allow_tf32` is on, as for torch's own matrix products."""
+    if name not in ("tf32", "fp32", "auto"):
+        raise ValueError("dense backend must be 'tf32', 'fp32' or 'auto'")
+    _ops.set_dense_backend({"tf32": 1, "fp32": 0, "auto": -1}[name])
 
 
 def get_dense_backend() -> str:
-    return "tf32" if _ops.get_dense_backend() else "fp32"
+    return {1: "tf32", 0: "fp32", -1: "auto"}[int(_ops.get_dense_backend())]
+
+
+def check_device_flag() -> None:
+    """Waits for the device and raises RuntimeError if a kernel of this library gave up a bounded wait since
+    the last check (its outputs are then invalid).  The modules call the non-waiting `poll_device_flag` on
+    every forward and in `update_selection_count`, which reports such a time-out one call late at most;
+    code that drives `torch.ops.mamtorch_kernel_v*` directly should call this where it synchronises anyway
+    (end of an epoch, before a checkpoint)."""
+    _ops.check_device_flag()
+
+
+def poll_device_flag() -> None:
+    """The same check without waiting for the device: raises if an EARLIER poll's copy of the flag shows a
+    time-out, then queues the next fetch on the current stream."""
+    _ops.poll_device_flag()
 
 
 class _DenseLinear(torch.autograd.Function):

@@ -107,6 +107,7 @@ class FullyConnected(Module):
         # if a backward pass already ran on these indices it counted the hits on its way
         hits = self._hit_sink.take(self.argmax) if self._hit_sink is not None else None
         MF.selection_count_update_(self.max_selection_count, self.argmax, self.argmin, hits)
+        MF.poll_device_flag()     # raises if a kernel of an earlier call gave up a bounded wait
 
     def selection_hits(self):
         """True per-weight hit counts (hit_max, hit_min) of the last stored forward: an extension,
@@ -118,6 +119,8 @@ class FullyConnected(Module):
 
     # -- forward (reference :133-208)
     def forward(self, input: Tensor) -> Tensor:
+        if input.is_cuda:
+            MF.poll_device_flag()     # raises if a kernel of an earlier call gave up a bounded wait
         if self.relu_in:
             input = F.relu(input)
         x = input.reshape(-1, input.size(-1))
@@ -138,6 +141,11 @@ class FullyConnected(Module):
             y = self.beta * dense
             if self.bias is not None:
                 y = y + self.bias
+            if self.store_args and self.splits <= 1:
+                # the reference runs the MAM kernel on this path whatever beta is and keeps its indices
+                # (:178-186), so that update_selection_count() works from the first step of the schedule
+                with torch.no_grad():
+                    _, self.argmax, self.argmin = MF.mam_linear(x.detach(), w.detach(), need_indices=True)
         elif self.splits > 1:
             # K is cut into slices; every slice contributes its own max+min (reference :164-176)
             y = None

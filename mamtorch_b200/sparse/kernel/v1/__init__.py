@@ -10,7 +10,7 @@ from __future__ import annotations
 import torch
 from torch import Tensor
 
-__all__ = ["cusparsemm", "mam_linear_csr", "prune_to_csr"]
+__all__ = ["cusparsemm", "mam_linear_csr", "prune_to_csr", "fullyconnected_csr", "fullyconnected_csr_backward"]
 
 
 def cusparsemm(a: Tensor, b: Tensor) -> Tensor:
@@ -32,6 +32,30 @@ def _(x, crow, col, val, bias, want_idx):
     if want_idx:
         out += [x.new_empty(shape, dtype=torch.int), x.new_empty(shape, dtype=torch.int)]
     return out
+
+
+@torch.library.register_fake("mamtorch_kernel_sparsev1::fullyconnected_csr")
+def _(a, crow, col, val, bias):
+    shape = (a.size(0), crow.size(0) - 1)
+    return [a.new_empty(shape), a.new_empty(shape, dtype=torch.int), a.new_empty(shape, dtype=torch.int)]
+
+
+@torch.library.register_fake("mamtorch_kernel_sparsev1::fullyconnected_csr_backward")
+def _(a, w_dense, grad, argmax, argmin):
+    return [torch.empty_like(a), torch.empty_like(w_dense)]
+
+
+def fullyconnected_csr(a: Tensor, w_csr: Tensor, bias: Tensor | None = None):
+    """[y, argmax, argmin] of the MAM layer on a pruned weight: a[M,K], w_csr sparse-CSR [N,K].  Operator
+    `mamtorch_kernel_sparsev1::fullyconnected_csr`, beside the reference's `cusparsemm`."""
+    return torch.ops.mamtorch_kernel_sparsev1.fullyconnected_csr.default(
+        a, w_csr.crow_indices(), w_csr.col_indices(), w_csr.values(), bias)
+
+
+def fullyconnected_csr_backward(a: Tensor, w_dense: Tensor, grad: Tensor, argmax: Tensor, argmin: Tensor):
+    """[a_grad, w_grad (dense, like w_dense[N,K])] through the selected pairs; `w_dense` is the weight with
+    zeros at the pruned positions."""
+    return torch.ops.mamtorch_kernel_sparsev1.fullyconnected_csr_backward.default(a, w_dense, grad, argmax, argmin)
 
 
 def prune_to_csr(weight: Tensor, keep_mask: Tensor) -> Tensor:

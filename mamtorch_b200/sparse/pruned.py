@@ -6,11 +6,14 @@ magnitude is at or below the p-quantile of that layer's magnitudes
 (`:137-160`, `GMP`) -- and then keeps running the dense kernels on the zeros.  Here the same masks are
 formed on the device and the layer runs on the stored weights only:
 
-  * `magnitude_threshold`, `magnitude_keep_mask`  the quantile threshold and the keep mask of one weight;
-  * `global_magnitude_threshold`                  one threshold over several weights;
-  * `PrunedFullyConnected`                        a MAM layer that keeps a dense parameter (so that it trains
-                                                  like the reference's zeroed layer: selected pruned positions
-                                                  receive gradient) plus its mask, and evaluates through CSR.
+  * `magnitude_threshold`, `magnitude_keep_mask`  the quantile threshold (torch.quantile's linear interpolation,
+                                                  as `LMP` uses it) and the keep mask of one weight;
+  * `global_magnitude_threshold`                  one threshold over several weights: the element at position
+                                                  int(p * n) of the sorted magnitudes, `GMP`'s own rule (`:147-151`);
+  * `PrunedFullyConnected`                        a MAM layer that keeps a dense parameter plus its mask and
+                                                  evaluates through CSR.  The forward sees `weight * keep_mask`,
+                                                  so the chain rule hands pruned positions a zero gradient: they
+                                                  stay where they are (and stay pruned) under any optimiser.
 """
 from __future__ import annotations
 
@@ -44,14 +47,40 @@ def magnitude_threshold(weight: Tensor, fraction: float) -> Tensor:
 
 
 def global_magnitude_threshold(weights, fraction: float) -> Tensor:
-    """One threshold for several weights together (global magnitude pruning)."""
+    """One threshold for several weights together (global magnitude pruning): the magnitude at position
+    int(fraction * n) of the n sorted magnitudes, clamped to the last one -- the reference's rule
+    (`examples/vitb16_imagenet1k/pruning_utils.py:147-151`), not an interpolated quantile."""
+    if not 0.0 <= fraction <= 1.0:
+        raise ValueError("fraction must be in [0, 1]")
     flat = torch.cat([w.detach().abs().flatten().float() for w in weights])
-    return _quantile(flat, fraction)
+    s = flat.sort().values
+    return s[max(0, min(int(fraction * s.numel()), s.numel() - 1))]
 
 
 def magnitude_keep_mask(weight: Tensor, threshold) -> Tensor:
     """1.0 where |weight| > threshold, 0.0 elsewhere: the reference zeroes `abs() <= threshold`."""
     return (weight.detach().abs() > threshold).to(weight.dtype)
+
+
+class _MamLinearCsrKept(torch.autograd.Function):
+    """CSR forward on a scratch buffer that keeps the regrouped sparsity pattern between calls; backward through
+    the selected pairs into the dense (zero-filled) weight."""
+
+    @staticmethod
+    def forward(ctx, x, crow, col, val, dense_weight, bias, ws, ready):
+        y, argmax, argmin = torch.ops.mamtorch_b200.csr_linear_forward_ws(x, crow, col, val, bias, True, ws, ready)
+        ctx.save_for_backward(x, dense_weight, argmax, argmin)
+        ctx.has_bias = bias is not None
+        ctx.mark_non_differentiable(argmax, argmin)
+        return y, argmax, argmin
+
+    @staticmethod
+    def backward(ctx, gy, _a, _b):
+        x, w, argmax, argmin = ctx.saved_tensors
+        gy = gy.contiguous()
+        dx, dw = torch.ops.mamtorch_b200.linear_backward(x, w, gy, argmax, argmin, 1.0)
+        dbias = gy.sum(0) if ctx.has_bias and ctx.needs_input_grad[5] else None
+        return dx, None, None, None, dw, dbias, None, None
 
 
 class PrunedFullyConnected(nn.Module):
@@ -73,6 +102,9 @@ class PrunedFullyConnected(nn.Module):
         self._csr_key = None
         self._ws = None          # scratch of the tiled kernels, kept between inference calls
         self._ws_key = None      # the CSR build whose regrouped entries the scratch holds
+        self._ws_pattern = None  # the mask whose regrouped pattern the scratch holds (training steps)
+        self._pattern_key = None
+        self._pattern_val = None
         nn.init.kaiming_uniform_(self.weight, a=math.sqrt(5))
         if self.bias is not None:
             bound = 1 / math.sqrt(in_features) if in_features > 0 else 0
@@ -100,7 +132,7 @@ class PrunedFullyConnected(nn.Module):
             threshold = magnitude_threshold(self.weight, fraction)
         self.keep_mask.copy_(magnitude_keep_mask(self.weight, threshold))
         self._csr = None
-        self._ws_key = None
+        self._ws_key = self._ws_pattern = self._pattern_key = None
         return self
 
     def sparsity(self) -> float:
@@ -113,36 +145,78 @@ class PrunedFullyConnected(nn.Module):
             self._csr_key = key
         return self._csr
 
+    def _scratch(self, x: Tensor, nnz: int):
+        """(scratch buffer large enough for this call or None where the tiled kernels do not apply, was it kept)."""
+        M, K = x.shape
+        need, _ = torch.ops.mamtorch_b200.csr_workspace_bytes(M, K, self.out_features, nnz)
+        if need == 0:
+            return None, False
+        kept = self._ws is not None and self._ws.numel() >= need and self._ws.device == x.device
+        if not kept:
+            self._ws = torch.empty(need, dtype=torch.uint8, device=x.device)
+            self._ws_key = self._ws_pattern = None
+        return self._ws, kept
+
     def _forward_kept_scratch(self, x: Tensor, csr: Tensor):
         """Inference on a weight that has not changed since the last call: the regrouped entries the tiled
         kernels work from are still in the scratch buffer, so only the activations are prepared again."""
         ops = torch.ops.mamtorch_b200
         crow, col, val = csr.crow_indices(), csr.col_indices(), csr.values()
-        M, K = x.shape
-        if M == 0 or val.numel() == 0:
+        if x.size(0) == 0 or val.numel() == 0:
             return None
-        need, _ = ops.csr_workspace_bytes(M, K, self.out_features, val.numel())
-        if need == 0:
+        ws, kept = self._scratch(x, val.numel())
+        if ws is None:
             return None                      # the tiled kernels do not apply (few rows): no scratch involved
-        ready = (self._ws is not None and self._ws_key == self._csr_key and self._ws.numel() >= need
-                 and self._ws.device == x.device)
-        if not ready and (self._ws is None or self._ws.numel() < need or self._ws.device != x.device):
-            self._ws = torch.empty(need, dtype=torch.uint8, device=x.device)
+        ready = 1 if (kept and self._ws_key == ("values", self._csr_key)) else 0
         out = ops.csr_linear_forward_ws(x.contiguous(), crow.contiguous(), col.contiguous(), val.contiguous(),
-                                        self.bias, True, self._ws, ready)
-        self._ws_key = self._csr_key
+                                        self.bias, True, ws, ready)
+        self._ws_key = ("values", self._csr_key)
+        self._ws_pattern = None
         return out
+
+    def _pattern(self):
+        """CSR pattern of the mask -- crow, col and the flat positions of the kept weights -- rebuilt only when
+        the mask changes; a training step then gathers the kept values with one index_select."""
+        key = (self.keep_mask._version, self.keep_mask.data_ptr())
+        if self._pattern_key != key:
+            csr = self.keep_mask.to_sparse_csr()
+            crow, col = csr.crow_indices().contiguous(), csr.col_indices().contiguous()
+            rows = torch.repeat_interleave(torch.arange(self.out_features, device=col.device), crow.diff())
+            self._pattern_val = (crow, col, rows * self.in_features + col)
+            self._pattern_key = key
+        return self._pattern_val
+
+    def _forward_training(self, x: Tensor):
+        """Forward + gradient on a weight whose values move every step while its mask stays: the sparsity
+        pattern (and the segment offsets regrouped from it in the scratch buffer) is kept across steps and
+        only the stored values are gathered and regrouped again."""
+        crow, col, flat = self._pattern()
+        dense = self.weight * self.keep_mask
+        if x.size(0) == 0 or flat.numel() == 0:
+            return None, dense
+        val = dense.detach().reshape(-1).index_select(0, flat)
+        ws, kept = self._scratch(x, flat.numel())
+        if ws is None:
+            return None, dense
+        ready = 2 if (kept and self._ws_pattern == self._pattern_key) else 0
+        out = _MamLinearCsrKept.apply(x.contiguous(), crow, col, val, dense, self.bias, ws, ready)
+        self._ws_pattern, self._ws_key = self._pattern_key, None
+        return out, dense
 
     def forward(self, input: Tensor) -> Tensor:
         x = input.reshape(-1, input.size(-1))
-        csr = self._weight_csr()
         wants_grad = torch.is_grad_enabled() and (self.weight.requires_grad or x.requires_grad)
-        out = None if wants_grad else self._forward_kept_scratch(x, csr)
-        if out is not None:
-            y, self.argmax, self.argmin = out
+        out = None
+        if wants_grad:
+            out, dense = self._forward_training(x)
+            if out is None:
+                out = mam_linear_csr(x, (dense.detach()).to_sparse_csr(), self.bias, dense_weight=dense)
         else:
-            dense = self.weight * self.keep_mask if torch.is_grad_enabled() and self.weight.requires_grad else None
-            y, self.argmax, self.argmin = mam_linear_csr(x, csr, self.bias, dense_weight=dense)
+            csr = self._weight_csr()
+            out = self._forward_kept_scratch(x, csr)
+            if out is None:
+                out = mam_linear_csr(x, csr, self.bias)
+        y, self.argmax, self.argmin = out
         return y.view(input.shape[:-1] + (self.out_features,))
 
     def extra_repr(self) -> str:

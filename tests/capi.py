@@ -18,7 +18,7 @@ def _stream():
 
 
 def set_variant(with_idx: bool, variant: int):
-    _lib.check(_lib.lib().mam_set_fwd_variant(int(with_idx), variant), "mam_set_fwd_variant")
+    _lib.check(_lib.lib().mam_tune_set(int(with_idx), variant), "mam_tune_set")
 
 
 def forward(a, b, layout=KN, bias=None, dense=None, blend=False, alpha=1.0, beta=0.0, want_idx=True):

@@ -13,9 +13,12 @@ from mamtorch_b200 import _lib
 
 
 def header_functions():
-    src = open(os.path.join(ROOT, "include", "mam_b200.h")).read()
-    src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
-    return sorted(set(re.findall(r"\b(mam_[a-z0-9_]+)\s*\(", src)))
+    names = set()
+    for header in ("mam_b200.h", "mam_b200_tuning.h"):
+        src = open(os.path.join(ROOT, "include", header)).read()
+        src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
+        names |= set(re.findall(r"\b(mam_[a-z0-9_]+)\s*\(", src))
+    return sorted(names)
 
 
 def test_library_exports_every_declared_symbol():
@@ -23,7 +26,7 @@ def test_library_exports_every_declared_symbol():
     names = header_functions()
     assert len(names) >= 10
     for n in names:
-        assert hasattr(L, n), f"{n} declared in include/mam_b200.h but not exported"
+        assert hasattr(L, n), f"{n} declared in include/*.h but not exported"
     assert sorted(_lib.ABI) == names, "ctypes table and header disagree"
 
 
@@ -31,8 +34,8 @@ def test_status_strings_and_version():
     L = _lib.lib()
     assert L.mam_abi_version() == 1
     assert _lib.status_str(0) == "ok"
-    seen = {_lib.status_str(i) for i in range(7)}
-    assert len(seen) == 7 and "unknown status" not in seen
+    seen = {_lib.status_str(i) for i in range(8)}
+    assert len(seen) == 8 and "unknown status" not in seen
     assert _lib.status_str(99) == "unknown status"
 
 
@@ -47,8 +50,9 @@ def test_bad_arguments_are_rejected_before_any_device_work():
     assert L.mam_bwd_f32(one, one, 0, one, one, one, one, null, 1.0, 4, 4, 4, null) == 1
     assert L.mam_selcount_i32(one, one, one, one, 0, 4, 4, null) == 1
     assert L.mam_transpose_f32(one, null, 4, 4, null) == 1
-    assert L.mam_set_fwd_variant(0, 99) == 1
-    assert L.mam_set_fwd_variant(0, -1) == 0
+    assert L.mam_tune_set(0, 99) == 1
+    assert L.mam_tune_set(99, 0) == 1
+    assert L.mam_tune_set(0, -1) == 0
 
 
 def test_workspace_query():

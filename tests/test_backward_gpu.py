@@ -55,7 +55,7 @@ def test_random_backward_against_c_oracle(shape, mode, cuda):
     imin[0, :] = imax[0, :]
     da_ref, dw_ref = c_oracle.backward(a.numpy(), w.numpy(), grad.numpy(), imax, imin, b_is_nk=True)
     from mamtorch_b200 import _lib
-    _lib.check(_lib.lib().mam_set_fwd_variant(3, mode), "backward form")
+    _lib.check(_lib.lib().mam_tune_set(3, mode), "backward form")
     try:
         da, dw = capi.backward(a.to(cuda), w.to(cuda), grad.to(cuda),
                                torch.from_numpy(imax).to(torch.int32).to(cuda),
@@ -64,7 +64,7 @@ def test_random_backward_against_c_oracle(shape, mode, cuda):
                                  torch.from_numpy(imax).to(torch.int32).to(cuda),
                                  torch.from_numpy(imin).to(torch.int32).to(cuda), capi.KN)
     finally:
-        _lib.lib().mam_set_fwd_variant(3, 0)
+        _lib.lib().mam_tune_set(3, 0)
     assert_grad_close(da.cpu().numpy(), da_ref)
     assert_grad_close(dw.cpu().numpy(), dw_ref)
     assert_grad_close(dak.cpu().numpy(), da_ref)

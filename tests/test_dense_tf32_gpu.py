@@ -68,12 +68,12 @@ def test_tf32_tail_slices_give_the_same_bits_as_whole_tiles(shape, cuda):
     a = torch.randint(-8, 9, (M, K), generator=g).float().to(cuda)
     w = torch.randint(-8, 9, (N, K), generator=g).float().to(cuda)
     try:
-        _lib.check(L.mam_set_fwd_variant(4, 0), "selector")
+        _lib.check(L.mam_tune_set(4, 0), "selector")
         whole = _dense(a, w)
-        _lib.check(L.mam_set_fwd_variant(4, 1), "selector")
+        _lib.check(L.mam_tune_set(4, 1), "selector")
         sliced = _dense(a, w)
     finally:
-        L.mam_set_fwd_variant(4, 1)
+        L.mam_tune_set(4, 1)
     torch.cuda.synchronize()
     assert L.mam_check_device_flag() == 0
     assert torch.equal(sliced, whole)

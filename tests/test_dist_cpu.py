@@ -7,7 +7,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from mamtorch_b200.dist import allreduce_gradients, row_shard, shard_rows
+from mamtorch_b200.dist import OverlappedGradSync, allreduce_gradients, row_shard, shard_rows
 from oracle import mam_oracle
 
 
@@ -46,7 +46,24 @@ def _worker(rank, world, port, out):
         bp = torch.nn.Parameter(torch.zeros(N))
         wp.grad = db.T.contiguous()
         bp.grad = gs.sum(0)
-        allreduce_gradients([wp, bp], bucket_bytes=64)       # tiny buckets: exercises packing and flushing
+        wp2 = torch.nn.Parameter(w.clone())
+        wp2.grad = db.T.contiguous()
+        allreduce_gradients([wp, bp], bucket_bytes=4096)     # both below the bucket size: packed into one launch
+        allreduce_gradients([wp2], bucket_bytes=64)          # at or above it: reduced in place, no staging copy
+        # gradient hooks: the all-reduce starts when autograd has accumulated the gradient, finish() waits
+        lin_w = torch.nn.Parameter(w.clone())
+        lin_b = torch.nn.Parameter(torch.zeros(N))
+        sync = OverlappedGradSync([lin_w, lin_b])
+        ((xs @ lin_w.T + lin_b) * gs).sum().backward()
+        sync.finish()
+        hooked_ok = torch.allclose(lin_w.grad, gy.T @ x, rtol=1e-5, atol=1e-5) and \
+            torch.allclose(lin_b.grad, gy.sum(0), rtol=1e-5, atol=1e-6)
+        sync.enabled = False
+        lin_w.grad = None
+        ((xs @ lin_w.T) * gs).sum().backward()
+        sync.finish()
+        hooked_ok &= torch.allclose(lin_w.grad, gs.T @ xs, rtol=1e-5, atol=1e-5)   # disabled: the rank's own gradient
+        sync.remove()
         if rank == 0:
             y_full, imax_f, imin_f = mam_oracle.mam_forward(x, b)
             _, db_full = mam_oracle.mam_backward(x, b, gy, imax_f, imin_f)
@@ -54,6 +71,8 @@ def _worker(rank, world, port, out):
             ok = torch.equal(y, y_full[lo:hi])
             ok &= torch.allclose(wp.grad, db_full.T, rtol=1e-5, atol=1e-6)
             ok &= torch.allclose(bp.grad, gy.sum(0), rtol=1e-5, atol=1e-6)
+            ok &= torch.allclose(wp2.grad, db_full.T, rtol=1e-5, atol=1e-6)
+            ok &= bool(hooked_ok)
             out.put(bool(ok))
     finally:
         dist.destroy_process_group()

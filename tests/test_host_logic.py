@@ -69,8 +69,12 @@ def test_magnitude_thresholds_and_masks_match_the_reference_rule():
         zeroed[zeroed.abs() <= thr] = 0          # examples/vitb16_imagenet1k/pruning_utils.py:105-107
         assert torch.equal(w * keep, zeroed)
     w2 = torch.randn(10, 30, generator=g) * 3
-    thr_g = global_magnitude_threshold([w, w2], 0.5)
-    assert torch.equal(thr_g, torch.quantile(torch.cat([w.flatten().abs(), w2.flatten().abs()]), 0.5))
+    # the global rule is the reference's literal one: sorted magnitudes, element int(p * n), clamped
+    # (examples/vitb16_imagenet1k/pruning_utils.py:147-151)
+    both = torch.cat([w.flatten().abs(), w2.flatten().abs()]).sort().values
+    for p in (0.0, 0.37, 0.5, 1.0):
+        thr_g = global_magnitude_threshold([w, w2], p)
+        assert torch.equal(thr_g, both[max(0, min(int(p * len(both)), len(both) - 1))])
     with pytest.raises(ValueError):
         magnitude_threshold(w, 1.5)
 

@@ -221,19 +221,92 @@ def test_conv2d_matches_im2col_oracle(cuda):
 
 
 def test_conv1d(cuda):
+    """MAMConv1d against the convolution oracle on the input with a height of one: all values, all indices
+    (k = c*kW + kw in both), gradients through the oracle's selected products, and the selection count."""
     import mamtorch_b200 as mamtorch
 
-    conv = mamtorch.nn.MAMConv1d(4, 6, 3, padding=1, bias=False).to(cuda)
-    x = _rand((3, 4, 11), 9, cuda)
+    torch.manual_seed(4)
+    conv = mamtorch.nn.MAMConv1d(4, 6, 3, padding=1, bias=True).to(cuda)
+    x = _rand((3, 4, 11), 9, cuda).requires_grad_()
     y = conv(x)
-    y_ref, imax_ref, _ = mam_oracle.mam_conv2d_forward(x.cpu().unsqueeze(2), conv.weight.detach().cpu().unsqueeze(2),
-                                                       stride=1, padding=0) if False else (None, None, None)
-    xp = torch.nn.functional.pad(x.cpu(), (1, 1))
-    w = conv.weight.detach().cpu()
-    for (b_, f, t) in [(0, 0, 0), (2, 5, 10), (1, 3, 4)]:
-        p = (xp[b_, :, t:t + 3] * w[f]).reshape(-1)
-        assert y[b_, f, t].item() == (p.max() + p.min()).item()
-        assert conv.argmax[b_, f, t].item() == int(p.argmax())
+    w4 = conv.weight.detach().cpu().unsqueeze(2)                       # [F,C,1,kW]
+    y_ref, imax_ref, imin_ref = mam_oracle.mam_conv2d_forward(x.detach().cpu().unsqueeze(2), w4, conv.bias.detach().cpu(),
+                                                              stride=1, padding=(0, 1))
+    assert y.shape == (3, 6, 11)
+    assert torch.equal(y.detach().cpu(), y_ref.squeeze(2))
+    assert torch.equal(conv.argmax.cpu().long(), imax_ref.squeeze(2))
+    assert torch.equal(conv.argmin.cpu().long(), imin_ref.squeeze(2))
+    gy = _rand((3, 6, 11), 10, cuda)
+    y.backward(gy)
+    xw = x.detach().cpu().requires_grad_()
+    ww = conv.weight.detach().cpu().requires_grad_()
+    rows = mam_oracle.conv2d_as_rows(xw.unsqueeze(2), (1, 3), padding=(0, 1))
+    wf = ww.reshape(6, -1)
+    im = imax_ref.permute(0, 2, 3, 1).reshape(-1, 6)
+    imn = imin_ref.permute(0, 2, 3, 1).reshape(-1, 6)
+    r = torch.arange(rows.shape[0])[:, None].expand_as(im)
+    c = torch.arange(6)[None, :].expand_as(im)
+    ((rows[r, im] * wf[c, im] + rows[r, imn] * wf[c, imn]) * gy.cpu().permute(0, 2, 1).reshape(-1, 6)).sum().backward()
+    assert_grad_close(x.grad.cpu().numpy(), xw.grad.numpy())
+    assert_grad_close(conv.weight.grad.cpu().numpy(), ww.grad.numpy())
+    conv.update_selection_count()
+    want = mam_oracle.selection_count_update(torch.zeros(6, 12, dtype=torch.int32), im, imn)
+    assert torch.equal(conv.max_selection_count.cpu().reshape(6, 12), want)
+
+
+def test_conv2d_selection_count_against_the_oracle(cuda):
+    import mamtorch_b200 as mamtorch
+
+    torch.manual_seed(5)
+    conv = mamtorch.nn.MAMConv2d(5, 7, 3, padding=1, stride=2).to(cuda)
+    x = _rand((2, 5, 9, 8), 12, cuda)
+    conv(x)
+    conv.update_selection_count()
+    conv(x * -1.5)
+    conv.update_selection_count()
+    want = torch.zeros(7, 45, dtype=torch.int32)
+    for xs in (x, x * -1.5):
+        _, imax, imin = mam_oracle.mam_conv2d_forward(xs.cpu(), conv.weight.detach().cpu(), conv.bias.detach().cpu(),
+                                                      stride=2, padding=1)
+        want = mam_oracle.selection_count_update(want, imax.permute(0, 2, 3, 1).reshape(-1, 7),
+                                                 imin.permute(0, 2, 3, 1).reshape(-1, 7))
+    assert torch.equal(conv.max_selection_count.cpu().reshape(7, 45), want)
+
+
+def test_store_args_before_the_first_vcon_step(cuda):
+    """While beta is still 1 (every layer with vcon_steps > 0 starts there) the output is the dense term alone,
+    but the indices are stored all the same, as in the reference (mamtorch/nn/v4/fullyconnected.py:178-186), so a
+    loop that updates the counts from step 0 works."""
+    import mamtorch_b200 as mamtorch
+
+    torch.manual_seed(6)
+    layer = mamtorch.nn.FullyConnected(48, 20, vcon_steps=4, store_args=True).to(cuda)
+    assert layer.beta == 1.0
+    x = _rand((9, 48), 13, cuda)
+    y = layer(x)
+    _, imax_ref, imin_ref = mam_oracle.mam_forward(x.cpu(), layer.weight.detach().T.contiguous().cpu())
+    assert torch.equal(layer.argmax.cpu().long(), imax_ref) and torch.equal(layer.argmin.cpu().long(), imin_ref)
+    want_y = x.cpu() @ layer.weight.detach().cpu().T + layer.bias.detach().cpu()
+    assert torch.allclose(y.detach().cpu(), want_y, rtol=1e-5, atol=1e-5)
+    layer.update_selection_count()
+    want = mam_oracle.selection_count_update(torch.zeros(20, 48, dtype=torch.int32), imax_ref, imin_ref)
+    assert torch.equal(layer.max_selection_count.cpu(), want)
+
+
+def test_device_flag_checks_are_exposed_to_torch_users(cuda):
+    """`check_device_flag` (waits for the device) and `poll_device_flag` (does not) are operators of the package;
+    after healthy launches neither raises."""
+    import mamtorch_b200 as mamtorch
+    from mamtorch_b200.nn import functional as MF
+
+    layer = mamtorch.nn.FullyConnected(64, 32, store_args=True).to(cuda)
+    layer(_rand((40, 64), 14, cuda)).sum().backward()
+    layer.update_selection_count()
+    MF.poll_device_flag()
+    torch.cuda.synchronize()
+    MF.poll_device_flag()
+    MF.check_device_flag()
+    torch.ops.mamtorch_b200.check_device_flag()
 
 
 def test_beta_blended_training_step(cuda):
