@@ -145,7 +145,7 @@ def bind_to_gpu_numa_node(local: int) -> None:
 # ------------------------------------------------------------------------------------------------
 class CpuPath:
     """The reference's CPU functions: its own checker (`test/reference.py`, byte-compiled into
-    oracle/_ref/reference.pyc by oracle/build_ref_py.py where a checkout was at hand when the tree was
+    oracle/_ref/reference_checker.bin by oracle/build_ref_py.py where a checkout was at hand when the tree was
     built; kind "reference") or their restatement in oracle/mam_oracle.py (kind "port")."""
 
     def __init__(self):
@@ -154,7 +154,7 @@ class CpuPath:
         self.threads = os.cpu_count() or 1
         torch.set_num_threads(self.threads)
         self.kind, self._ref = "port", None
-        pyc = os.path.join(ROOT, "oracle", "_ref", "reference.pyc")
+        pyc = os.path.join(ROOT, "oracle", "_ref", "reference_checker.bin")
         if os.path.exists(pyc):
             try:
                 import importlib.machinery

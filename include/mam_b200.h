@@ -90,6 +90,24 @@ int mam_fwd_f32(const float* a, const float* b, int b_layout,
                 int64_t M, int64_t K, int64_t N,
                 void* workspace, size_t workspace_bytes, void* stream);
 
+/* mam_fwd_f32 with the module's output dropout (torch.nn.functional.dropout in training,
+ * mamtorch/nn/v4/fullyconnected.py:204-206) applied in the kernel epilogue, after the bias: element
+ * i = m*N + n of y is set to 0 with probability drop_rate and multiplied by 1 / (1 - drop_rate) otherwise
+ * (0 <= drop_rate < 1; 0 is mam_fwd_f32).  The decision for element i is a pure function of (drop_seed, i) --
+ * a counter-based generator -- so no mask is stored: mam_drop_f32 with the same seed and rate forms it again
+ * for the backward.  The random stream is this library's own, not torch's. */
+int mam_fwd_drop_f32(const float* a, const float* b, int b_layout,
+                     const float* bias, const float* dense, int blend, float alpha, float beta,
+                     float drop_rate, uint64_t drop_seed,
+                     float* y, int32_t* argmax, int32_t* argmin,
+                     int64_t M, int64_t K, int64_t N,
+                     void* workspace, size_t workspace_bytes, void* stream);
+/* out[i] = in[i] * scale where the generator above keeps element i under (seed, rate), else 0; i < n, in == out
+ * allowed.  Three uses: the backward of the epilogue dropout (scale = 1 / (1 - rate) on the upstream gradient),
+ * the module's weight drop (mamtorch/nn/v4/fullyconnected.py:143-148: scale = 1 on the weight, one pass in
+ * place of bernoulli + multiply and their two [N,K] temporaries) and its backward (scale = 1 on dW). */
+int mam_drop_f32(const float* in, float* out, int64_t n, float rate, float scale, uint64_t seed, void* stream);
+
 /* Values-only forward with K cut into consecutive slices of split_width columns (the last one may be
  * shorter): y[m,n] = sum over slices, in ascending order, of (max + min over the slice's products), then the
  * blend / bias epilogue of mam_fwd_f32.  One launch for what the reference module's `splits` option does with
@@ -138,9 +156,20 @@ int mam_bwd_f32(const float* a, const float* b, int b_layout, const float* grad,
                 float* da, float* db, float scale,
                 int64_t M, int64_t K, int64_t N, void* stream);
 
-/* The same backward with the selection hits of this pass accumulated on the way: hit_max[n,k] +=
- * #rows with argmax[m,n]==k, hit_min likewise ([N,K] int32, added into; pass both NULL for no
- * counting).  One sweep over grad / argmax / argmin serves dW and the counts. */
+/* The same backward with the selection hits of this pass delivered too: hit_max[n,k] += #rows with
+ * argmax[m,n]==k, hit_min likewise ([N,K] int32, added into; pass both NULL for no counting).  Without
+ * scratch memory (this entry point and mam_bwd_count_ex_f32) the hits come from a second sweep over the two
+ * index matrices after the gradient kernel, as mam_selcount_i32 does it.  mam_bwd_count_ws_f32 below makes it
+ * ONE sweep: given 16 bytes of 256-byte aligned scratch per weight, every dW term goes to L2 together with
+ * its hit as one 16-byte vector reduction {term, max hit, min hit, -} and a short pass splits the records into
+ * db and the hit matrices.  mam_bwd_count_workspace_bytes(M, K, N) returns the scratch size where that form is
+ * the faster one on B200 and 0 where it is not (the wider reduction costs more than the second sweep once the
+ * records outgrow L2, or where the gradient kernel's time is its L2 reductions already: K in 640..832) or is
+ * not available (M >= 2^24: the hits ride as fp32 sums of 1.0).  A caller that passes scratch of 16*K*N bytes
+ * although the query answered 0 for speed still gets the one-sweep form.  With workspace == NULL it is
+ * mam_bwd_count_ex_f32.  The device-side form of the bookkeeping in
+ * FullyConnected.update_selection_count (mamtorch/nn/v4/fullyconnected.py:114-131) riding on
+ * fullyconnected_backward_cuda (mamtorch/kernel/v4/csrc/cuda/fullyconnected_backward.cu:80-135). */
 int mam_bwd_count_f32(const float* a, const float* b, int b_layout, const float* grad,
                       const int32_t* argmax, const int32_t* argmin,
                       float* da, float* db, int32_t* hit_max, int32_t* hit_min, float scale,
@@ -154,6 +183,11 @@ int mam_bwd_count_ex_f32(const float* a, const float* b, int b_layout, const flo
                          const int32_t* argmax, const int32_t* argmin,
                          float* da, int da_layout, float* db, int32_t* hit_max, int32_t* hit_min, float scale,
                          int64_t M, int64_t K, int64_t N, void* stream);
+size_t mam_bwd_count_workspace_bytes(int64_t M, int64_t K, int64_t N);
+int mam_bwd_count_ws_f32(const float* a, const float* b, int b_layout, const float* grad,
+                         const int32_t* argmax, const int32_t* argmin,
+                         float* da, int da_layout, float* db, int32_t* hit_max, int32_t* hit_min, float scale,
+                         int64_t M, int64_t K, int64_t N, void* workspace, size_t workspace_bytes, void* stream);
 
 /* Patch rows of a convolution input: rows[m][k] = x[b][c][ho*sh-ph+kh][wo*sw-pw+kw] (0 outside the image),
  * m = (b*Ho+ho)*Wo+wo, k = (c*kH+kh)*kW+kw, Ho = (H+2*ph-kH)/sh+1, Wo likewise; x is [B,C,H,W], rows is

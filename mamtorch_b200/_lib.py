@@ -28,10 +28,14 @@ ABI = {
     "mam_timer_disarm": (_i32, []),
     "mam_fwd_workspace_bytes": (_sz, [_i64, _i64, _i64, _i32, _i32]),
     "mam_fwd_f32": (_i32, [_vp, _vp, _i32, _vp, _vp, _i32, _f32, _f32, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _sz, _vp]),
+    "mam_fwd_drop_f32": (_i32, [_vp, _vp, _i32, _vp, _vp, _i32, _f32, _f32, _f32, ctypes.c_uint64, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _sz, _vp]),
+    "mam_drop_f32": (_i32, [_vp, _vp, _i64, _f32, _f32, ctypes.c_uint64, _vp]),
     "mam_fwd_kn_static_f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "mam_bwd_f32": (_i32, [_vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _f32, _i64, _i64, _i64, _vp]),
     "mam_bwd_count_f32": (_i32, [_vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f32, _i64, _i64, _i64, _vp]),
     "mam_bwd_count_ex_f32": (_i32, [_vp, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _f32, _i64, _i64, _i64, _vp]),
+    "mam_bwd_count_workspace_bytes": (_sz, [_i64, _i64, _i64]),
+    "mam_bwd_count_ws_f32": (_i32, [_vp, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _f32, _i64, _i64, _i64, _vp, _sz, _vp]),
     "mam_conv_bwd_f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _f32, _i64, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _i64, _vp]),
     "mam_conv_bwd_direct_f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _f32, _i64, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _i64, _vp]),
     "mam_conv_bwd_direct_applies": (_i32, [_i64, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _i32, _i32]),

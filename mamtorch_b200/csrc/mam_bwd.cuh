@@ -16,13 +16,44 @@ namespace mamb200 {
 
 constexpr int BWD_THREADS = 256;
 
+// One dW term on its way to L2.  Plain form: an fp32 reduction into dw[wi].  FUSED form: `dw` is a scratch array
+// of 16-byte records {dW sum, max hits, min hits, unused} in the weight operand's layout, and the term travels
+// with the selection hit it stands for in ONE 16-byte vector reduction -- the same number of L2 operations as
+// the plain form, and no second sweep over the index matrices for the counts.  The counts are sums of 1.0f,
+// exact below 2^24 hits per weight and call; mam_bwd_unpack_kernel splits the records afterwards.
+template <bool FUSED, bool IS_MAX>
+__device__ __forceinline__ void dw_term(float* dw, long long wi, float term) {
+    if constexpr (FUSED) {
+        asm volatile("red.global.v4.f32.add [%0], {%1, %2, %3, %4};" ::"l"(dw + wi * 4), "f"(term),
+                     "f"(IS_MAX ? 1.f : 0.f), "f"(IS_MAX ? 0.f : 1.f), "f"(0.f)
+                     : "memory");
+    } else {
+        atomicAdd(&dw[wi], term);
+    }
+}
+
+// acc[i] = {dW sum, max hits, min hits, -} for element i of the weight operand's layout -> dw[i] and, added into
+// the caller's [N,K] matrices, the hits.
+template <bool B_NK>
+__global__ void __launch_bounds__(256)
+mam_bwd_unpack_kernel(const float4* __restrict__ acc, float* __restrict__ dw, int* __restrict__ hit_max,
+                      int* __restrict__ hit_min, long long K, long long N) {
+    const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+    if (i >= K * N) return;
+    const float4 v = acc[i];
+    dw[i] = v.x;
+    const long long j = B_NK ? i : (i % N) * K + i / N;
+    if (v.y != 0.f) hit_max[j] += (int)v.y;
+    if (v.z != 0.f) hit_min[j] += (int)v.z;
+}
+
 // B_NK: w is W[N,K] and dw has the same layout; otherwise b[K,N].
 // DA_KM: da is written transposed, da[k*M + m] (what the convolution's fold kernel wants: unit stride
 // along the output pixels); a CTA's rows are consecutive, so every k still gets one whole sector.
 // CONV: a is not a matrix of patch rows but the convolution input x[B,C,H,W] itself; row m is output
 // pixel (b, ho, wo) and a[m][k] is read where the patch element k = (c*kH+kh)*kW+kw lives in x (zero
 // in the padding), so the patch rows need not be kept for the backward.
-template <bool B_NK, bool DA_KM = false, bool CONV = false>
+template <bool B_NK, bool DA_KM = false, bool CONV = false, bool FUSED = false>
 __global__ void __launch_bounds__(BWD_THREADS)
 mam_bwd_kernel(const float* __restrict__ a, const float* __restrict__ w, const float* __restrict__ g,
                const int* __restrict__ argmax, const int* __restrict__ argmin,
@@ -68,12 +99,12 @@ mam_bwd_kernel(const float* __restrict__ a, const float* __restrict__ w, const f
             if (ok1) {
                 const long long wi = B_NK ? n * K + k1 : (long long)k1 * N + n;
                 atomicAdd(&dar[k1], __fmul_rn(w[wi], gv));
-                atomicAdd(&dw[wi], __fmul_rn(a_at(k1), gv));
+                dw_term<FUSED, true>(dw, wi, __fmul_rn(a_at(k1), gv));
             }
             if (ok2) {
                 const long long wi = B_NK ? n * K + k2 : (long long)k2 * N + n;
                 atomicAdd(&dar[k2], __fmul_rn(w[wi], gv));
-                atomicAdd(&dw[wi], __fmul_rn(a_at(k2), gv));
+                dw_term<FUSED, false>(dw, wi, __fmul_rn(a_at(k2), gv));
             }
         }
     }
@@ -123,7 +154,7 @@ __device__ __forceinline__ void warp_row_add(float* row, int k, bool ok, float v
     __syncwarp();
 }
 
-template <bool B_NK, bool A_SMEM>
+template <bool B_NK, bool A_SMEM, bool FUSED = false>
 __global__ void __launch_bounds__(BWD_THREADS)
 mam_bwd_rowwarp_kernel(const float* __restrict__ a, const float* __restrict__ w, const float* __restrict__ g,
                        const int* __restrict__ argmax, const int* __restrict__ argmin,
@@ -172,12 +203,12 @@ mam_bwd_rowwarp_kernel(const float* __restrict__ a, const float* __restrict__ w,
             if (ok1[u]) {
                 const long long wi = B_NK ? n * K + k1[u] : (long long)k1[u] * N + n;
                 t1[u] = __fmul_rn(w[wi], gv[u]);
-                atomicAdd(&dw[wi], __fmul_rn(A_SMEM ? as[k1[u]] : arow[k1[u]], gv[u]));
+                dw_term<FUSED, true>(dw, wi, __fmul_rn(A_SMEM ? as[k1[u]] : arow[k1[u]], gv[u]));
             }
             if (ok2[u]) {
                 const long long wi = B_NK ? n * K + k2[u] : (long long)k2[u] * N + n;
                 t2[u] = __fmul_rn(w[wi], gv[u]);
-                atomicAdd(&dw[wi], __fmul_rn(A_SMEM ? as[k2[u]] : arow[k2[u]], gv[u]));
+                dw_term<FUSED, false>(dw, wi, __fmul_rn(A_SMEM ? as[k2[u]] : arow[k2[u]], gv[u]));
             }
         }
 #pragma unroll

@@ -358,6 +358,9 @@ int g_dense_split = 1;  // 0: the TF32 product runs whole tiles only (cross-chec
 int g_conv_direct_rows = 0;  // 0 auto, else output rows per CTA of mam_conv_bwd_direct_kernel (if they fit)
 int g_bwd_mode = 0;  // 0 auto, 1 CTA-shared rows, 2 two kernels, 3 row per warp (a parked in shared memory where it fits), 4 row per warp (a read from L1)
 
+// K for which the automatic choice takes the row-per-warp gradient kernel (measured, see mam_bwd_count_ws_f32)
+bool bwd_rowwarp_band(int64_t K) { return g_bwd_mode == 0 && K >= 640 && K <= 832; }
+
 template <bool NK>
 int launch_bwd_split(const float* a, const float* b, const float* grad, const int32_t* argmax, const int32_t* argmin,
                      float* da, float* db, int32_t* hit_max, int32_t* hit_min, float scale, int64_t M, int64_t K,
@@ -528,9 +531,37 @@ int mam_nchw_to_nhwc_f32(const float* x, float* out, int64_t B, int64_t C, int64
     return MAM_OK;
 }
 
+namespace {
+// rate in [0, 1) -> threshold on a 32-bit draw; false if the rate is out of range
+bool drop_threshold(float rate, unsigned* thr) {
+    if (!(rate >= 0.f && rate < 1.f)) return false;
+    const double t = (double)rate * 4294967296.0;
+    *thr = t >= 4294967295.0 ? 4294967295u : (unsigned)t;
+    return true;
+}
+}  // namespace
+
 int mam_fwd_f32(const float* a, const float* b, int b_layout, const float* bias, const float* dense, int blend,
                 float alpha, float beta, float* y, int32_t* argmax, int32_t* argmin, int64_t M, int64_t K,
                 int64_t N, void* workspace, size_t workspace_bytes, void* stream) {
+    return mam_fwd_drop_f32(a, b, b_layout, bias, dense, blend, alpha, beta, 0.f, 0, y, argmax, argmin, M, K, N,
+                            workspace, workspace_bytes, stream);
+}
+
+int mam_drop_f32(const float* in, float* out, int64_t n, float rate, float scale, uint64_t seed, void* stream) {
+    unsigned thr = 0;
+    if (bad_ptr(in) || bad_ptr(out) || n <= 0 || !drop_threshold(rate, &thr)) return MAM_ERR_INVALID_ARGUMENT;
+    const long long blocks = (n + 255) / 256;
+    if (blocks > 2147483647LL) return MAM_ERR_UNSUPPORTED;
+    mam_drop_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(in, out, n, seed, thr, scale);
+    MAM_CUDA(cudaGetLastError());
+    return MAM_OK;
+}
+
+int mam_fwd_drop_f32(const float* a, const float* b, int b_layout, const float* bias, const float* dense, int blend,
+                     float alpha, float beta, float drop_rate, uint64_t drop_seed, float* y, int32_t* argmax,
+                     int32_t* argmin, int64_t M, int64_t K, int64_t N, void* workspace, size_t workspace_bytes,
+                     void* stream) {
     if (bad_ptr(a) || bad_ptr(b) || bad_ptr(y) || M <= 0 || K <= 0 || N <= 0) return MAM_ERR_INVALID_ARGUMENT;
     if (b_layout != MAM_B_KN && b_layout != MAM_B_NK) return MAM_ERR_INVALID_ARGUMENT;
     if ((argmax == nullptr) != (argmin == nullptr)) return MAM_ERR_INVALID_ARGUMENT;
@@ -541,6 +572,11 @@ int mam_fwd_f32(const float* a, const float* b, int b_layout, const float* bias,
     cudaStream_t cs = (cudaStream_t)stream;
     const bool want_idx = argmax != nullptr;
     EpilogueArgs ep{bias, dense, alpha, beta, blend};
+    if (drop_rate != 0.f) {
+        if (!drop_threshold(drop_rate, &ep.drop_threshold)) return MAM_ERR_INVALID_ARGUMENT;
+        ep.drop_seed = drop_seed;
+        ep.drop_scale = 1.0f / (1.0f - drop_rate);
+    }
 
     int variant = g_variant[want_idx ? 1 : 0];
     const bool tma_ok = (K % 4 == 0) && aligned16(a) && aligned16(b) && K / FWD_BK < 65535;
@@ -627,6 +663,27 @@ int mam_bwd_count_f32(const float* a, const float* b, int b_layout, const float*
 int mam_bwd_count_ex_f32(const float* a, const float* b, int b_layout, const float* grad, const int32_t* argmax,
                          const int32_t* argmin, float* da, int da_layout, float* db, int32_t* hit_max,
                          int32_t* hit_min, float scale, int64_t M, int64_t K, int64_t N, void* stream) {
+    return mam_bwd_count_ws_f32(a, b, b_layout, grad, argmax, argmin, da, da_layout, db, hit_max, hit_min, scale, M, K,
+                                N, nullptr, 0, stream);
+}
+
+size_t mam_bwd_count_workspace_bytes(int64_t M, int64_t K, int64_t N) {
+    // counts ride as sums of 1.0f: exact while no weight can be hit 2^24 times in one call
+    if (M <= 0 || K <= 0 || N <= 0 || M >= (1LL << 24)) return 0;
+    // Where the 16-byte records pay (B200, 12608 rows unless said otherwise; gradient kernel + hits, separate
+    // sweep vs riding along): with the CTA-shared gradient kernel and records that stay in L2, K x N = 3072 x 768:
+    // 0.304 -> 0.273 ms.  Not in the row-per-warp band, whose time IS its L2 reductions and where the wider
+    // reduction costs more than the second sweep saves (768 x 3072: 0.889 -> 0.960 ms), and not once the records
+    // outgrow L2 (4096 rows, 4096 x 4096, 268 MB of records: 0.644 -> 0.725 ms).  The query answers 0 there and
+    // callers run the second sweep.
+    if (bwd_rowwarp_band(K) || (double)K * (double)N * 16.0 > 64.0 * 1024 * 1024) return 0;
+    return round256((size_t)K * (size_t)N * 16);
+}
+
+int mam_bwd_count_ws_f32(const float* a, const float* b, int b_layout, const float* grad, const int32_t* argmax,
+                         const int32_t* argmin, float* da, int da_layout, float* db, int32_t* hit_max,
+                         int32_t* hit_min, float scale, int64_t M, int64_t K, int64_t N, void* workspace,
+                         size_t workspace_bytes, void* stream) {
     if (da_layout != MAM_DA_MK && da_layout != MAM_DA_KM) return MAM_ERR_INVALID_ARGUMENT;
     if (bad_ptr(a) || bad_ptr(b) || bad_ptr(grad) || bad_ptr(argmax) || bad_ptr(argmin) || bad_ptr(da) ||
         bad_ptr(db) || M <= 0 || K <= 0 || N <= 0)
@@ -645,6 +702,27 @@ int mam_bwd_count_ex_f32(const float* a, const float* b, int b_layout, const flo
     // (16 = one 64-byte run) when their accumulators still leave room for several CTAs per SM
     if (da_layout == MAM_DA_KM && 16 * K * 4 <= 48 * 1024) rows = 16;
     const bool count = hit_max != nullptr;
+    // the hits travel with the dW terms when the caller brought the scratch for the 16-byte records
+    // (a caller that brings the scratch gets the records whatever the query's advice, except beyond 2^24 rows)
+    const size_t fused_need = M < (1LL << 24) ? round256((size_t)K * (size_t)N * 16) : 0;
+    const bool fused = count && workspace != nullptr && fused_need != 0 && g_bwd_mode != 2;
+    if (fused && (workspace_bytes < fused_need || (reinterpret_cast<uintptr_t>(workspace) & 255u)))
+        return MAM_ERR_WORKSPACE;
+    float* dw_dst = fused ? static_cast<float*>(workspace) : db;
+    const size_t dw_fill = fused ? (size_t)K * (size_t)N * 16 : (size_t)K * (size_t)N * 4;
+    auto unpack = [&]() -> int {
+        const long long blocks = (K * N + 255) / 256;
+        if (blocks > 2147483647LL) return MAM_ERR_UNSUPPORTED;
+        TimedLaunch t(MAM_KERNEL_SELCOUNT, cs);
+        if (b_layout == MAM_B_NK)
+            mam_bwd_unpack_kernel<true><<<(unsigned)blocks, 256, 0, cs>>>(static_cast<const float4*>(workspace), db,
+                                                                          hit_max, hit_min, K, N);
+        else
+            mam_bwd_unpack_kernel<false><<<(unsigned)blocks, 256, 0, cs>>>(static_cast<const float4*>(workspace), db,
+                                                                           hit_max, hit_min, K, N);
+        MAM_CUDA(cudaGetLastError());
+        return MAM_OK;
+    };
     // columns owned per CTA in the two-kernel form: at most 8, shared memory permitting, and enough
     // CTAs to cover the SMs twice
     const long long per_col = K * 4 * (count ? 3 : 1);
@@ -671,45 +749,55 @@ int mam_bwd_count_ex_f32(const float* a, const float* b, int b_layout, const flo
     // measures), 1024 x 4096 1.12 vs 1.22; but 512 x 2048 0.62 vs 0.58 (per row the zero / stage / write-out of K
     // floats weighs more), 896 x 3584 1.10 vs 1.03, 1280 x 5120 1.95 vs 1.30, 3072 x 768 0.42 vs 0.23 (a warp's rows
     // leave room for too few warps per SM).  The automatic choice takes this form only in the band where it won.
-    const bool rw_auto = g_bwd_mode == 0 && K >= 640 && K <= 832;
+    const bool rw_auto = bwd_rowwarp_band(K);
     if (rw_fits && (rw_auto || g_bwd_mode == 3 || g_bwd_mode == 4)) {
         const bool a_smem = g_bwd_mode != 4 && 2 * RW_ROWS * rw_row <= ((size_t)d->max_smem - 2048) / 2;
         const size_t smem_rw = RW_ROWS * rw_row * (a_smem ? 2 : 1);
         const long long grid_rw = (M + RW_ROWS - 1) / RW_ROWS;
         if (grid_rw > 2147483647LL) return MAM_ERR_UNSUPPORTED;
-        MAM_CUDA(cudaMemsetAsync(db, 0, (size_t)K * (size_t)N * 4, cs));
+        MAM_CUDA(cudaMemsetAsync(dw_dst, 0, dw_fill, cs));
         auto launch = [&](auto kern) -> int {
             MAM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_rw));
             TimedLaunch t(MAM_KERNEL_BWD, cs);
-            kern<<<(unsigned)grid_rw, BWD_THREADS, smem_rw, cs>>>(a, b, grad, argmax, argmin, da, db, M, K, N, scale);
+            kern<<<(unsigned)grid_rw, BWD_THREADS, smem_rw, cs>>>(a, b, grad, argmax, argmin, da, dw_dst, M, K, N, scale);
             return MAM_OK;
         };
         const bool nk = b_layout == MAM_B_NK;
-        st = nk ? (a_smem ? launch(mam_bwd_rowwarp_kernel<true, true>) : launch(mam_bwd_rowwarp_kernel<true, false>))
-                : (a_smem ? launch(mam_bwd_rowwarp_kernel<false, true>) : launch(mam_bwd_rowwarp_kernel<false, false>));
+        if (fused)
+            st = nk ? (a_smem ? launch(mam_bwd_rowwarp_kernel<true, true, true>) : launch(mam_bwd_rowwarp_kernel<true, false, true>))
+                    : (a_smem ? launch(mam_bwd_rowwarp_kernel<false, true, true>) : launch(mam_bwd_rowwarp_kernel<false, false, true>));
+        else
+            st = nk ? (a_smem ? launch(mam_bwd_rowwarp_kernel<true, true>) : launch(mam_bwd_rowwarp_kernel<true, false>))
+                    : (a_smem ? launch(mam_bwd_rowwarp_kernel<false, true>) : launch(mam_bwd_rowwarp_kernel<false, false>));
         if (st != MAM_OK) return st;
         MAM_CUDA(cudaGetLastError());
+        if (fused) return unpack();
         if (count) return mam_selcount_i32(argmax, argmin, hit_max, hit_min, M, K, N, stream);
         return MAM_OK;
     }
     const size_t smem = (size_t)rows * (size_t)K * 4;
     const long long grid = (M + rows - 1) / rows;
     if (grid > 2147483647LL) return MAM_ERR_UNSUPPORTED;
-    MAM_CUDA(cudaMemsetAsync(db, 0, (size_t)K * (size_t)N * 4, cs));
+    MAM_CUDA(cudaMemsetAsync(dw_dst, 0, dw_fill, cs));
     {
         auto launch = [&](auto kern) -> int {
             MAM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             TimedLaunch t(MAM_KERNEL_BWD, cs);
-            kern<<<(unsigned)grid, BWD_THREADS, smem, cs>>>(a, b, grad, argmax, argmin, da, db, M, K, N, rows, scale,
+            kern<<<(unsigned)grid, BWD_THREADS, smem, cs>>>(a, b, grad, argmax, argmin, da, dw_dst, M, K, N, rows, scale,
                                                             ConvGeom{});
             return MAM_OK;
         };
         const bool nk = b_layout == MAM_B_NK, km = da_layout == MAM_DA_KM;
-        st = nk ? (km ? launch(mam_bwd_kernel<true, true>) : launch(mam_bwd_kernel<true, false>))
-                : (km ? launch(mam_bwd_kernel<false, true>) : launch(mam_bwd_kernel<false, false>));
+        if (fused)
+            st = nk ? (km ? launch(mam_bwd_kernel<true, true, false, true>) : launch(mam_bwd_kernel<true, false, false, true>))
+                    : (km ? launch(mam_bwd_kernel<false, true, false, true>) : launch(mam_bwd_kernel<false, false, false, true>));
+        else
+            st = nk ? (km ? launch(mam_bwd_kernel<true, true>) : launch(mam_bwd_kernel<true, false>))
+                    : (km ? launch(mam_bwd_kernel<false, true>) : launch(mam_bwd_kernel<false, false>));
         if (st != MAM_OK) return st;
     }
     MAM_CUDA(cudaGetLastError());
+    if (fused) return unpack();
     if (count) return mam_selcount_i32(argmax, argmin, hit_max, hit_min, M, K, N, stream);
     return MAM_OK;
 }

@@ -19,7 +19,31 @@ struct EpilogueArgs {
     float alpha;         // scale of (max+min); used only when blend != 0
     float beta;          // scale of dense
     int blend;           // 0: y = (max+min) [+ bias]
+    // output dropout, applied last: element i = m*N+n is kept (and scaled) where mam_drop_keeps(seed, i, threshold)
+    unsigned long long drop_seed;
+    unsigned drop_threshold;   // rate * 2^32
+    float drop_scale;          // 1 / (1 - rate); 0 = no dropout
 };
+
+// The keep / drop decision of element `idx` under `seed`: a counter-based generator (the splitmix64 mixing
+// function on seed + idx * golden ratio), so that the same mask is formed again wherever it is needed --
+// forward epilogue, backward, weight drop -- without ever being stored.  Dropped with probability
+// threshold / 2^32.
+__device__ __forceinline__ bool mam_drop_keeps(unsigned long long seed, unsigned long long idx, unsigned threshold) {
+    unsigned long long z = seed + idx * 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    z ^= z >> 31;
+    return (unsigned)(z >> 32) >= threshold;
+}
+
+// out[i] = in[i] * scale where element i is kept, else 0 (in == out is fine)
+__global__ void __launch_bounds__(256)
+mam_drop_kernel(const float* __restrict__ in, float* __restrict__ out, long long n, unsigned long long seed,
+                unsigned threshold, float scale) {
+    const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+    if (i < n) out[i] = mam_drop_keeps(seed, (unsigned long long)i, threshold) ? __fmul_rn(in[i], scale) : 0.f;
+}
 
 // y = alpha*(vmax+vmin) + beta*dense + bias, every step individually rounded (no contraction),
 // in the order of the reference's host glue (mamtorch/kernel/v3/csrc/cuda/fullyconnected.cu:153-160).
@@ -30,17 +54,14 @@ __device__ __forceinline__ float mam_epilogue_term(float s, const EpilogueArgs& 
         if (e.dense) s = __fadd_rn(s, __fmul_rn(e.dense[m * N + n], e.beta));
     }
     if (e.bias) s = __fadd_rn(s, e.bias[n]);
+    if (e.drop_scale != 0.f)
+        s = mam_drop_keeps(e.drop_seed, (unsigned long long)(m * N + n), e.drop_threshold) ? __fmul_rn(s, e.drop_scale)
+                                                                                           : 0.f;
     return s;
 }
 __device__ __forceinline__ float mam_epilogue(float vmax, float vmin, const EpilogueArgs& e,
                                               long long m, long long n, long long N) {
-    float s = __fadd_rn(vmax, vmin);
-    if (e.blend) {
-        s = __fmul_rn(s, e.alpha);
-        if (e.dense) s = __fadd_rn(s, __fmul_rn(e.dense[m * N + n], e.beta));
-    }
-    if (e.bias) s = __fadd_rn(s, e.bias[n]);
-    return s;
+    return mam_epilogue_term(__fadd_rn(vmax, vmin), e, m, n, N);
 }
 
 constexpr int GEN_TILE = 64;

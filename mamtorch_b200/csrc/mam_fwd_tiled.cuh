@@ -98,8 +98,8 @@ struct Im2colCursor {
 
 struct FwdParams {
     float* y;
-    int* cid_max;  // TRACK: chunk ids (later resolved in place to exact k)
-    int* cid_min;
+    int* cid_max;  // TRACK: receives (max chunk id) | (min chunk id) << 16; the resolver turns it into the exact
+    int* cid_min;  //        argmax in place and writes the argmin here
     long long M, K, N;
     EpilogueArgs ep;
     float one;     // 1.0f kept opaque to the compiler (see merge below)
@@ -117,9 +117,6 @@ __device__ __forceinline__ void static_for(F&& f) {
     }
 }
 
-__device__ __forceinline__ ulonglong2 lds128(const unsigned char* p) {
-    return *reinterpret_cast<const ulonglong2*>(p);
-}
 // LDS.128 from a 32-bit shared-window address plus a compile-time byte offset.  Going through a
 // generic pointer instead costs two integer adds per load on the ALU pipe -- the pipe the max/min
 // instructions saturate.
@@ -128,6 +125,36 @@ __device__ __forceinline__ ulonglong2 lds128_at(uint32_t addr) {
     ulonglong2 v;
     asm volatile("ld.shared.v2.u64 {%0, %1}, [%2+%3];" : "=l"(v.x), "=l"(v.y) : "r"(addr), "n"(OFF));
     return v;
+}
+
+// Shared-memory accesses of the resolver by 32-bit shared-window address.  The kernels carve their dynamic
+// shared memory up through integer arithmetic (1024-byte alignment), after which the compiler no longer
+// knows that the pointers are shared memory and would emit generic loads, stores and atomics.
+__device__ __forceinline__ ulonglong2 lds128_s(uint32_t addr) {
+    ulonglong2 v;
+    asm volatile("ld.shared.v2.u64 {%0, %1}, [%2];" : "=l"(v.x), "=l"(v.y) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ int lds32_s(uint32_t addr) {
+    int v;
+    asm volatile("ld.shared.s32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ unsigned lds16_s(uint32_t addr) {
+    unsigned short v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void sts32_s(uint32_t addr, int v) {
+    asm volatile("st.shared.s32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ void sts16_s(uint32_t addr, unsigned v) {
+    asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"((unsigned short)v) : "memory");
+}
+__device__ __forceinline__ int atoms_add_s(uint32_t addr, int v) {
+    int old;
+    asm volatile("atom.shared.add.s32 %0, [%1], %2;" : "=r"(old) : "r"(addr), "r"(v) : "memory");
+    return old;
 }
 
 // CONV: the a-operand is fetched by im2col-mode TMA (tmA is an im2col map, prm.conv describes the geometry).
@@ -378,8 +405,8 @@ mam_fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                     const uint32_t amin = id_addr + (uint32_t)(((i * TN + j) * 2 + 1) * Cfg::CONSUMERS * 2);
                     asm volatile("ld.shared.u16 %0, [%1];" : "=h"(cmax) : "r"(amax) : "memory");
                     asm volatile("ld.shared.u16 %0, [%1];" : "=h"(cmin) : "r"(amin) : "memory");
-                    prm.cid_max[m * N + n] = (int)cmax;
-                    prm.cid_min[m * N + n] = (int)cmin;
+                    // both chunk ids in one word (K / 32 < 65535): the resolver reads half as much
+                    prm.cid_max[m * N + n] = (int)((unsigned)cmax | ((unsigned)cmin << 16));
                 }
             }
         }
@@ -393,7 +420,7 @@ mam_fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
 // chunk of one a-row against one W-row.  A CTA owns an RM x RN tile of outputs.  It counting-sorts
 // the tile's 2*RM*RN tasks by chunk in shared memory (integer shared-memory atomics), then
 // streams the tile's operand chunks through a TMA ring like the main kernel's, and for chunk c
-// its threads split the tasks of bucket c between them.
+// its threads split the tasks of bucket c between them, each taking a run of consecutive tasks.
 //
 // Shared-memory bandwidth is the floor here (every task reads its own 2 x 128 bytes), so the
 // stage is NOT swizzled: lane L reads the eight 16-byte groups of its rows in the rotated order
@@ -407,11 +434,17 @@ struct ResolveCfg {
     static constexpr int A_BYTES = RM * FWD_BK * 4, W_BYTES = RN * FWD_BK * 4;
     static constexpr int STAGE_BYTES = A_BYTES + W_BYTES;
     static constexpr int TASKS = 2 * RM * RN;
-    // bucket counters are sized by the number of chunks, so that three stages still leave room for two CTAs
-    // per SM at ordinary K (105 KB at K <= 4096; 121 KB and one CTA per SM at the 65536 limit)
+    // Bucket counters: `segments` per chunk (see pass A of the kernel), as many as keep the two counter arrays
+    // under ~8 KB, so that three stages still leave room for two CTAs per SM at ordinary K (at most 113 KB up to
+    // K = 32000; 121 KB and one CTA per SM at the 65536 limit).
     __host__ __device__ static constexpr int nk_pad(int nk) { return (nk + 3) & ~3; }
+    __host__ __device__ static constexpr int segments(int nk) {
+        int s = WARPS;
+        while (s > 1 && s * nk > 1000) s >>= 1;
+        return s;
+    }
     static constexpr int smem_bytes(int nk) {
-        return 1024 + STAGES * STAGE_BYTES + 2 * STAGES * 8 + 64 + TASKS * 2 + (2 * nk_pad(nk) + 8) * 4;
+        return 1024 + STAGES * STAGE_BYTES + 2 * STAGES * 8 + 64 + TASKS * 2 + (2 * nk_pad(nk * segments(nk)) + 8) * 4;
     }
     static constexpr int LOOKAHEAD = STAGES - 1;
 };
@@ -428,9 +461,11 @@ mam_resolve_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
     uint64_t* empty_bar = full_bar + C::STAGES;
     unsigned short* tasks = reinterpret_cast<unsigned short*>(smem + C::STAGES * C::STAGE_BYTES + 2 * C::STAGES * 8 + 64);
-    int* cursor = reinterpret_cast<int*>(tasks + C::TASKS);  // [nk]   running insert position
     const int nk_for_layout = (int)((K + FWD_BK - 1) / FWD_BK);
-    int* start = cursor + C::nk_pad(nk_for_layout) + 4;       // [nk+1] bucket boundaries
+    const int segs = C::segments(nk_for_layout);              // counters per chunk
+    const int entries = nk_for_layout * segs;
+    int* cursor = reinterpret_cast<int*>(tasks + C::TASKS);  // [entries]   tasks per (chunk, segment)
+    int* start = cursor + C::nk_pad(entries) + 4;             // [entries+1] where each (chunk, segment) begins
     __shared__ int warp_sums[C::WARPS];
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -446,7 +481,8 @@ mam_resolve_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         }
         mbar_fence_init();
     }
-    for (int i = tid; i < nk; i += C::THREADS) cursor[i] = 0;
+    const uint32_t cursor_s = smem_u32(cursor), start_s = smem_u32(start), tasks_s = smem_u32(tasks);
+    for (int i = tid; i < entries; i += C::THREADS) sts32_s(cursor_s + 4u * i, 0);
     __syncthreads();
 
     // producer state (thread 0)
@@ -475,36 +511,52 @@ mam_resolve_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         for (int i = 0; i < C::LOOKAHEAD; ++i) produce_one();
     }
 
-    // ---- pass A: read this thread's chunk ids once (all loads in flight together), count per chunk
-    constexpr int PER_THREAD = C::RM * C::RN / C::THREADS;
-    unsigned ids[PER_THREAD];  // (max chunk) | (min chunk) << 16; 0xffffffff = outside the matrix
+    // ---- pass A: read this thread's chunk ids once (all loads in flight together) and take a place in the
+    // bucket of each: the value an integer shared-memory atomic returns IS the task's rank, so the sort needs
+    // one round of atomics, not a counting round and a placing round.  Every warp owns RM / WARPS consecutive
+    // a-rows and walks them in order; counters are kept per (chunk, segment), a segment being the rows of one
+    // warp (of two or more warps where K has too many chunks for 8 counters each), and a warp's atomics on one
+    // address take effect in program order.  A bucket is therefore laid out segment by segment and, inside a
+    // segment, a-row by a-row: tasks that are neighbours in a bucket mostly share their a-row, which pass C
+    // turns into register reuse.  No barrier is needed until all ranks are taken.
+    constexpr int ROWS_PER_WARP = C::RM / C::WARPS;          // 8
+    constexpr int COLS_PER_LANE = C::RN / 32;                // 4
+    constexpr int IDS = ROWS_PER_WARP * COLS_PER_LANE;       // (max, min) pairs per thread
+    const int seg = (warp * segs) / C::WARPS;
+    unsigned ids[IDS];   // (max chunk) | (min chunk) << 16; 0xffffffff = outside the matrix
 #pragma unroll
-    for (int i = 0; i < PER_THREAD; ++i) {
-        const int o = i * C::THREADS + tid;
-        const long long m = m0 + o / C::RN, n = n0 + o % C::RN;
-        ids[i] = 0xffffffffu;
-        if (m < M && n < N) {
-            const int c1 = min(max(argmax[m * N + n], 0), nk - 1);
-            const int c2 = min(max(argmin[m * N + n], 0), nk - 1);
-            ids[i] = (unsigned)c1 | ((unsigned)c2 << 16);
+    for (int r = 0; r < ROWS_PER_WARP; ++r)
+#pragma unroll
+        for (int q = 0; q < COLS_PER_LANE; ++q) {
+            const long long m = m0 + warp * ROWS_PER_WARP + r, n = n0 + q * 32 + lane;
+            unsigned v = 0xffffffffu;
+            if (m < M && n < N) {
+                const unsigned packed = (unsigned)argmax[m * N + n];   // as the main kernel left it
+                const int c1 = min((int)(packed & 0xffffu), nk - 1);
+                const int c2 = min((int)(packed >> 16), nk - 1);
+                v = (unsigned)c1 | ((unsigned)c2 << 16);
+            }
+            ids[r * COLS_PER_LANE + q] = v;
         }
-    }
+    unsigned rk[IDS];    // (rank of the max task) | (rank of the min task) << 16; ranks < 2*RM*RN = 16384
 #pragma unroll
-    for (int i = 0; i < PER_THREAD; ++i) {
+    for (int i = 0; i < IDS; ++i) {
+        rk[i] = 0u;
         if (ids[i] != 0xffffffffu) {
-            atomicAdd(&cursor[ids[i] & 0xffffu], 1);
-            atomicAdd(&cursor[ids[i] >> 16], 1);
+            const unsigned r1 = (unsigned)atoms_add_s(cursor_s + 4u * ((ids[i] & 0xffffu) * segs + seg), 1);
+            const unsigned r2 = (unsigned)atoms_add_s(cursor_s + 4u * ((ids[i] >> 16) * segs + seg), 1);
+            rk[i] = r1 | (r2 << 16);
         }
     }
     __syncthreads();
-    // ---- exclusive scan of the nk counts (nk <= NK_MAX = 8 * THREADS)
+    // ---- exclusive scan of the nk * segs counts, chunk-major (at most NK_MAX = 8 * THREADS of them)
     {
         constexpr int PER = C::NK_MAX / C::THREADS;
         int v[PER], sum = 0;
 #pragma unroll
         for (int i = 0; i < PER; ++i) {
             const int idx = tid * PER + i;
-            v[i] = idx < nk ? cursor[idx] : 0;
+            v[i] = idx < entries ? lds32_s(cursor_s + 4u * idx) : 0;
             sum += v[i];
         }
         int incl = sum;
@@ -521,27 +573,32 @@ mam_resolve_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
 #pragma unroll
         for (int i = 0; i < PER; ++i) {
             const int idx = tid * PER + i;
-            if (idx < nk) {
-                start[idx] = run;
-                cursor[idx] = run;
-            }
+            if (idx < entries) sts32_s(start_s + 4u * idx, run);
             run += v[i];
         }
-        if (tid == C::THREADS - 1) start[nk] = run;
+        if (tid == C::THREADS - 1) sts32_s(start_s + 4u * entries, run);
     }
     __syncthreads();
-    // ---- pass B: scatter task codes into chunk order
+    // ---- pass B: every task code goes to (start of its bucket segment) + (its rank); plain stores.
+    // code = (row * RN + column) << 1 | (1 for a min task)
 #pragma unroll
-    for (int i = 0; i < PER_THREAD; ++i) {
-        const int o = i * C::THREADS + tid;
-        if (ids[i] != 0xffffffffu) {
-            tasks[atomicAdd(&cursor[ids[i] & 0xffffu], 1)] = (unsigned short)(o << 1);
-            tasks[atomicAdd(&cursor[ids[i] >> 16], 1)] = (unsigned short)((o << 1) | 1);
+    for (int r = 0; r < ROWS_PER_WARP; ++r)
+#pragma unroll
+        for (int q = 0; q < COLS_PER_LANE; ++q) {
+            const int i = r * COLS_PER_LANE + q;
+            const unsigned o = (unsigned)((warp * ROWS_PER_WARP + r) * C::RN + q * 32 + lane);
+            if (ids[i] != 0xffffffffu) {
+                const int p1 = lds32_s(start_s + 4u * ((ids[i] & 0xffffu) * segs + seg)) + (int)(rk[i] & 0xffffu);
+                const int p2 = lds32_s(start_s + 4u * ((ids[i] >> 16) * segs + seg)) + (int)(rk[i] >> 16);
+                sts16_s(tasks_s + 2u * p1, o << 1);
+                sts16_s(tasks_s + 2u * p2, (o << 1) | 1u);
+            }
         }
-    }
     __syncthreads();
 
-    // ---- pass C: stream the chunks, resolve the tasks of each
+    // ---- pass C: stream the chunks, resolve the tasks of each.  A thread takes a run of consecutive tasks
+    // of the bucket; consecutive tasks mostly share their a-row (see pass A), whose chunk then stays in
+    // registers and only the W-row is read again.
     int stage = 0;
     uint32_t phase = 0;
     [[maybe_unused]] int r_cc = 0, r_kh = 0, r_kw = 0;   // convolution: channel block and tap of the chunk being resolved
@@ -551,10 +608,9 @@ mam_resolve_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
             atomicExch(error, 1);
             return;
         }
-        const unsigned char* As = smem + stage * C::STAGE_BYTES;
-        const unsigned char* Ws = As + C::A_BYTES;
+        const uint32_t As = smem_u32(smem) + (uint32_t)(stage * C::STAGE_BYTES);
+        const uint32_t Ws = As + (uint32_t)C::A_BYTES;
         const int nq = (kc + 1 < nk) ? FWD_BK / 4 : tail_quads;
-        const int t_end = start[kc + 1];
         // Convolution rows: the chunk is 32 channels of one tap; indices leave in the numbering
         // k = (c*kH + kh)*kW + kw of weight.view(F, -1), i.e. kout = kout0 + e * kH*kW for element e.
         int kout0 = kc * FWD_BK, kout_step = 1;
@@ -566,24 +622,34 @@ mam_resolve_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                 if (++r_kh == conv.kH) { r_kh = 0; ++r_kw; }
             }
         }
-        for (int t = start[kc] + tid; t < t_end; t += C::THREADS) {
-            const unsigned code = tasks[t];
+        const int b0 = lds32_s(start_s + 4u * (kc * segs)), b1 = lds32_s(start_s + 4u * ((kc + 1) * segs));
+        const int per = (b1 - b0 + C::THREADS - 1) / C::THREADS;   // tasks per thread in this chunk
+        const int t_first = b0 + tid * per;
+        const int t_last = min(t_first + per, b1);
+        // the a-row's chunk, rotated: register r holds true 16-byte group (r + lane) & 7
+        ulonglong2 areg[FWD_BK / 4];
+        int cached_ra = -1;
+        for (int t = t_first; t < t_last; ++t) {
+            const unsigned code = lds16_s(tasks_s + 2u * t);
             const int o = (int)(code >> 1);
             const int ra = o / C::RN, rw = o % C::RN;
             const float sgn = (code & 1u) ? -1.0f : 1.0f;
             const f32x2_t sgn2 = pack2(sgn, sgn);
-            const unsigned char* ap = As + ra * 128;
-            const unsigned char* wp = Ws + rw * 128;
-            // rotated pass over the eight groups: register r holds true group (r + lane) & 7
+            const uint32_t ap = As + (uint32_t)ra * 128u;
+            const uint32_t wp = Ws + (uint32_t)rw * 128u;
+            if (ra != cached_ra) {
+                cached_ra = ra;
+#pragma unroll
+                for (int r = 0; r < FWD_BK / 4; ++r) areg[r] = lds128_s(ap + ((uint32_t)((r + lane) & 7) << 4));
+            }
             float qm[FWD_BK / 4];
 #pragma unroll
             for (int r = 0; r < FWD_BK / 4; ++r) {
-                const uint32_t off = (uint32_t)((r + lane) & 7) << 4;
-                const ulonglong2 av = lds128(ap + off);
-                const ulonglong2 wv = lds128(wp + off);
+                const ulonglong2 wv = lds128_s(wp + ((uint32_t)((r + lane) & 7) << 4));
                 float p0, p1, p2, p3;
-                unpack2(mul2(mul2(av.x, sgn2), wv.x), p0, p1);
-                unpack2(mul2(mul2(av.y, sgn2), wv.y), p2, p3);
+                // a min task looks for the maximum of the negated products (the sign flip is exact)
+                unpack2(mul2(mul2(areg[r].x, sgn2), wv.x), p0, p1);
+                unpack2(mul2(mul2(areg[r].y, sgn2), wv.y), p2, p3);
                 qm[r] = fmaxf(fmax3(p0, p1, p2), p3);
             }
             // groups at or beyond nq (ragged last chunk) hold zero fill: exclude them
@@ -602,8 +668,8 @@ mam_resolve_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
             }
             bq = min(bq, nq - 1);  // only reachable when every product is NaN
             // first element of group bq equal to the extreme
-            const ulonglong2 av = lds128(ap + ((uint32_t)bq << 4));
-            const ulonglong2 wv = lds128(wp + ((uint32_t)bq << 4));
+            const ulonglong2 av = lds128_s(ap + ((uint32_t)bq << 4));
+            const ulonglong2 wv = lds128_s(wp + ((uint32_t)bq << 4));
             float p0, p1, p2, p3;
             unpack2(mul2(mul2(av.x, sgn2), wv.x), p0, p1);
             unpack2(mul2(mul2(av.y, sgn2), wv.y), p2, p3);
@@ -634,8 +700,9 @@ mam_resolve_kernel(const float* __restrict__ a, const float* __restrict__ w,
     const int nk = (int)((K + FWD_BK - 1) / FWD_BK);
     const float* ar = a + m * K;
     const float* wr = w + n * K;
+    const unsigned packed = (unsigned)argmax[idx];   // (max chunk id) | (min chunk id) << 16
     {
-        int c = min(max(argmax[idx], 0), nk - 1);
+        int c = min((int)(packed & 0xffffu), nk - 1);
         const int k0 = c * FWD_BK, k1 = (int)min((long long)k0 + FWD_BK, K);
         float best = -INFINITY;
         int bk = k0;
@@ -646,7 +713,7 @@ mam_resolve_kernel(const float* __restrict__ a, const float* __restrict__ w,
         argmax[idx] = bk;
     }
     {
-        int c = min(max(argmin[idx], 0), nk - 1);
+        int c = min((int)(packed >> 16), nk - 1);
         const int k0 = c * FWD_BK, k1 = (int)min((long long)k0 + FWD_BK, K);
         float best = INFINITY;
         int bk = k0;

@@ -45,7 +45,8 @@ struct Fwd {
 
 // b_layout: MAM_B_KN -> w is b[K,N]; MAM_B_NK -> w is W[N,K]
 Fwd forward_impl(const at::Tensor& a, const at::Tensor& w, int b_layout, const c10::optional<at::Tensor>& bias,
-                 const c10::optional<at::Tensor>& dense, bool blend, double alpha, double beta, bool want_idx) {
+                 const c10::optional<at::Tensor>& dense, bool blend, double alpha, double beta, bool want_idx,
+                 double drop_rate = 0.0, int64_t drop_seed = 0) {
     check_matrix(a, "a");
     check_matrix(w, "b");
     const int64_t M = a.size(0), K = a.size(1);
@@ -84,12 +85,13 @@ Fwd forward_impl(const at::Tensor& a, const at::Tensor& w, int b_layout, const c
         ws_p = ws.data_ptr();
     }
     auto stream = at::cuda::getCurrentCUDAStream();
-    const int st = mam_fwd_f32(a.data_ptr<float>(), w.data_ptr<float>(), b_layout, bias_p, dense_p, blend ? 1 : 0,
-                               (float)alpha, (float)beta, out.y.data_ptr<float>(),
-                               want_idx ? out.argmax.data_ptr<int32_t>() : nullptr,
-                               want_idx ? out.argmin.data_ptr<int32_t>() : nullptr, M, K, N, ws_p, ws_bytes,
-                               stream.stream());
-    check_status(st, "mam_fwd_f32");
+    TORCH_CHECK(drop_rate >= 0.0 && drop_rate < 1.0, "drop_rate must be in [0, 1)");
+    const int st = mam_fwd_drop_f32(a.data_ptr<float>(), w.data_ptr<float>(), b_layout, bias_p, dense_p, blend ? 1 : 0,
+                                    (float)alpha, (float)beta, (float)drop_rate, (uint64_t)drop_seed,
+                                    out.y.data_ptr<float>(), want_idx ? out.argmax.data_ptr<int32_t>() : nullptr,
+                                    want_idx ? out.argmin.data_ptr<int32_t>() : nullptr, M, K, N, ws_p, ws_bytes,
+                                    stream.stream());
+    check_status(st, "mam_fwd_drop_f32");
     return out;
 }
 
@@ -119,13 +121,18 @@ std::vector<at::Tensor> backward_impl(const at::Tensor& a, const at::Tensor& w, 
         dw.zero_();
     } else {
         auto stream = at::cuda::getCurrentCUDAStream();
-        const int st = mam_bwd_count_ex_f32(a.data_ptr<float>(), w.data_ptr<float>(), b_layout, grad.data_ptr<float>(),
+        // with counting: scratch for the 16-byte {dW, max hits, min hits} records, so that the hits ride on the
+        // dW reductions instead of costing a second sweep over the indices
+        const size_t ws_bytes = count ? mam_bwd_count_workspace_bytes(M, K, N) : 0;
+        at::Tensor ws;
+        if (ws_bytes) ws = at::empty({(int64_t)ws_bytes}, a.options().dtype(at::kByte));
+        const int st = mam_bwd_count_ws_f32(a.data_ptr<float>(), w.data_ptr<float>(), b_layout, grad.data_ptr<float>(),
                                             argmax.data_ptr<int32_t>(), argmin.data_ptr<int32_t>(), da.data_ptr<float>(),
                                             da_km ? MAM_DA_KM : MAM_DA_MK, dw.data_ptr<float>(),
                                             count ? hmax.data_ptr<int32_t>() : nullptr,
                                             count ? hmin.data_ptr<int32_t>() : nullptr, (float)scale, M, K, N,
-                                            stream.stream());
-        check_status(st, "mam_bwd_count_ex_f32");
+                                            ws_bytes ? ws.data_ptr() : nullptr, ws_bytes, stream.stream());
+        check_status(st, "mam_bwd_count_ws_f32");
     }
     if (count) return {da, dw, hmax, hmin};
     return {da, dw};
@@ -253,6 +260,32 @@ std::vector<at::Tensor> linear_forward(const at::Tensor& x, const at::Tensor& we
     auto r = forward_impl(x, weight, MAM_B_NK, bias, dense_t, blend, alpha, beta, want_idx);
     if (!want_idx) return {r.y};
     return {r.y, r.argmax, r.argmin};
+}
+// linear_forward with the output dropout applied in the kernel epilogue: every element is dropped with
+// probability drop_rate by a counter-based generator keyed by (drop_seed, element index), kept ones are scaled
+// by 1 / (1 - drop_rate).  drop_apply forms the same mask again (the backward uses it on the upstream gradient).
+std::vector<at::Tensor> linear_forward_drop(const at::Tensor& x, const at::Tensor& weight,
+                                            const c10::optional<at::Tensor>& bias,
+                                            const c10::optional<at::Tensor>& dense_t, double alpha, double beta,
+                                            bool want_idx, double drop_rate, int64_t drop_seed) {
+    const bool blend = !(alpha == 1.0 && beta == 0.0);
+    auto r = forward_impl(x, weight, MAM_B_NK, bias, dense_t, blend, alpha, beta, want_idx, drop_rate, drop_seed);
+    if (!want_idx) return {r.y};
+    return {r.y, r.argmax, r.argmin};
+}
+// out = t * scale where element i (row-major) is kept under (seed, rate), else 0
+at::Tensor drop_apply(const at::Tensor& t, double rate, double scale, int64_t seed) {
+    TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kFloat, "t must be a float32 CUDA tensor");
+    TORCH_CHECK(rate >= 0.0 && rate < 1.0, "rate must be in [0, 1)");
+    auto tc = t.contiguous();
+    c10::cuda::CUDAGuard guard(t.device());
+    auto out = at::empty_like(tc);
+    if (tc.numel() == 0) return out;
+    auto stream = at::cuda::getCurrentCUDAStream();
+    check_status(mam_drop_f32(tc.data_ptr<float>(), out.data_ptr<float>(), tc.numel(), (float)rate, (float)scale,
+                              (uint64_t)seed, stream.stream()),
+                 "mam_drop_f32");
+    return out;
 }
 // y[M,N] with K cut into slices of split_width columns, each contributing its own max + min; an empty tensor
 // where the single-launch form does not apply (the caller then goes slice by slice)
@@ -693,6 +726,8 @@ TORCH_LIBRARY_IMPL(mamtorch_kernel_v4, CUDA, m) {
 
 TORCH_LIBRARY(mamtorch_b200, m) {
     m.def("linear_forward(Tensor x, Tensor weight, Tensor? bias, Tensor? dense, float alpha, float beta, bool want_idx) -> Tensor[]");
+    m.def("linear_forward_drop(Tensor x, Tensor weight, Tensor? bias, Tensor? dense, float alpha, float beta, bool want_idx, float drop_rate, int drop_seed) -> Tensor[]");
+    m.def("drop_apply(Tensor t, float rate, float scale, int seed) -> Tensor");
     m.def("linear_backward(Tensor x, Tensor weight, Tensor grad, Tensor argmax, Tensor argmin, float scale) -> Tensor[]");
     m.def("linear_backward_count(Tensor x, Tensor weight, Tensor grad, Tensor argmax, Tensor argmin, float scale) -> Tensor[]");
     m.def("linear_backward_km(Tensor x, Tensor weight, Tensor grad, Tensor argmax, Tensor argmin, float scale) -> Tensor[]");
@@ -718,6 +753,8 @@ TORCH_LIBRARY(mamtorch_b200, m) {
 }
 TORCH_LIBRARY_IMPL(mamtorch_b200, CUDA, m) {
     m.impl("linear_forward", &linear_forward);
+    m.impl("linear_forward_drop", &linear_forward_drop);
+    m.impl("drop_apply", &drop_apply);
     m.impl("linear_backward", &linear_backward);
     m.impl("linear_backward_count", &linear_backward_count);
     m.impl("linear_backward_km", &linear_backward_km);

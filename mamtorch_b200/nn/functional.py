@@ -23,6 +23,21 @@ def _(x, weight, bias, dense, alpha, beta, want_idx):
     return out
 
 
+@torch.library.register_fake("mamtorch_b200::linear_forward_drop")
+def _(x, weight, bias, dense, alpha, beta, want_idx, drop_rate, drop_seed):
+    torch._check(x.dim() == 2 and weight.dim() == 2 and x.size(1) == weight.size(1))
+    shape = (x.size(0), weight.size(0))
+    out = [x.new_empty(shape)]
+    if want_idx:
+        out += [x.new_empty(shape, dtype=torch.int), x.new_empty(shape, dtype=torch.int)]
+    return out
+
+
+@torch.library.register_fake("mamtorch_b200::drop_apply")
+def _(t, rate, scale, seed):
+    return torch.empty_like(t, memory_format=torch.contiguous_format)
+
+
 @torch.library.register_fake("mamtorch_b200::linear_backward")
 def _(x, weight, grad, argmax, argmin, scale):
     return [torch.empty_like(x), torch.empty_like(weight)]
@@ -183,14 +198,45 @@ def dense_linear(x: Tensor, weight: Tensor) -> Tensor:
     return _DenseLinear.apply(x.contiguous(), weight.contiguous())
 
 
-class _MamLinear(torch.autograd.Function):
-    """y = alpha*(max_k x*w + min_k x*w) + beta*dense + bias, gradient through the selected pairs."""
+def fresh_drop_seed() -> int:
+    """A seed for the library's counter-based drop masks, drawn from torch's CPU generator: reproducible
+    under torch.manual_seed and without a device synchronisation."""
+    return int(torch.randint(0, 2 ** 62, (1,)).item())
+
+
+class _WeightDrop(torch.autograd.Function):
+    """weight * mask with mask ~ Bernoulli(1 - rate) per element, unscaled, as the reference module's weight
+    drop (`mamtorch/nn/v4/fullyconnected.py:143-148`): one kernel pass forward and one backward, the mask formed
+    again from its seed instead of being stored."""
 
     @staticmethod
-    def forward(ctx, x, weight, bias, dense, alpha, beta, hit_sink=None):
-        y, argmax, argmin = _ops.linear_forward(x, weight, bias, dense, alpha, beta, True)
+    def forward(ctx, weight, rate, seed):
+        ctx.rate, ctx.seed = rate, seed
+        return _ops.drop_apply(weight, rate, 1.0, seed)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _ops.drop_apply(g, ctx.rate, 1.0, ctx.seed), None, None
+
+
+def weight_drop(weight: Tensor, rate: float, seed: int | None = None) -> Tensor:
+    return _WeightDrop.apply(weight, float(rate), fresh_drop_seed() if seed is None else int(seed))
+
+
+class _MamLinear(torch.autograd.Function):
+    """y = drop(alpha*(max_k x*w + min_k x*w) + beta*dense + bias), gradient through the selected pairs.  The
+    output dropout (drop_rate > 0) happens in the forward kernel's epilogue; its mask is formed again from
+    (drop_seed, element index) for the backward."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, dense, alpha, beta, hit_sink=None, drop_rate=0.0, drop_seed=0):
+        if drop_rate > 0:
+            y, argmax, argmin = _ops.linear_forward_drop(x, weight, bias, dense, alpha, beta, True, drop_rate, drop_seed)
+        else:
+            y, argmax, argmin = _ops.linear_forward(x, weight, bias, dense, alpha, beta, True)
         ctx.save_for_backward(x, weight, argmax, argmin)
         ctx.alpha, ctx.beta, ctx.hit_sink = alpha, beta, hit_sink
+        ctx.drop_rate, ctx.drop_seed = drop_rate, drop_seed
         ctx.has_bias, ctx.has_dense = bias is not None, dense is not None
         ctx.mark_non_differentiable(argmax, argmin)
         return y, argmax, argmin
@@ -199,6 +245,8 @@ class _MamLinear(torch.autograd.Function):
     def backward(ctx, gy, _g1, _g2):
         x, weight, argmax, argmin = ctx.saved_tensors
         gy = gy.contiguous()
+        if ctx.drop_rate > 0:
+            gy = _ops.drop_apply(gy, ctx.drop_rate, 1.0 / (1.0 - ctx.drop_rate), ctx.drop_seed)
         dx = dw = dbias = ddense = None
         if ctx.needs_input_grad[0] or ctx.needs_input_grad[1]:
             if ctx.hit_sink is not None:
@@ -210,25 +258,34 @@ class _MamLinear(torch.autograd.Function):
             dbias = gy.sum(0)
         if ctx.has_dense and ctx.needs_input_grad[3]:
             ddense = gy * ctx.beta
-        return dx, dw, dbias, ddense, None, None, None
+        return dx, dw, dbias, ddense, None, None, None, None, None
 
 
 def mam_linear(x: Tensor, weight: Tensor, bias: Tensor | None = None, dense: Tensor | None = None,
-               alpha: float = 1.0, beta: float = 0.0, need_indices: bool = True, hit_sink: "HitSink | None" = None):
+               alpha: float = 1.0, beta: float = 0.0, need_indices: bool = True, hit_sink: "HitSink | None" = None,
+               drop_rate: float = 0.0, drop_seed: int | None = None):
     """x[M,K], weight[N,K] -> (y[M,N], argmax, argmin) or (y, None, None).
 
-    With `need_indices=False` the values-only kernel runs (no autograd: use it for inference)."""
+    With `need_indices=False` the values-only kernel runs (no autograd: use it for inference).
+    `drop_rate > 0` applies output dropout in the kernel epilogue (a training-time option: it always drops)."""
     x = x.contiguous()
     weight = weight.contiguous()
+    drop_rate = float(drop_rate)
+    if drop_rate > 0 and drop_seed is None:
+        drop_seed = fresh_drop_seed()
+    drop_seed = int(drop_seed or 0)
     if not need_indices and torch.is_grad_enabled() and (
             x.requires_grad or weight.requires_grad or (bias is not None and bias.requires_grad)
             or (dense is not None and dense.requires_grad)):
         need_indices = True  # a gradient is wanted: only the index-producing kernel can route it
-        y, _, _ = _MamLinear.apply(x, weight, bias, dense, float(alpha), float(beta))
+        y, _, _ = _MamLinear.apply(x, weight, bias, dense, float(alpha), float(beta), None, drop_rate, drop_seed)
         return y, None, None
     if need_indices:
-        return _MamLinear.apply(x, weight, bias, dense, float(alpha), float(beta), hit_sink)
-    y, = _ops.linear_forward(x, weight, bias, dense, float(alpha), float(beta), False)
+        return _MamLinear.apply(x, weight, bias, dense, float(alpha), float(beta), hit_sink, drop_rate, drop_seed)
+    if drop_rate > 0:
+        y, = _ops.linear_forward_drop(x, weight, bias, dense, float(alpha), float(beta), False, drop_rate, drop_seed)
+    else:
+        y, = _ops.linear_forward(x, weight, bias, dense, float(alpha), float(beta), False)
     return y, None, None
 
 

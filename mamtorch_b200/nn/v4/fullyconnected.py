@@ -128,7 +128,8 @@ class FullyConnected(Module):
         if self.training and self.wdrop_rate != 0:
             if not 0 < self.wdrop_rate < 1:
                 raise Exception("wdrop_rate must be between 0 and 1.")
-            w = torch.bernoulli(torch.full_like(w, 1 - self.wdrop_rate)) * w
+            # one kernel pass, the mask formed again from its seed in the backward (no stored mask, no temporaries)
+            w = MF.weight_drop(w, self.wdrop_rate)
 
         dense = None
         if self.beta > 0:
@@ -170,11 +171,16 @@ class FullyConnected(Module):
             if self.bias is not None:
                 y = y + self.bias
         else:
+            # output dropout rides in the kernel epilogue (training only; F.dropout is the identity otherwise)
+            fused_drop = self.drop_rate if (self.training and 0 < self.drop_rate < 1) else 0.0
             y, argmax, argmin = MF.mam_linear(x, w, self.bias, dense, self.alpha, self.beta if dense is not None else 0.0,
                                               need_indices=need_idx,
-                                              hit_sink=self._hit_sink if (self.store_args and self.training) else None)
+                                              hit_sink=self._hit_sink if (self.store_args and self.training) else None,
+                                              drop_rate=fused_drop)
             if self.store_args:
                 self.argmax, self.argmin = argmax, argmin
+            if fused_drop > 0:
+                return y.view(input.shape[:-1] + (self.out_features,))
 
         y = y.view(input.shape[:-1] + (self.out_features,))
         if self.drop_rate > 0:

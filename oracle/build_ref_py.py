@@ -3,7 +3,7 @@ infrastructure only: nothing in the product path loads what this makes.
 
 The source -- `test/reference.py` of a checkout of SSIGPRO/mamtorch (26 lines of plain torch:
 `fullyconnected_reference`, `fullyconnected_backward_reference`) -- is compiled where it lies; it is not
-copied.  The output, oracle/_ref/reference.pyc, is a build product like the shared objects beside it: it
+copied.  The output, oracle/_ref/reference_checker.bin, is a build product like the shared objects beside it: it
 stays out of version control and travels with the built tree, so that `bench.py --impl reference` and the
 `cpu_baseline` leg can time the reference's unmodified CPU path (kind "reference") on a machine that has
 no checkout.  Where the file is missing, or was compiled by another Python version, bench.py falls back
@@ -19,7 +19,7 @@ import py_compile
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-OUT = os.path.join(HERE, "_ref", "reference.pyc")
+OUT = os.path.join(HERE, "_ref", "reference_checker.bin")
 
 
 def build(ref: str | None = None) -> str | None:

@@ -96,6 +96,50 @@ def test_backward_counts_hits_on_the_way(cuda):
     assert_grad_close(dw.cpu().numpy(), dw_ref.cpu().numpy())
 
 
+@pytest.mark.parametrize("layout", [capi.NK, capi.KN])
+@pytest.mark.parametrize("shape", [(3000, 768, 200), (1500, 3072, 96), (257, 40, 515), (64, 5, 33)])
+def test_backward_with_hits_riding_on_the_dw_reductions(shape, layout, cuda):
+    """mam_bwd_count_ws_f32 with scratch for the 16-byte {dW, max hits, min hits} records: one sweep, the same
+    gradients (to rounding) and exactly the same hits as the gradient kernel followed by mam_selcount_i32 -- in
+    both weight layouts, with both gradient kernels (K = 768 takes the row-per-warp form), hits accumulated
+    into the caller's matrices over two calls."""
+    import ctypes
+
+    from mamtorch_b200 import _lib
+
+    M, K, N = shape
+    L = _lib.lib()
+    gen = torch.Generator().manual_seed(M + K)
+    a = torch.randn(M, K, generator=gen).to(cuda)
+    w = (torch.randn(N, K, generator=gen) * K ** -0.5).to(cuda)
+    grad = torch.randn(M, N, generator=gen).to(cuda)
+    _, imax, imin = capi.forward(a, w, capi.NK)
+    imin[0, :] = imax[0, :]          # coincident selections count for both sides
+    b = w if layout == capi.NK else w.T.contiguous()
+    da_ref, db_ref = capi.backward(a, b, grad, imax, imin, layout)
+    hmax_ref, hmin_ref = capi.selcount(imax, imin, K)
+    assert L.mam_bwd_count_workspace_bytes(1 << 24, K, N) == 0            # counts would no longer be exact
+    assert L.mam_bwd_count_workspace_bytes(M, K, 1 << 22) == 0 or K < 4   # records beyond L2: second sweep advised
+    need = ((K * N * 16 + 255) // 256) * 256
+    ws = torch.empty(need, dtype=torch.uint8, device=cuda)
+    da, db = torch.empty_like(a), torch.empty_like(b)
+    hmax = torch.zeros((N, K), dtype=torch.int32, device=cuda)
+    hmin = torch.zeros((N, K), dtype=torch.int32, device=cuda)
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    for _ in range(2):
+        st = L.mam_bwd_count_ws_f32(p(a), p(b), layout, p(grad), p(imax), p(imin), p(da), 0, p(db), p(hmax), p(hmin),
+                                    1.0, M, K, N, p(ws), need, stream)
+        _lib.check(st, "mam_bwd_count_ws_f32")
+    assert capi.device_flag_ok()
+    assert torch.equal(hmax, 2 * hmax_ref) and torch.equal(hmin, 2 * hmin_ref)
+    assert_grad_close(da.cpu().numpy(), da_ref.cpu().numpy())
+    assert_grad_close(db.cpu().numpy(), db_ref.cpu().numpy())
+    # scratch too small or misaligned is refused before anything is launched
+    assert L.mam_bwd_count_ws_f32(p(a), p(b), layout, p(grad), p(imax), p(imin), p(da), 0, p(db), p(hmax), p(hmin),
+                                  1.0, M, K, N, p(ws), need - 256, stream) == 3
+
+
 @pytest.mark.parametrize("name", ["relu_pruned_64x96x64", "edge_128x160x128"])
 def test_selection_count_golden(name, cuda):
     g = load_golden(name)

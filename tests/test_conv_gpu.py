@@ -305,7 +305,10 @@ def test_channels_last_copy(shape, cuda):
     out = torch.ops.mamtorch_b200.conv_channels_last(x)
     assert out.shape == (B, H, W, C) and out.is_contiguous()
     assert torch.equal(out, x.permute(0, 2, 3, 1))
-    # already channels-last in memory: handed back as a view, no copy
+    # the operator always returns a fresh tensor (its schema says so); an input that already is channels-last
+    # in memory gives the same values, and the module uses such an input in place without calling it
     xcl = x.contiguous(memory_format=torch.channels_last)
-    view = torch.ops.mamtorch_b200.conv_channels_last(xcl)
-    assert view.data_ptr() == xcl.data_ptr() and torch.equal(view, out)
+    copy = torch.ops.mamtorch_b200.conv_channels_last(xcl)
+    assert copy.data_ptr() != xcl.data_ptr() and torch.equal(copy, out)
+    assert xcl.permute(0, 2, 3, 1).is_contiguous()
+    torch.library.opcheck(torch.ops.mamtorch_b200.conv_channels_last, (xcl,))

@@ -53,7 +53,7 @@ def test_blended_ops_match_reference_formula(ns, backend, cuda):
             assert torch.equal(cf, c)
     finally:
         torch.backends.cuda.matmul.allow_tf32 = prev
-        MF.set_dense_backend("tf32")
+        MF.set_dense_backend("auto")
     assert np.array_equal(imax.cpu().numpy(), g["argmax"]) and np.array_equal(imin.cpu().numpy(), g["argmin"])
     np.testing.assert_allclose(c.cpu().numpy(), g["y"], rtol=tol, atol=tol * float(np.abs(g["y"]).max()))
     assert_grad_close(da.cpu().numpy(), g["agrad"], rtol=tol)
@@ -249,9 +249,12 @@ def test_conv1d(cuda):
     ((rows[r, im] * wf[c, im] + rows[r, imn] * wf[c, imn]) * gy.cpu().permute(0, 2, 1).reshape(-1, 6)).sum().backward()
     assert_grad_close(x.grad.cpu().numpy(), xw.grad.numpy())
     assert_grad_close(conv.weight.grad.cpu().numpy(), ww.grad.numpy())
+    # the convolution modules keep the two counts apart (mamtorch/nn/backup/mamconv2d.txt:90-114): +1 per call for
+    # every weight some output pixel selected as max, likewise for min
     conv.update_selection_count()
-    want = mam_oracle.selection_count_update(torch.zeros(6, 12, dtype=torch.int32), im, imn)
-    assert torch.equal(conv.max_selection_count.cpu().reshape(6, 12), want)
+    hmax, hmin = mam_oracle.selection_hits(im, imn, 12)
+    assert torch.equal(conv.max_selection_count.cpu().reshape(6, 12), (hmax > 0).int())
+    assert torch.equal(conv.min_selection_count.cpu().reshape(6, 12), (hmin > 0).int())
 
 
 def test_conv2d_selection_count_against_the_oracle(cuda):
@@ -264,13 +267,17 @@ def test_conv2d_selection_count_against_the_oracle(cuda):
     conv.update_selection_count()
     conv(x * -1.5)
     conv.update_selection_count()
-    want = torch.zeros(7, 45, dtype=torch.int32)
+    want_max = torch.zeros(7, 45, dtype=torch.int32)
+    want_min = torch.zeros(7, 45, dtype=torch.int32)
     for xs in (x, x * -1.5):
         _, imax, imin = mam_oracle.mam_conv2d_forward(xs.cpu(), conv.weight.detach().cpu(), conv.bias.detach().cpu(),
                                                       stride=2, padding=1)
-        want = mam_oracle.selection_count_update(want, imax.permute(0, 2, 3, 1).reshape(-1, 7),
-                                                 imin.permute(0, 2, 3, 1).reshape(-1, 7))
-    assert torch.equal(conv.max_selection_count.cpu().reshape(7, 45), want)
+        hmax, hmin = mam_oracle.selection_hits(imax.permute(0, 2, 3, 1).reshape(-1, 7),
+                                               imin.permute(0, 2, 3, 1).reshape(-1, 7), 45)
+        want_max += (hmax > 0).int()      # +1 per call and weight, max and min kept apart
+        want_min += (hmin > 0).int()      # (mamtorch/nn/backup/mamconv2d.txt:90-114)
+    assert torch.equal(conv.max_selection_count.cpu().reshape(7, 45), want_max)
+    assert torch.equal(conv.min_selection_count.cpu().reshape(7, 45), want_min)
 
 
 def test_store_args_before_the_first_vcon_step(cuda):
@@ -407,3 +414,79 @@ def test_conv_benchmark_shape_properties(cuda):
     c = torch.arange(128, device=cuda)[None, :].expand_as(im)
     want = rows[r, im] * wf[c, im] + rows[r, imn] * wf[c, imn]
     assert torch.equal(y[:8].permute(0, 2, 3, 1).reshape(-1, 128), want)
+
+
+def test_output_dropout_in_the_kernel_epilogue(cuda):
+    """Training-mode output dropout rides in the forward epilogue: y = mask * (mam + bias) / (1 - p) with a mask
+    that depends only on (seed, element), so the values-only and index-producing kernels, the any-shape kernel and
+    `drop_apply` all form the same one; the backward routes mask * gy / (1 - p) through the selected pairs."""
+    from mamtorch_b200.nn import functional as MF
+
+    ops = torch.ops.mamtorch_b200
+    p, seed = 0.3, 123456789
+    for (M, K, N) in ((300, 96, 200), (70, 65, 66)):          # tiled kernels / any-shape kernel (K % 4 != 0)
+        x, w, bias = _rand((M, K), 20, cuda), _rand((N, K), 21, cuda, K ** -0.5), _rand((N,), 22, cuda)
+        y0, imax0, imin0 = ops.linear_forward(x, w, bias, None, 1.0, 0.0, True)
+        y1, imax1, imin1 = ops.linear_forward_drop(x, w, bias, None, 1.0, 0.0, True, p, seed)
+        y2, = ops.linear_forward_drop(x, w, bias, None, 1.0, 0.0, False, p, seed)
+        mask = ops.drop_apply(torch.ones_like(y0), p, 1.0, seed)
+        assert set(mask.unique().tolist()) == {0.0, 1.0}
+        assert abs(float(mask.mean()) - (1 - p)) < 0.02
+        want = mask * (y0 * (1.0 / (1.0 - p)))
+        assert torch.equal(y1, want) and torch.equal(y2, want)
+        assert torch.equal(imax1, imax0) and torch.equal(imin1, imin0)
+        other = ops.drop_apply(torch.ones_like(y0), p, 1.0, seed + 1)
+        assert not torch.equal(other, mask)
+        # autograd: the same function written with the explicit mask
+        xa, wa = x.clone().requires_grad_(), w.clone().requires_grad_()
+        xb, wb = x.clone().requires_grad_(), w.clone().requires_grad_()
+        gy = _rand((M, N), 23, cuda)
+        ya, _, _ = MF.mam_linear(xa, wa, bias, drop_rate=p, drop_seed=seed)
+        yb, _, _ = MF.mam_linear(xb, wb, bias)
+        ya.backward(gy)
+        (yb * mask * (1.0 / (1.0 - p))).backward(gy)
+        assert torch.equal(ya, want)
+        assert_grad_close(xa.grad.cpu().numpy(), xb.grad.cpu().numpy())
+        assert_grad_close(wa.grad.cpu().numpy(), wb.grad.cpu().numpy())
+
+
+def test_module_weight_drop_and_output_dropout(cuda):
+    """FullyConnected with wdrop_rate and drop_rate: in training both masks come from the library's generator
+    (reproducible under torch.manual_seed, different from call to call), weight drop is unscaled as in the
+    reference (mamtorch/nn/v4/fullyconnected.py:143-148), dropped weights and dropped outputs get no gradient;
+    in eval mode the layer is the plain one."""
+    import mamtorch_b200 as mamtorch
+    from mamtorch_b200.nn import functional as MF
+
+    torch.manual_seed(7)
+    layer = mamtorch.nn.FullyConnected(128, 96, wdrop_rate=0.25, drop_rate=0.4).to(cuda)
+    plain = mamtorch.nn.FullyConnected(128, 96).to(cuda)
+    plain.load_state_dict(layer.state_dict())
+    x = _rand((50, 128), 30, cuda)
+    layer.eval()
+    plain.eval()
+    assert torch.equal(layer(x), plain(x))
+    layer.train()
+    torch.manual_seed(99)
+    y1 = layer(x)
+    torch.manual_seed(99)
+    y2 = layer(x)
+    y3 = layer(x)
+    assert torch.equal(y1, y2) and not torch.equal(y1, y3)
+    frac_zero = float((y1 == 0).float().mean())
+    assert abs(frac_zero - 0.4) < 0.05
+    # the two pieces on their own
+    w = layer.weight.detach()
+    wd = MF.weight_drop(w, 0.25, seed=5)
+    kept = wd != 0
+    assert torch.equal(wd[kept], w[kept]) and abs(float(kept.float().mean()) - 0.75) < 0.02
+    wr = w.clone().requires_grad_()
+    MF.weight_drop(wr, 0.25, seed=5).sum().backward()
+    assert torch.equal(wr.grad, kept.float())
+    # gradients flow and dropped outputs contribute nothing
+    xg = x.clone().requires_grad_()
+    torch.manual_seed(99)
+    yg = layer(xg)
+    yg.backward(torch.ones_like(yg))
+    assert torch.equal(yg, y1) and xg.grad.shape == x.shape and layer.weight.grad.shape == layer.weight.shape
+    assert float(layer.bias.grad.min()) >= 0 and abs(float(layer.bias.grad.sum()) - float((y1 != 0).sum()) / 0.6) < 1.0

@@ -111,5 +111,5 @@ def test_sparse_namespace_carries_the_csr_mam_pair(case, cuda):
     da0, db0 = torch.ops.mamtorch_kernel_v4.fullyconnected_backward(a, w.T.contiguous(), c, argmax0, argmin0)
     assert_grad_close(da.cpu().numpy(), da0.cpu().numpy())
     assert_grad_close(dw.cpu().numpy(), db0.T.cpu().numpy())
-    torch.library.opcheck(torch.ops.mamtorch_kernel_sparsev1.fullyconnected_csr,
-                          (a, w_csr.crow_indices(), w_csr.col_indices(), w_csr.values(), None))
+    crow, col, val = (t.clone() for t in (w_csr.crow_indices(), w_csr.col_indices(), w_csr.values()))
+    torch.library.opcheck(torch.ops.mamtorch_kernel_sparsev1.fullyconnected_csr, (a, crow, col, val, None))

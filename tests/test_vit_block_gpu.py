@@ -18,7 +18,7 @@ def fp32_dense():
 
     MF.set_dense_backend("fp32")
     yield
-    MF.set_dense_backend("tf32")
+    MF.set_dense_backend("auto")
 
 
 def test_swapped_hf_vit_starts_dense_and_ends_mam(cuda, fp32_dense):
