@@ -118,6 +118,16 @@ int mam_fwd_splits_f32(const float* a, const float* w, const float* bias, const 
                        float alpha, float beta, float* y, int64_t M, int64_t K, int64_t N,
                        int64_t split_width, void* stream);
 
+/* The same with indices, for training: argmax / argmin receive one [M,N] matrix PER SLICE ([slices][M][N],
+ * slices = ceil(K / split_width)), each holding the slice's selected k in the numbering of the whole row.  One
+ * launch of the index-producing forward for all slices (their partial sums are banked in y on the way) and one
+ * index-resolver launch per slice, in place of one forward call, one addition pass and one autograd node per
+ * slice (mamtorch/nn/v4/fullyconnected.py:164-176).  Same preconditions and MAM_ERR_UNSUPPORTED rule as
+ * mam_fwd_splits_f32.  mam_bwd_splits_f32 is its backward. */
+int mam_fwd_splits_idx_f32(const float* a, const float* w, const float* bias, const float* dense, int blend,
+                           float alpha, float beta, float* y, int32_t* argmax, int32_t* argmin,
+                           int64_t M, int64_t K, int64_t N, int64_t split_width, void* stream);
+
 /* Forward for callers that cannot allocate device memory.  (No counterpart in the reference:
  * its host code allocates freely through ATen.)
  *
@@ -183,6 +193,13 @@ int mam_bwd_count_ex_f32(const float* a, const float* b, int b_layout, const flo
                          const int32_t* argmax, const int32_t* argmin,
                          float* da, int da_layout, float* db, int32_t* hit_max, int32_t* hit_min, float scale,
                          int64_t M, int64_t K, int64_t N, void* stream);
+/* mam_bwd_count_ws_f32 for `slices` pairs of index matrices ([slices][M][N], as mam_fwd_splits_idx_f32 leaves
+ * them): every slice routes the same upstream gradient through its own selected pairs, all in one pass over
+ * the rows; hits (optional) are counted over all slices.  slices == 1 is mam_bwd_count_ws_f32. */
+int mam_bwd_splits_f32(const float* a, const float* b, int b_layout, const float* grad,
+                       const int32_t* argmax, const int32_t* argmin, int slices,
+                       float* da, int da_layout, float* db, int32_t* hit_max, int32_t* hit_min, float scale,
+                       int64_t M, int64_t K, int64_t N, void* workspace, size_t workspace_bytes, void* stream);
 size_t mam_bwd_count_workspace_bytes(int64_t M, int64_t K, int64_t N);
 int mam_bwd_count_ws_f32(const float* a, const float* b, int b_layout, const float* grad,
                          const int32_t* argmax, const int32_t* argmin,

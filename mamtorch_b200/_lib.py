@@ -34,6 +34,8 @@ ABI = {
     "mam_bwd_f32": (_i32, [_vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _f32, _i64, _i64, _i64, _vp]),
     "mam_bwd_count_f32": (_i32, [_vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f32, _i64, _i64, _i64, _vp]),
     "mam_bwd_count_ex_f32": (_i32, [_vp, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _f32, _i64, _i64, _i64, _vp]),
+    "mam_fwd_splits_idx_f32": (_i32, [_vp, _vp, _vp, _vp, _i32, _f32, _f32, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp]),
+    "mam_bwd_splits_f32": (_i32, [_vp, _vp, _i32, _vp, _vp, _vp, _i32, _vp, _i32, _vp, _vp, _vp, _f32, _i64, _i64, _i64, _vp, _sz, _vp]),
     "mam_bwd_count_workspace_bytes": (_sz, [_i64, _i64, _i64]),
     "mam_bwd_count_ws_f32": (_i32, [_vp, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _f32, _i64, _i64, _i64, _vp, _sz, _vp]),
     "mam_conv_bwd_f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _f32, _i64, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _i64, _vp]),

@@ -58,7 +58,9 @@ __global__ void __launch_bounds__(BWD_THREADS)
 mam_bwd_kernel(const float* __restrict__ a, const float* __restrict__ w, const float* __restrict__ g,
                const int* __restrict__ argmax, const int* __restrict__ argmin,
                float* __restrict__ da, float* __restrict__ dw,
-               long long M, long long K, long long N, int rows_per_cta, float scale, ConvGeom cg = ConvGeom{}) {
+               long long M, long long K, long long N, int rows_per_cta, float scale, ConvGeom cg, int slices) {
+    // slices > 1: argmax / argmin hold one [M,N] matrix per slice of K (the module's `splits`); every slice
+    // routes the same upstream gradient through its own selected pairs
     extern __shared__ float da_s[];  // [rows_per_cta][K]
     const long long m0 = (long long)blockIdx.x * rows_per_cta;
     const int rows = (int)min((long long)rows_per_cta, M - m0);
@@ -91,9 +93,10 @@ mam_bwd_kernel(const float* __restrict__ a, const float* __restrict__ w, const f
             }
         };
         float* dar = da_s + (long long)r * K;
-        for (long long n = threadIdx.x; n < N; n += BWD_THREADS) {
+        for (long long sn = threadIdx.x; sn < N * slices; sn += BWD_THREADS) {
+            const long long sl = sn / N, n = sn - sl * N;
             const float gv = __fmul_rn(g[m * N + n], scale);
-            int k1 = argmax[m * N + n], k2 = argmin[m * N + n];
+            int k1 = argmax[sl * M * N + m * N + n], k2 = argmin[sl * M * N + m * N + n];
             // an index outside [0,K) cannot come from the forward; skip it rather than fault
             const bool ok1 = (unsigned)k1 < (unsigned long long)K, ok2 = (unsigned)k2 < (unsigned long long)K;
             if (ok1) {
@@ -159,7 +162,7 @@ __global__ void __launch_bounds__(BWD_THREADS)
 mam_bwd_rowwarp_kernel(const float* __restrict__ a, const float* __restrict__ w, const float* __restrict__ g,
                        const int* __restrict__ argmax, const int* __restrict__ argmin,
                        float* __restrict__ da, float* __restrict__ dw,
-                       long long M, long long K, long long N, float scale) {
+                       long long M, long long K, long long N, float scale, int slices) {
     extern __shared__ float rw_s[];   // per warp: da row [K] (+ a row [K])
     constexpr int WARPS = BWD_THREADS / 32, U = BWD_RW_UNROLL;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -174,8 +177,9 @@ mam_bwd_rowwarp_kernel(const float* __restrict__ a, const float* __restrict__ w,
     }
     __syncwarp();
     const float* grow = g + m * N;
-    const int* r1 = argmax + m * N;
-    const int* r2 = argmin + m * N;
+    for (int sl = 0; sl < slices; ++sl) {   // one [M,N] pair of index matrices per slice of K
+    const int* r1 = argmax + (long long)sl * M * N + m * N;
+    const int* r2 = argmin + (long long)sl * M * N + m * N;
     for (long long nb = 0; nb < N; nb += 32 * U) {
         float gv[U], t1[U], t2[U];
         int k1[U], k2[U];
@@ -216,6 +220,7 @@ mam_bwd_rowwarp_kernel(const float* __restrict__ a, const float* __restrict__ w,
             warp_row_add(dar, k1[u], ok1[u], t1[u], lane);
             warp_row_add(dar, k2[u], ok2[u], t2[u], lane);
         }
+    }
     }
     for (long long k = lane; k < K; k += 32) da[m * K + k] = dar[k];
 }

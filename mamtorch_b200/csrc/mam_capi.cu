@@ -92,12 +92,13 @@ int get_encode() {
 }
 
 // [rows, K] fp32 row-major matrix -> boxes of [box_rows][32 floats], 128-byte swizzle (or none), zero fill.
+// pitch: floats between the starts of consecutive rows (0: K), for a matrix that is a column slice of a wider one
 int encode_rows_k(CUtensorMap* tm, const float* base, long long rows, long long K, int box_rows,
-                  bool swizzle = true) {
+                  bool swizzle = true, long long pitch = 0) {
     int st = get_encode();
     if (st != MAM_OK) return st;
     cuuint64_t gdim[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-    cuuint64_t gstr[1] = {(cuuint64_t)K * 4};
+    cuuint64_t gstr[1] = {(cuuint64_t)(pitch ? pitch : K) * 4};
     cuuint32_t box[2] = {(cuuint32_t)FWD_BK, (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = g_encode(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), gdim, gstr, box,
@@ -195,6 +196,7 @@ using ValCfg5 = FwdCfg<4, 8, 4, 2, 4, false, 2, false, false>;  // 64x128 tile, 
 using ValCfg6 = FwdCfg<4, 8, 4, 2, 4, false, 2, true>;          // 64x128 tile, 256 threads
 using ValCfg7 = FwdCfg<4, 4, 8, 2, 6, false, 4, false>;         // 128x64 tile, 512 threads
 using SplitCfg = FwdCfg<4, 8, 4, 2, 4, false, 2, false, true, true>;   // 64x128 tile, slices of K summed in the kernel
+using SplitIdxCfg = FwdCfg<4, 8, 4, 2, 4, true, 2, false, true, true>;  // the same with chunk ids per slice
 using IdxCfg0 = FwdCfg<4, 8, 4, 2, 4, true, 2, false, false>;   // 64x128 tile, 256 threads, scalar multiplies
 using IdxCfg1 = FwdCfg<4, 8, 4, 2, 4, true, 2, false>;          // 64x128 tile, 256 threads
 using IdxCfg2 = FwdCfg<4, 8, 4, 2, 4, true, 1, false>;
@@ -271,6 +273,9 @@ bool conv_implicit_applies(const ConvGeom& g, const float* x_nhwc) {
     return true;
 }
 
+int run_resolver(const float* a, const float* w, int32_t* argmax, int32_t* argmin, int64_t M, int64_t K, int64_t N,
+                 int64_t pitch, int k_offset, int* flag, const Im2colRows& conv, cudaStream_t cs, const ConvSrc* cv);
+
 // The tiled forward (and, with indices, the resolver behind it) on K-contiguous operands a[M,K] (or,
 // with `cv`, patch rows read from a channels-last convolution input) and w[N,K].
 int run_tiled(const float* a, const float* w, float* y, int32_t* argmax, int32_t* argmin, int64_t M, int64_t K,
@@ -320,13 +325,23 @@ int run_tiled(const float* a, const float* w, float* y, int32_t* argmax, int32_t
         }
     }
     if (st != MAM_OK) return st;
+    return run_resolver(a, w, argmax, argmin, M, K, N, 0, 0, flag, prm.conv, cs, cv);
+}
+
+// Chunk ids -> exact indices.  pitch / k_offset: the operands are the column slice [k_offset, k_offset + K) of
+// matrices whose rows are `pitch` floats apart (0: K); a and w already point at the slice's first column.
+int run_resolver(const float* a, const float* w, int32_t* argmax, int32_t* argmin, int64_t M, int64_t K, int64_t N,
+                 int64_t pitch, int k_offset, int* flag, const Im2colRows& conv, cudaStream_t cs, const ConvSrc* cv) {
+    int st = MAM_OK;
     const int nkc = (int)((K + FWD_BK - 1) / FWD_BK);
     if (cv && nkc > ResolveCfg::NK_MAX) return MAM_ERR_UNSUPPORTED;
+    if (pitch && (nkc > ResolveCfg::NK_MAX || g_resolve_simple != 0)) return MAM_ERR_UNSUPPORTED;
     if ((nkc <= ResolveCfg::NK_MAX && g_resolve_simple == 0) || cv) {
         CUtensorMap tmA, tmW;
-        st = cv ? encode_im2col_rows(&tmA, *cv, ResolveCfg::RM, false) : encode_rows_k(&tmA, a, M, K, ResolveCfg::RM, false);
+        st = cv ? encode_im2col_rows(&tmA, *cv, ResolveCfg::RM, false)
+                : encode_rows_k(&tmA, a, M, K, ResolveCfg::RM, false, pitch);
         if (st != MAM_OK) return st;
-        st = encode_rows_k(&tmW, w, N, K, ResolveCfg::RN, false);
+        st = encode_rows_k(&tmW, w, N, K, ResolveCfg::RN, false, pitch);
         if (st != MAM_OK) return st;
         const long long tiles = ((M + ResolveCfg::RM - 1) / ResolveCfg::RM) * ((N + ResolveCfg::RN - 1) / ResolveCfg::RN);
         if (tiles > 2147483647LL) return MAM_ERR_UNSUPPORTED;
@@ -336,12 +351,12 @@ int run_tiled(const float* a, const float* w, float* y, int32_t* argmax, int32_t
             MAM_CUDA(cudaFuncSetAttribute(mam_resolve_tiled_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           rsmem));
             mam_resolve_tiled_kernel<true><<<(unsigned)tiles, ResolveCfg::THREADS, rsmem, cs>>>(
-                tmA, tmW, argmax, argmin, M, K, N, flag, prm.conv);
+                tmA, tmW, argmax, argmin, M, K, N, flag, conv, 0);
         } else {
             MAM_CUDA(cudaFuncSetAttribute(mam_resolve_tiled_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           rsmem));
             mam_resolve_tiled_kernel<false><<<(unsigned)tiles, ResolveCfg::THREADS, rsmem, cs>>>(
-                tmA, tmW, argmax, argmin, M, K, N, flag, prm.conv);
+                tmA, tmW, argmax, argmin, M, K, N, flag, conv, k_offset);
         }
     } else {
         const long long total = M * N;
@@ -633,6 +648,37 @@ int mam_fwd_splits_f32(const float* a, const float* w, const float* bias, const 
     return launch_tiled<SplitCfg>(a, w, prm, *d, (cudaStream_t)stream);
 }
 
+int mam_fwd_splits_idx_f32(const float* a, const float* w, const float* bias, const float* dense, int blend,
+                           float alpha, float beta, float* y, int32_t* argmax, int32_t* argmin, int64_t M, int64_t K,
+                           int64_t N, int64_t split_width, void* stream) {
+    if (bad_ptr(a) || bad_ptr(w) || bad_ptr(y) || bad_ptr(argmax) || bad_ptr(argmin) || M <= 0 || K <= 0 || N <= 0 ||
+        split_width <= 0)
+        return MAM_ERR_INVALID_ARGUMENT;
+    if (K >= (1LL << 31) || N >= (1LL << 31) || M >= (1LL << 31)) return MAM_ERR_UNSUPPORTED;
+    if (split_width % FWD_BK != 0 || split_width >= K || K % 4 != 0 || !aligned16(a) || !aligned16(w) ||
+        K / FWD_BK >= 65535 || split_width / FWD_BK > ResolveCfg::NK_MAX || g_resolve_simple != 0)
+        return MAM_ERR_UNSUPPORTED;
+    const DevInfo* d = nullptr;
+    int st = device_info(&d);
+    if (st != MAM_OK) return st;
+    cudaStream_t cs = (cudaStream_t)stream;
+    int* flag = nullptr;
+    MAM_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&flag), g_wait_gave_up));
+    EpilogueArgs ep{bias, dense, alpha, beta, blend};
+    FwdParams prm{y, argmax, argmin, M, K, N, ep, 1.0f, flag, Im2colRows{}, (int)(split_width / FWD_BK)};
+    st = launch_tiled<SplitIdxCfg>(a, w, prm, *d, cs);
+    if (st != MAM_OK) return st;
+    // every slice is a problem of its own for the resolver: its columns of a and w, its pair of index matrices
+    const int64_t slices = (K + split_width - 1) / split_width;
+    for (int64_t sl = 0; sl < slices; ++sl) {
+        const int64_t k0 = sl * split_width, width = (k0 + split_width <= K) ? split_width : K - k0;
+        st = run_resolver(a + k0, w + k0, argmax + sl * M * N, argmin + sl * M * N, M, width, N, K, (int)k0, flag,
+                          Im2colRows{}, cs, nullptr);
+        if (st != MAM_OK) return st;
+    }
+    return MAM_OK;
+}
+
 int mam_fwd_kn_static_f32(const float* a, const float* b, float* y, int32_t* argmax, int32_t* argmin, int64_t M,
                           int64_t K, int64_t N, void* stream) {
     if (M <= 0 || K <= 0 || N <= 0) return MAM_ERR_INVALID_ARGUMENT;
@@ -684,6 +730,15 @@ int mam_bwd_count_ws_f32(const float* a, const float* b, int b_layout, const flo
                          const int32_t* argmin, float* da, int da_layout, float* db, int32_t* hit_max,
                          int32_t* hit_min, float scale, int64_t M, int64_t K, int64_t N, void* workspace,
                          size_t workspace_bytes, void* stream) {
+    return mam_bwd_splits_f32(a, b, b_layout, grad, argmax, argmin, 1, da, da_layout, db, hit_max, hit_min, scale, M, K,
+                              N, workspace, workspace_bytes, stream);
+}
+
+int mam_bwd_splits_f32(const float* a, const float* b, int b_layout, const float* grad, const int32_t* argmax,
+                       const int32_t* argmin, int slices, float* da, int da_layout, float* db, int32_t* hit_max,
+                       int32_t* hit_min, float scale, int64_t M, int64_t K, int64_t N, void* workspace,
+                       size_t workspace_bytes, void* stream) {
+    if (slices < 1 || (long long)slices * M >= (1LL << 31)) return MAM_ERR_INVALID_ARGUMENT;
     if (da_layout != MAM_DA_MK && da_layout != MAM_DA_KM) return MAM_ERR_INVALID_ARGUMENT;
     if (bad_ptr(a) || bad_ptr(b) || bad_ptr(grad) || bad_ptr(argmax) || bad_ptr(argmin) || bad_ptr(da) ||
         bad_ptr(db) || M <= 0 || K <= 0 || N <= 0)
@@ -731,7 +786,7 @@ int mam_bwd_count_ws_f32(const float* a, const float* b, int b_layout, const flo
     while (cols > 1 && (N + cols - 1) / cols < 2LL * d->sms) cols >>= 1;
     // Measured on B200 the single-kernel form is faster at every benchmarked shape (0.87 vs 1.32 ms at
     // 12608x768x3072): the column-owned sweep is latency-bound.  The two-kernel form stays selectable.
-    const bool split = g_bwd_mode == 2 && da_layout == MAM_DA_MK;
+    const bool split = g_bwd_mode == 2 && da_layout == MAM_DA_MK && slices == 1;
     if (split && cols >= 1) {
         if (b_layout == MAM_B_NK)
             return launch_bwd_split<true>(a, b, grad, argmax, argmin, da, db, hit_max, hit_min, scale, M, K, N, rows,
@@ -759,7 +814,8 @@ int mam_bwd_count_ws_f32(const float* a, const float* b, int b_layout, const flo
         auto launch = [&](auto kern) -> int {
             MAM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_rw));
             TimedLaunch t(MAM_KERNEL_BWD, cs);
-            kern<<<(unsigned)grid_rw, BWD_THREADS, smem_rw, cs>>>(a, b, grad, argmax, argmin, da, dw_dst, M, K, N, scale);
+            kern<<<(unsigned)grid_rw, BWD_THREADS, smem_rw, cs>>>(a, b, grad, argmax, argmin, da, dw_dst, M, K, N, scale,
+                                                                   slices);
             return MAM_OK;
         };
         const bool nk = b_layout == MAM_B_NK;
@@ -772,7 +828,7 @@ int mam_bwd_count_ws_f32(const float* a, const float* b, int b_layout, const flo
         if (st != MAM_OK) return st;
         MAM_CUDA(cudaGetLastError());
         if (fused) return unpack();
-        if (count) return mam_selcount_i32(argmax, argmin, hit_max, hit_min, M, K, N, stream);
+        if (count) return mam_selcount_i32(argmax, argmin, hit_max, hit_min, M * slices, K, N, stream);
         return MAM_OK;
     }
     const size_t smem = (size_t)rows * (size_t)K * 4;
@@ -784,7 +840,7 @@ int mam_bwd_count_ws_f32(const float* a, const float* b, int b_layout, const flo
             MAM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             TimedLaunch t(MAM_KERNEL_BWD, cs);
             kern<<<(unsigned)grid, BWD_THREADS, smem, cs>>>(a, b, grad, argmax, argmin, da, dw_dst, M, K, N, rows, scale,
-                                                            ConvGeom{});
+                                                            ConvGeom{}, slices);
             return MAM_OK;
         };
         const bool nk = b_layout == MAM_B_NK, km = da_layout == MAM_DA_KM;
@@ -798,7 +854,7 @@ int mam_bwd_count_ws_f32(const float* a, const float* b, int b_layout, const flo
     }
     MAM_CUDA(cudaGetLastError());
     if (fused) return unpack();
-    if (count) return mam_selcount_i32(argmax, argmin, hit_max, hit_min, M, K, N, stream);
+    if (count) return mam_selcount_i32(argmax, argmin, hit_max, hit_min, M * slices, K, N, stream);
     return MAM_OK;
 }
 
@@ -868,7 +924,7 @@ int mam_conv_bwd_f32(const float* x, const float* w, const float* grad, const in
     {
         TimedLaunch t(MAM_KERNEL_BWD, cs);
         mam_bwd_kernel<true, true, true><<<(unsigned)grid, BWD_THREADS, smem, cs>>>(x, w, grad, argmax, argmin, cols_t,
-                                                                                     dw, M, K, N, rows, scale, g);
+                                                                                     dw, M, K, N, rows, scale, g, 1);
     }
     MAM_CUDA(cudaGetLastError());
     return MAM_OK;
@@ -1295,20 +1351,20 @@ int mam_spmm_csr_ws_f32(const int64_t* crow, const int64_t* col, const float* va
 int mam_spmm_csr_f32(const int64_t* crow, const int64_t* col, const float* val, const float* b, float* c, int64_t N,
                      int64_t K, int64_t Mc, void* stream) {
     if (bad_ptr(crow) || bad_ptr(b) || bad_ptr(c) || N <= 0 || K <= 0 || Mc <= 0) return MAM_ERR_INVALID_ARGUMENT;
-    if (N > 65535) {
-        // grid.y limit: process row blocks
-        for (int64_t n0 = 0; n0 < N; n0 += 65535) {
-            const int64_t nn = N - n0 < 65535 ? N - n0 : 65535;
-            dim3 grid((unsigned)((Mc + 127) / 128), (unsigned)nn);
+    // four columns per thread where rows of b and c can be read and written 16 bytes at a time
+    const bool v4 = Mc % 4 == 0 && aligned16(b) && aligned16(c);
+    const long long per_cta = v4 ? 512 : 128;
+    for (int64_t n0 = 0; n0 < N; n0 += 65535) {   // grid.y limit: row blocks
+        const int64_t nn = N - n0 < 65535 ? N - n0 : 65535;
+        dim3 grid((unsigned)((Mc + per_cta - 1) / per_cta), (unsigned)nn);
+        if (v4)
+            mam_spmm_csr_v4_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(
+                reinterpret_cast<const long long*>(crow) + n0, reinterpret_cast<const long long*>(col), val, b,
+                c + n0 * Mc, nn, Mc);
+        else
             mam_spmm_csr_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(
                 reinterpret_cast<const long long*>(crow) + n0, reinterpret_cast<const long long*>(col), val, b,
                 c + n0 * Mc, nn, Mc);
-        }
-    } else {
-        dim3 grid((unsigned)((Mc + 127) / 128), (unsigned)N);
-        mam_spmm_csr_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(reinterpret_cast<const long long*>(crow),
-                                                                    reinterpret_cast<const long long*>(col), val, b, c,
-                                                                    N, Mc);
     }
     MAM_CUDA(cudaGetLastError());
     return MAM_OK;

@@ -159,4 +159,46 @@ mam_spmm_csr_kernel(const long long* __restrict__ crow, const long long* __restr
     c[n * Mc + j] = acc;
 }
 
+// The same product, four columns per thread (B and C rows 16-byte aligned, Mc % 4 == 0) and four stored entries
+// in flight: every row of B a stored entry names is fetched with 16-byte loads, 2 KB per CTA and entry, and the
+// four fetches are issued before the first is used.  The additions stay in ascending column order, so the sums
+// are the ones of the kernel above bit for bit.  This is the form for very sparse operands, where the product
+// is bound by the L2 traffic of the gathered B rows (nnz * Mc * 4 bytes) and nothing is there to reuse.
+__global__ void __launch_bounds__(128)
+mam_spmm_csr_v4_kernel(const long long* __restrict__ crow, const long long* __restrict__ col,
+                       const float* __restrict__ val, const float* __restrict__ b, float* __restrict__ c,
+                       long long N, long long Mc) {
+    const long long n = blockIdx.y;
+    const long long j = ((long long)blockIdx.x * 128 + threadIdx.x) * 4;
+    if (n >= N || j >= Mc) return;
+    const long long s = crow[n], e = crow[n + 1];
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    long long t = s;
+    for (; t + 4 <= e; t += 4) {
+        float v[4];
+        float4 x[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            v[u] = val[t + u];
+            x[u] = *reinterpret_cast<const float4*>(b + col[t + u] * Mc + j);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            acc.x = fmaf(v[u], x[u].x, acc.x);
+            acc.y = fmaf(v[u], x[u].y, acc.y);
+            acc.z = fmaf(v[u], x[u].z, acc.z);
+            acc.w = fmaf(v[u], x[u].w, acc.w);
+        }
+    }
+    for (; t < e; ++t) {
+        const float v = val[t];
+        const float4 x = *reinterpret_cast<const float4*>(b + col[t] * Mc + j);
+        acc.x = fmaf(v, x.x, acc.x);
+        acc.y = fmaf(v, x.y, acc.y);
+        acc.z = fmaf(v, x.z, acc.z);
+        acc.w = fmaf(v, x.w, acc.w);
+    }
+    *reinterpret_cast<float4*>(c + n * Mc + j) = acc;
+}
+
 }  // namespace mamb200

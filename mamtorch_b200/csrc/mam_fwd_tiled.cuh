@@ -36,8 +36,9 @@ template <int TM_, int TN_, int WM_, int WN_, int STAGES_, bool TRACK_, int UQ_ 
 struct FwdCfg {
     // K cut into slices of prm.split_chunks chunks: y = sum over slices of (max + min) of the slice, added in
     // ascending slice order -- the module's `splits` (mamtorch/nn/v4/fullyconnected.py:164-176) in one launch
+    // With TRACK the slices' partial sums are banked in y itself (there is no room for a third accumulator set)
+    // and every slice leaves its own chunk ids: prm.cid_max holds one [M,N] matrix per slice.
     static constexpr bool SPLIT = SPLIT_;
-    static_assert(!(SPLIT_ && TRACK_), "slices are summed in the values-only kernel");
     static constexpr bool MUL2 = MUL2_;     // packed mul.rn.f32x2 (true) or four scalar multiplies
     static constexpr int UQ = UQ_;          // 16-byte k groups per unrolled loop body
     static constexpr bool BATCH = BATCH_;   // form all products of a W row before any max/min
@@ -251,28 +252,58 @@ mam_fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
             }
         }
 
-        float ysum[Cfg::SPLIT ? TM : 1][Cfg::SPLIT ? TN : 1];
+        float ysum[(Cfg::SPLIT && !TRACK) ? TM : 1][(Cfg::SPLIT && !TRACK) ? TN : 1];
         int next_split = prm.split_chunks;
-        if constexpr (Cfg::SPLIT) {
+        if constexpr (Cfg::SPLIT && !TRACK) {
 #pragma unroll
             for (int i = 0; i < TM; ++i)
 #pragma unroll
                 for (int j = 0; j < TN; ++j) ysum[i][j] = 0.f;
         }
+        [[maybe_unused]] int slice_base = 0;   // first chunk of the current slice (TRACK: ids are slice-relative)
         for (int kc = 0; kc < nk; ++kc) {
             if constexpr (Cfg::SPLIT) {
                 if (kc == next_split) {   // a slice of K ends: bank its max + min, start the next one
                     next_split += prm.split_chunks;
+                    if constexpr (TRACK) {
+                        const long long slice = kc / prm.split_chunks - 1;   // the slice that just ended
+                        const long long mrow0 = (long long)tm * Cfg::BM + wm * 4 * TM + lane_m;
+                        const long long ncol0 = (long long)tn * Cfg::BN + wn * 8 * TN + lane_n;
+                        slice_base = kc;
 #pragma unroll
-                    for (int i = 0; i < TM; ++i)
+                        for (int i = 0; i < TM; ++i)
 #pragma unroll
-                        for (int j = 0; j < TN; ++j) {
-                            const float t = __fadd_rn(vmax[i][j], vmin[i][j]);
-                            // the first slice stands alone (0 + t would turn -0 into +0)
-                            ysum[i][j] = (kc == prm.split_chunks) ? t : __fadd_rn(ysum[i][j], t);
-                            vmax[i][j] = -INFINITY;
-                            vmin[i][j] = INFINITY;
-                        }
+                            for (int j = 0; j < TN; ++j) {
+                                const long long m = mrow0 + i * 4, n = ncol0 + j * 8;
+                                const uint32_t amax = id_addr + (uint32_t)(((i * TN + j) * 2 + 0) * Cfg::CONSUMERS * 2);
+                                const uint32_t amin = id_addr + (uint32_t)(((i * TN + j) * 2 + 1) * Cfg::CONSUMERS * 2);
+                                if (m < M && n < N) {
+                                    const float t = __fadd_rn(vmax[i][j], vmin[i][j]);
+                                    float* yp = prm.y + m * N + n;
+                                    // the first slice stands alone (0 + t would turn -0 into +0)
+                                    *yp = slice == 0 ? t : __fadd_rn(*yp, t);
+                                    unsigned short cmax, cmin;
+                                    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(cmax) : "r"(amax) : "memory");
+                                    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(cmin) : "r"(amin) : "memory");
+                                    prm.cid_max[slice * M * N + m * N + n] = (int)((unsigned)cmax | ((unsigned)cmin << 16));
+                                }
+                                asm volatile("st.shared.u16 [%0], %1;" ::"r"(amax), "h"((unsigned short)0) : "memory");
+                                asm volatile("st.shared.u16 [%0], %1;" ::"r"(amin), "h"((unsigned short)0) : "memory");
+                                vmax[i][j] = -INFINITY;
+                                vmin[i][j] = INFINITY;
+                            }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < TM; ++i)
+#pragma unroll
+                            for (int j = 0; j < TN; ++j) {
+                                const float t = __fadd_rn(vmax[i][j], vmin[i][j]);
+                                // the first slice stands alone (0 + t would turn -0 into +0)
+                                ysum[i][j] = (kc == prm.split_chunks) ? t : __fadd_rn(ysum[i][j], t);
+                                vmax[i][j] = -INFINITY;
+                                vmin[i][j] = INFINITY;
+                            }
+                    }
                 }
             }
             if (tid == 0 && !produce_one()) atomicExch(prm.error, 1);
@@ -357,7 +388,7 @@ mam_fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                 // merge the chunk extremes into the running ones; one ALU compare per accumulator.
                 // The value move is a multiply by an opaque 1.0 (exact for every input, keeps the
                 // sign of zero) so that it issues on the FMA pipe rather than the saturated ALU pipe.
-                const unsigned short kid = (unsigned short)kc;
+                const unsigned short kid = (unsigned short)(Cfg::SPLIT ? kc - slice_base : kc);
                 static_for<0, TM * TN>([&](auto slot) {
                     constexpr int S = decltype(slot)::value;
                     constexpr int i = S / TN, j = S % TN;
@@ -394,7 +425,10 @@ mam_fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
             for (int j = 0; j < TN; ++j) {
                 const long long n = ncol0 + j * 8;
                 if (n >= N) continue;
-                if constexpr (Cfg::SPLIT)
+                if constexpr (Cfg::SPLIT && TRACK)   // the earlier slices' sum waits in y
+                    prm.y[m * N + n] = mam_epilogue_term(
+                        __fadd_rn(prm.y[m * N + n], __fadd_rn(vmax[i][j], vmin[i][j])), prm.ep, m, n, N);
+                else if constexpr (Cfg::SPLIT)
                     prm.y[m * N + n] = mam_epilogue_term(
                         __fadd_rn(ysum[i][j], __fadd_rn(vmax[i][j], vmin[i][j])), prm.ep, m, n, N);
                 else
@@ -406,7 +440,8 @@ mam_fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                     asm volatile("ld.shared.u16 %0, [%1];" : "=h"(cmax) : "r"(amax) : "memory");
                     asm volatile("ld.shared.u16 %0, [%1];" : "=h"(cmin) : "r"(amin) : "memory");
                     // both chunk ids in one word (K / 32 < 65535): the resolver reads half as much
-                    prm.cid_max[m * N + n] = (int)((unsigned)cmax | ((unsigned)cmin << 16));
+                    const long long last_slice = Cfg::SPLIT ? (long long)((nk - 1) / prm.split_chunks) : 0;
+                    prm.cid_max[last_slice * M * N + m * N + n] = (int)((unsigned)cmax | ((unsigned)cmin << 16));
                 }
             }
         }
@@ -453,7 +488,7 @@ template <bool CONV>
 __global__ void __launch_bounds__(ResolveCfg::THREADS, 2)
 mam_resolve_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW,
                          int* __restrict__ argmax, int* __restrict__ argmin,
-                         long long M, long long K, long long N, int* error, const Im2colRows conv) {
+                         long long M, long long K, long long N, int* error, const Im2colRows conv, int k_offset) {
     using C = ResolveCfg;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(
@@ -677,7 +712,9 @@ mam_resolve_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
             if (p2 == best) e = 2;
             if (p1 == best) e = 1;
             if (p0 == best) e = 0;
-            const int kbest = CONV ? kout0 + (bq * 4 + e) * kout_step : kout0 + bq * 4 + e;
+            // k_offset: the problem is a slice of a wider K (slices of the module's `splits`); indices leave
+            // in the numbering of the whole row
+            const int kbest = CONV ? kout0 + (bq * 4 + e) * kout_step : kout0 + bq * 4 + e + k_offset;
             const long long m = m0 + ra, n = n0 + rw;
             if (code & 1u) argmin[m * N + n] = kbest; else argmax[m * N + n] = kbest;
         }

@@ -321,6 +321,75 @@ at::Tensor linear_forward_splits(const at::Tensor& x, const at::Tensor& weight, 
     check_status(st, "mam_fwd_splits_f32");
     return y;
 }
+// {y[M,N], argmax[S,M,N], argmin[S,M,N]} with K cut into S slices of split_width columns, every slice keeping its
+// own selected pairs (indices in the numbering of the whole row); {} (no tensors) where the single-launch form
+// does not apply and the caller goes slice by slice
+std::vector<at::Tensor> linear_forward_splits_idx(const at::Tensor& x, const at::Tensor& weight,
+                                                  const c10::optional<at::Tensor>& bias,
+                                                  const c10::optional<at::Tensor>& dense_t, double alpha, double beta,
+                                                  int64_t split_width) {
+    check_matrix(x, "x");
+    check_matrix(weight, "weight");
+    const int64_t M = x.size(0), K = x.size(1), N = weight.size(0);
+    TORCH_CHECK(weight.size(1) == K, "weight must be [N, K]");
+    TORCH_CHECK(split_width > 0, "split_width must be positive");
+    const float* bias_p = nullptr;
+    const float* dense_p = nullptr;
+    at::Tensor bias_c;
+    if (bias.has_value() && bias->defined()) {
+        TORCH_CHECK(bias->is_cuda() && bias->scalar_type() == at::kFloat && bias->numel() == N, "bias must be float32 [N]");
+        bias_c = bias->contiguous();
+        bias_p = bias_c.data_ptr<float>();
+    }
+    if (dense_t.has_value() && dense_t->defined()) {
+        check_matrix(*dense_t, "dense");
+        TORCH_CHECK(dense_t->size(0) == M && dense_t->size(1) == N, "dense must be [M, N]");
+        dense_p = dense_t->data_ptr<float>();
+    }
+    c10::cuda::CUDAGuard guard(x.device());
+    if (M == 0 || N == 0 || K == 0) return {};
+    const int64_t S = (K + split_width - 1) / split_width;
+    auto y = at::empty({M, N}, x.options());
+    auto amax = at::empty({S, M, N}, x.options().dtype(at::kInt));
+    auto amin = at::empty({S, M, N}, x.options().dtype(at::kInt));
+    const bool blend = !(alpha == 1.0 && beta == 0.0);
+    auto stream = at::cuda::getCurrentCUDAStream();
+    const int st = mam_fwd_splits_idx_f32(x.data_ptr<float>(), weight.data_ptr<float>(), bias_p, dense_p, blend ? 1 : 0,
+                                          (float)alpha, (float)beta, y.data_ptr<float>(), amax.data_ptr<int32_t>(),
+                                          amin.data_ptr<int32_t>(), M, K, N, split_width, stream.stream());
+    if (st == MAM_ERR_UNSUPPORTED) return {};
+    check_status(st, "mam_fwd_splits_idx_f32");
+    return {y, amax, amin};
+}
+// {dx, dw} through the selected pairs of every slice (argmax / argmin [S,M,N])
+std::vector<at::Tensor> linear_backward_splits(const at::Tensor& x, const at::Tensor& weight, const at::Tensor& grad,
+                                               const at::Tensor& argmax, const at::Tensor& argmin, double scale) {
+    check_matrix(x, "x");
+    check_matrix(weight, "weight");
+    check_matrix(grad, "grad");
+    TORCH_CHECK(argmax.is_cuda() && argmax.dim() == 3 && argmax.scalar_type() == at::kInt && argmax.is_contiguous(),
+                "argmax must be a contiguous int32 CUDA [S,M,N] tensor");
+    TORCH_CHECK(argmin.sizes() == argmax.sizes() && argmin.scalar_type() == at::kInt && argmin.is_contiguous(),
+                "argmin must match argmax");
+    const int64_t M = x.size(0), K = x.size(1), N = weight.size(0), S = argmax.size(0);
+    TORCH_CHECK(weight.size(1) == K && grad.size(0) == M && grad.size(1) == N, "shape mismatch");
+    TORCH_CHECK(argmax.size(1) == M && argmax.size(2) == N && S >= 1, "index shapes must be [S,M,N]");
+    c10::cuda::CUDAGuard guard(x.device());
+    auto da = at::empty_like(x);
+    auto dw = at::empty_like(weight);
+    if (M == 0 || N == 0 || K == 0) {
+        da.zero_();
+        dw.zero_();
+        return {da, dw};
+    }
+    auto stream = at::cuda::getCurrentCUDAStream();
+    check_status(mam_bwd_splits_f32(x.data_ptr<float>(), weight.data_ptr<float>(), MAM_B_NK, grad.data_ptr<float>(),
+                                    argmax.data_ptr<int32_t>(), argmin.data_ptr<int32_t>(), (int)S, da.data_ptr<float>(),
+                                    MAM_DA_MK, dw.data_ptr<float>(), nullptr, nullptr, (float)scale, M, K, N, nullptr, 0,
+                                    stream.stream()),
+                 "mam_bwd_splits_f32");
+    return {da, dw};
+}
 std::vector<at::Tensor> linear_backward(const at::Tensor& x, const at::Tensor& weight, const at::Tensor& grad,
                                         const at::Tensor& argmax, const at::Tensor& argmin, double scale) {
     return backward_impl(x, weight, MAM_B_NK, grad, argmax, argmin, scale);
@@ -629,17 +698,13 @@ std::vector<at::Tensor> csr_linear_forward_ws(const at::Tensor& x, const at::Ten
     return {y, amax, amin};
 }
 
-// cusparsemm(a_sparse[N,K], b[K,M]) -> dense [N,M]
-at::Tensor spmm_csr(const at::Tensor& a, const at::Tensor& b) {
-    TORCH_CHECK(b.is_cuda() && b.dim() == 2 && b.scalar_type() == at::kFloat, "b must be a 2-D float CUDA tensor");
-    TORCH_CHECK(a.dim() == 2 && a.size(1) == b.size(0), "inner dimensions differ");
+// c[N,Mc] = A . b for A given by its CSR components
+at::Tensor spmm_components(const at::Tensor& crow, const at::Tensor& col, const at::Tensor& val, int64_t N, int64_t K,
+                           const at::Tensor& b) {
     c10::cuda::CUDAGuard guard(b.device());
-    const int64_t N = a.size(0), K = a.size(1), Mc = b.size(1);
+    const int64_t Mc = b.size(1);
     auto c = at::zeros({N, Mc}, b.options());
     if (N == 0 || Mc == 0 || K == 0) return c;
-    auto crow = a.crow_indices().to(at::kLong).contiguous();
-    auto col = a.col_indices().to(at::kLong).contiguous();
-    auto val = a.values().to(at::kFloat).contiguous();
     if (val.numel() == 0) return c;
     auto bc = b.contiguous();
     auto stream = at::cuda::getCurrentCUDAStream();
@@ -653,7 +718,25 @@ at::Tensor spmm_csr(const at::Tensor& a, const at::Tensor& b) {
                  "mam_spmm_csr_ws_f32");
     return c;
 }
-at::Tensor spmm_coo(const at::Tensor& a, const at::Tensor& b) { return spmm_csr(a.to_sparse_csr(), b); }
+// cusparsemm(a_sparse[N,K], b[K,M]) -> dense [N,M], a in CSR layout
+at::Tensor spmm_csr(const at::Tensor& a, const at::Tensor& b) {
+    TORCH_CHECK(b.is_cuda() && b.dim() == 2 && b.scalar_type() == at::kFloat, "b must be a 2-D float CUDA tensor");
+    TORCH_CHECK(a.dim() == 2 && a.size(1) == b.size(0), "inner dimensions differ");
+    return spmm_components(a.crow_indices().to(at::kLong).contiguous(), a.col_indices().to(at::kLong).contiguous(),
+                           a.values().to(at::kFloat).contiguous(), a.size(0), a.size(1), b);
+}
+// The same for a COO operand.  A coalesced COO tensor keeps its entries sorted by (row, column), which is CSR
+// order already: the column indices and the values are used where they are and only the N+1 row offsets are
+// formed (one small kernel), instead of converting the whole tensor on every call.
+at::Tensor spmm_coo(const at::Tensor& a, const at::Tensor& b) {
+    TORCH_CHECK(b.is_cuda() && b.dim() == 2 && b.scalar_type() == at::kFloat, "b must be a 2-D float CUDA tensor");
+    TORCH_CHECK(a.dim() == 2 && a.size(1) == b.size(0), "inner dimensions differ");
+    if (!a.is_coalesced() || a.sparse_dim() != 2 || a.dense_dim() != 0) return spmm_csr(a.to_sparse_csr(), b);
+    auto idx = a._indices();                                   // [2, nnz] int64
+    auto crow = at::_convert_indices_from_coo_to_csr(idx.select(0, 0).contiguous(), a.size(0), /*out_int32=*/false);
+    return spmm_components(crow, idx.select(0, 1).contiguous(), a._values().to(at::kFloat).contiguous(), a.size(0),
+                           a.size(1), b);
+}
 
 }  // namespace
 
@@ -736,6 +819,8 @@ TORCH_LIBRARY(mamtorch_b200, m) {
     m.def("conv_backward_direct(Tensor x, Tensor weight, Tensor grad, Tensor argmax, Tensor argmin, float scale, int kH, int kW, int sh, int sw, int ph, int pw) -> Tensor[]");
     m.def("conv_direct_applies(int B, int C, int H, int W, int kH, int kW, int sh, int sw, int ph, int pw) -> bool", &conv_direct_applies);
     m.def("linear_forward_splits(Tensor x, Tensor weight, Tensor? bias, Tensor? dense, float alpha, float beta, int split_width) -> Tensor");
+    m.def("linear_forward_splits_idx(Tensor x, Tensor weight, Tensor? bias, Tensor? dense, float alpha, float beta, int split_width) -> Tensor[]");
+    m.def("linear_backward_splits(Tensor x, Tensor weight, Tensor grad, Tensor argmax, Tensor argmin, float scale) -> Tensor[]");
     m.def("conv_channels_last(Tensor x) -> Tensor");
     m.def("conv_forward_implicit(Tensor x_nhwc, Tensor w_taps, Tensor? bias, Tensor? dense, float alpha, float beta, int kH, int kW, int sh, int sw, int ph, int pw, bool need_indices) -> Tensor[]");
     m.def("conv_implicit_applies(int B, int C, int H, int W, int kH, int kW, int sh, int sw, int ph, int pw) -> bool", &conv_implicit_applies);
@@ -764,6 +849,8 @@ TORCH_LIBRARY_IMPL(mamtorch_b200, CUDA, m) {
     m.impl("conv_forward_implicit", &conv_forward_implicit);
     m.impl("conv_channels_last", &conv_channels_last);
     m.impl("linear_forward_splits", &linear_forward_splits);
+    m.impl("linear_forward_splits_idx", &linear_forward_splits_idx);
+    m.impl("linear_backward_splits", &linear_backward_splits);
     m.impl("conv_col2im", &conv_col2im);
     m.impl("selection_hits", &selection_hits);
     m.impl("selection_count_update_", &selection_count_update_);

@@ -68,6 +68,18 @@ def _(x, crow, col, val, bias, want_idx, workspace, entries_ready):
     return [y, y.new_empty(y.shape, dtype=torch.int32), y.new_empty(y.shape, dtype=torch.int32)]
 
 
+@torch.library.register_fake("mamtorch_b200::linear_forward_splits_idx")
+def _(x, weight, bias, dense, alpha, beta, split_width):
+    M, K, N = x.size(0), x.size(1), weight.size(0)
+    S = (K + split_width - 1) // split_width
+    return [x.new_empty((M, N)), x.new_empty((S, M, N), dtype=torch.int), x.new_empty((S, M, N), dtype=torch.int)]
+
+
+@torch.library.register_fake("mamtorch_b200::linear_backward_splits")
+def _(x, weight, grad, argmax, argmin, scale):
+    return [torch.empty_like(x), torch.empty_like(weight)]
+
+
 @torch.library.register_fake("mamtorch_b200::linear_forward_splits")
 def _(x, weight, bias, dense, alpha, beta, split_width):
     return x.new_empty((x.size(0), weight.size(0)))
@@ -287,6 +299,52 @@ def mam_linear(x: Tensor, weight: Tensor, bias: Tensor | None = None, dense: Ten
     else:
         y, = _ops.linear_forward(x, weight, bias, dense, float(alpha), float(beta), False)
     return y, None, None
+
+
+class _MamLinearSplits(torch.autograd.Function):
+    """The module's `splits` in training: y = alpha * sum over K slices of (max + min of the slice) + beta*dense + bias
+    from ONE launch of the index-producing forward (plus one index resolver per slice), every slice keeping its
+    own selected pairs; the backward routes the gradient through all of them in one pass."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, dense, alpha, beta, split_width):
+        out = _ops.linear_forward_splits_idx(x, weight, bias, dense, alpha, beta, split_width)
+        if len(out) == 0:
+            raise _SplitsUnsupported()
+        y, argmax, argmin = out
+        ctx.save_for_backward(x, weight, argmax, argmin)
+        ctx.alpha, ctx.beta = alpha, beta
+        ctx.has_bias, ctx.has_dense = bias is not None, dense is not None
+        return y
+
+    @staticmethod
+    def backward(ctx, gy):
+        x, weight, argmax, argmin = ctx.saved_tensors
+        gy = gy.contiguous()
+        dx = dw = dbias = ddense = None
+        if ctx.needs_input_grad[0] or ctx.needs_input_grad[1]:
+            dx, dw = _ops.linear_backward_splits(x, weight, gy, argmax, argmin, ctx.alpha)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            dbias = gy.sum(0)
+        if ctx.has_dense and ctx.needs_input_grad[3]:
+            ddense = gy * ctx.beta
+        return dx, dw, dbias, ddense, None, None, None
+
+
+class _SplitsUnsupported(Exception):
+    pass
+
+
+def mam_linear_splits(x: Tensor, weight: Tensor, split_width: int, bias: Tensor | None = None,
+                      dense: Tensor | None = None, alpha: float = 1.0, beta: float = 0.0):
+    """Differentiable MAM layer with K cut into slices of `split_width` columns, all slices in one launch.
+    Returns None where that form does not apply (slice width not a multiple of 32, K % 4 != 0, unaligned
+    operands): the caller then goes slice by slice."""
+    try:
+        return _MamLinearSplits.apply(x.contiguous(), weight.contiguous(), bias, dense, float(alpha), float(beta),
+                                      int(split_width))
+    except _SplitsUnsupported:
+        return None
 
 
 def selection_hits(argmax: Tensor, argmin: Tensor, in_features: int):

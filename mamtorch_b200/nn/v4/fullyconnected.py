@@ -160,6 +160,17 @@ class FullyConnected(Module):
                     if self.drop_rate > 0:
                         y = F.dropout(y, self.drop_rate, self.training)
                     return y
+            elif self.in_subfeatures * (self.splits - 1) < self.in_features:
+                # training: all slices in one launch of the index-producing forward, one backward pass over all
+                # of them (same restrictions on the slice width)
+                y = MF.mam_linear_splits(x, w, self.in_subfeatures, self.bias, dense,
+                                         self.alpha if dense is not None else 1.0,
+                                         self.beta if dense is not None else 0.0)
+                if y is not None:
+                    y = y.view(input.shape[:-1] + (self.out_features,))
+                    if self.drop_rate > 0:
+                        y = F.dropout(y, self.drop_rate, self.training)
+                    return y
             bounds = [(i * self.in_subfeatures, self.in_subfeatures) for i in range(self.splits - 1)]
             bounds.append((self.in_features - self.in_subfeatures_last, self.in_subfeatures_last))
             for start, width in bounds:

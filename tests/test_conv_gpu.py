@@ -312,3 +312,36 @@ def test_channels_last_copy(shape, cuda):
     assert copy.data_ptr() != xcl.data_ptr() and torch.equal(copy, out)
     assert xcl.permute(0, 2, 3, 1).is_contiguous()
     torch.library.opcheck(torch.ops.mamtorch_b200.conv_channels_last, (xcl,))
+
+
+def test_conv1d_without_patch_rows(cuda):
+    """MAMConv1d with reduction_order="taps" and a channel count that is a multiple of 32: a convolution of height
+    one through the im2col-mode TMA path (no patch rows), against the oracle in tap order, forward and backward,
+    and against the patch-row module where no extreme is tied."""
+    import mamtorch_b200 as mamtorch
+
+    B, C, Lx, Fo, k = 12, 64, 700, 40, 5
+    assert _lib.lib().mam_conv_fwd_applies(B, C, 1, Lx, 1, k, 1, 1, 0, 2) == 1
+    torch.manual_seed(3)
+    taps = mamtorch.nn.MAMConv1d(C, Fo, k, padding=2, reduction_order="taps").to(cuda)
+    rows = mamtorch.nn.MAMConv1d(C, Fo, k, padding=2).to(cuda)
+    rows.load_state_dict(taps.state_dict())
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(B, C, Lx, generator=g).to(cuda)
+    gy = torch.randn(B, Fo, Lx, generator=g).to(cuda)
+    xa, xb = x.clone().requires_grad_(), x.clone().requires_grad_()
+    ya, yb = taps(xa), rows(xb)
+    torch.cuda.synchronize()
+    assert capi.device_flag_ok()
+    geom = (B, C, 1, Lx, 1, k, 1, 1, 0, 2, Fo)
+    y_ref, imax_ref, imin_ref = _tap_order_oracle(x.cpu().unsqueeze(2), taps.weight.detach().cpu().unsqueeze(2), geom)
+    y_ref = y_ref + taps.bias.detach().cpu()
+    flat = lambda t: t.permute(0, 2, 1).reshape(-1, Fo)
+    assert torch.equal(flat(ya.detach()).cpu(), y_ref)
+    assert torch.equal(flat(taps.argmax).cpu().long(), imax_ref) and torch.equal(flat(taps.argmin).cpu().long(), imin_ref)
+    assert torch.equal(ya, yb)                                  # values do not depend on the reduction order
+    assert torch.equal(taps.argmax, rows.argmax)                # random data: no ties, so neither do the indices
+    ya.backward(gy)
+    yb.backward(gy)
+    assert_grad_close(xa.grad.cpu().numpy(), xb.grad.cpu().numpy())
+    assert_grad_close(taps.weight.grad.cpu().numpy(), rows.weight.grad.cpu().numpy())

@@ -490,3 +490,66 @@ def test_module_weight_drop_and_output_dropout(cuda):
     yg.backward(torch.ones_like(yg))
     assert torch.equal(yg, y1) and xg.grad.shape == x.shape and layer.weight.grad.shape == layer.weight.shape
     assert float(layer.bias.grad.min()) >= 0 and abs(float(layer.bias.grad.sum()) - float((y1 != 0).sum()) / 0.6) < 1.0
+
+
+@pytest.mark.parametrize("shape,splits", [((200, 256, 130), 2), ((300, 768, 200), 4), ((70, 160, 66), 3), ((129, 96, 40), 2)])
+def test_training_splits_in_one_launch(shape, splits, cuda):
+    """`splits` in training: every slice of K contributes its own max + min and routes gradients through its own
+    selected pairs (mamtorch/nn/v4/fullyconnected.py:164-176).  One launch for all slices must equal the
+    slice-by-slice composition: values and per-slice indices bit for bit (against the oracle on each slice),
+    gradients to rounding.  (160 / 3 -> slices of 54: not a multiple of 32, the module goes slice by slice.)"""
+    import math
+
+    import mamtorch_b200 as mamtorch
+    from mamtorch_b200.nn import functional as MF
+
+    M, K, N = shape
+    width = math.ceil(K / splits)
+    x, w, bias = _rand((M, K), 40, cuda), _rand((N, K), 41, cuda, K ** -0.5), _rand((N,), 42, cuda)
+    gy = _rand((M, N), 43, cuda)
+    # oracle: slice by slice
+    y_ref = torch.zeros(M, N)
+    idx_ref = []
+    for s0 in range(0, K, width):
+        ys, imax, imin = mam_oracle.mam_forward(x[:, s0:s0 + width].cpu(), w[:, s0:s0 + width].T.contiguous().cpu())
+        y_ref = ys if s0 == 0 else y_ref + ys
+        idx_ref.append((imax + s0, imin + s0))
+    y_ref = y_ref + bias.cpu()
+    out = torch.ops.mamtorch_b200.linear_forward_splits_idx(x, w, bias, None, 1.0, 0.0, width)
+    if width % 32 == 0:
+        y, amax, amin = out
+        assert amax.shape == (len(idx_ref), M, N)
+        assert torch.equal(y.cpu(), y_ref)
+        for s, (imax, imin) in enumerate(idx_ref):
+            assert torch.equal(amax[s].cpu().long(), imax) and torch.equal(amin[s].cpu().long(), imin)
+        da, dw = torch.ops.mamtorch_b200.linear_backward_splits(x, w, gy, amax, amin, 1.0)
+        da_ref = torch.zeros(M, K, dtype=torch.float64)
+        dw_ref = torch.zeros(N, K, dtype=torch.float64)
+        for imax, imin in idx_ref:
+            a_, b_ = mam_oracle.mam_backward(x.cpu(), w.T.contiguous().cpu(), gy.cpu(), imax, imin)
+            da_ref += a_.double()
+            dw_ref += b_.T.double()
+        assert_grad_close(da.cpu().numpy(), da_ref.numpy())
+        assert_grad_close(dw.cpu().numpy(), dw_ref.numpy())
+    else:
+        assert len(out) == 0 and MF.mam_linear_splits(x, w, width, bias) is None
+    # the module, in training mode, whichever route it takes
+    torch.manual_seed(1)
+    layer = mamtorch.nn.FullyConnected(K, N, splits=splits).to(cuda).train()
+    with torch.no_grad():
+        layer.weight.copy_(w)
+        layer.bias.copy_(bias)
+    xg = x.clone().requires_grad_()
+    ym = layer(xg)
+    ym.backward(gy)
+    assert torch.allclose(ym.detach().cpu(), y_ref, rtol=1e-6, atol=1e-6) if width % 32 else torch.equal(ym.detach().cpu(), y_ref)
+    da_ref = torch.zeros(M, K, dtype=torch.float64)
+    dw_ref = torch.zeros(N, K, dtype=torch.float64)
+    for imax, imin in idx_ref:
+        a_, b_ = mam_oracle.mam_backward(x.cpu(), w.T.contiguous().cpu(), gy.cpu(), imax, imin)
+        da_ref += a_.double()
+        dw_ref += b_.T.double()
+    assert_grad_close(xg.grad.cpu().numpy(), da_ref.numpy())
+    assert_grad_close(layer.weight.grad.cpu().numpy(), dw_ref.numpy())
+    assert_grad_close(layer.bias.grad.cpu().numpy(), gy.sum(0).cpu().numpy())
+    torch.ops.mamtorch_b200.check_device_flag()
