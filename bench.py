@@ -788,6 +788,10 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference", "reference_cuda"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-other-configs", action="store_true", help="headline workload only")
+    ap.add_argument("--grad-sync", default="hooks", choices=["hooks", "deferred", "serial"],
+                    help="N > 1: all-reduce each weight gradient from its hook while the backward runs on (hooks, "
+                         "default: measured best), all of them asynchronously right after the backward, under the "
+                         "selection-count kernels (deferred), or after the whole step (serial)")
     ap.add_argument("--fwd-variant", type=int, default=-1, help="tile configuration of the index-producing forward")
     ap.add_argument("--workload", default="vit_mlp", choices=["vit_mlp", "sharded_sparse"],
                     help="vit_mlp: the headline configuration (default); sharded_sparse: the large pruned layer, "
@@ -846,7 +850,7 @@ def main():
     params = [fc1.weight, fc2.weight, fc1.bias, fc2.bias]
     # N > 1: every parameter's gradient is all-reduced in place from a hook that fires as soon as autograd has
     # accumulated it, on NCCL's own stream; finish() makes the compute stream wait for the collectives
-    sync = OverlappedGradSync(params) if world > 1 else None
+    sync = OverlappedGradSync(params, deferred=args.grad_sync != "hooks") if world > 1 else None
 
     def step(x, gy):
         for p in params:
@@ -854,6 +858,8 @@ def main():
         x = x.detach().requires_grad_()   # a fresh leaf every step: dX is produced, never accumulated
         y = fc2(fc1(x))
         y.backward(gy)
+        if sync is not None and args.grad_sync == "deferred":
+            sync.start()
         fc1.update_selection_count()
         fc2.update_selection_count()
         if sync is not None:
@@ -978,7 +984,7 @@ def main():
     peaks = fp32_peaks(sms, max_mhz)
     achieved = flops_per_launch / (kavg * 1e-3) / 1e12
     roofline = {"bound": "fp32_cuda_core", "kernel": "mam_fwd_tiled_kernel (index-tracking variant "
-                + L.mam_fwd_variant_name(1, args.fwd_variant if args.fwd_variant >= 0 else 1).decode() + ")",
+                + L.mam_fwd_variant_name(1, args.fwd_variant if args.fwd_variant >= 0 else 2).decode() + ")",
                 "achieved": achieved, "peak": peaks["fma_counted_tflops"], "unit": "TFLOP/s",
                 "frac": achieved / peaks["fma_counted_tflops"],
                 "peak_source": f"{sms} SMs x 128 lanes x 2 x {max_mhz:.0f} MHz (FMA counted as 2; no fp32 entry in "

@@ -53,14 +53,15 @@ mam_bwd_unpack_kernel(const float4* __restrict__ acc, float* __restrict__ dw, in
 // CONV: a is not a matrix of patch rows but the convolution input x[B,C,H,W] itself; row m is output
 // pixel (b, ho, wo) and a[m][k] is read where the patch element k = (c*kH+kh)*kW+kw lives in x (zero
 // in the padding), so the patch rows need not be kept for the backward.
-template <bool B_NK, bool DA_KM = false, bool CONV = false, bool FUSED = false>
+template <bool B_NK, bool DA_KM = false, bool CONV = false, bool FUSED = false, bool SLICED = false>
 __global__ void __launch_bounds__(BWD_THREADS)
 mam_bwd_kernel(const float* __restrict__ a, const float* __restrict__ w, const float* __restrict__ g,
                const int* __restrict__ argmax, const int* __restrict__ argmin,
                float* __restrict__ da, float* __restrict__ dw,
                long long M, long long K, long long N, int rows_per_cta, float scale, ConvGeom cg, int slices) {
-    // slices > 1: argmax / argmin hold one [M,N] matrix per slice of K (the module's `splits`); every slice
-    // routes the same upstream gradient through its own selected pairs
+    // SLICED: argmax / argmin hold one [M,N] matrix per slice of K (the module's `splits`), `slices` of them;
+    // every slice routes the same upstream gradient through its own selected pairs.  (A template parameter, so
+    // that the ordinary kernel keeps the loop nest the compiler schedules best.)
     extern __shared__ float da_s[];  // [rows_per_cta][K]
     const long long m0 = (long long)blockIdx.x * rows_per_cta;
     const int rows = (int)min((long long)rows_per_cta, M - m0);
@@ -93,10 +94,12 @@ mam_bwd_kernel(const float* __restrict__ a, const float* __restrict__ w, const f
             }
         };
         float* dar = da_s + (long long)r * K;
-        for (long long sn = threadIdx.x; sn < N * slices; sn += BWD_THREADS) {
-            const long long sl = sn / N, n = sn - sl * N;
+        for (int sl = 0; sl < (SLICED ? slices : 1); ++sl) {
+        const int* amax_row = argmax + (SLICED ? (long long)sl * M * N : 0) + m * N;
+        const int* amin_row = argmin + (SLICED ? (long long)sl * M * N : 0) + m * N;
+        for (long long n = threadIdx.x; n < N; n += BWD_THREADS) {
             const float gv = __fmul_rn(g[m * N + n], scale);
-            int k1 = argmax[sl * M * N + m * N + n], k2 = argmin[sl * M * N + m * N + n];
+            int k1 = amax_row[n], k2 = amin_row[n];
             // an index outside [0,K) cannot come from the forward; skip it rather than fault
             const bool ok1 = (unsigned)k1 < (unsigned long long)K, ok2 = (unsigned)k2 < (unsigned long long)K;
             if (ok1) {
@@ -109,6 +112,7 @@ mam_bwd_kernel(const float* __restrict__ a, const float* __restrict__ w, const f
                 atomicAdd(&dar[k2], __fmul_rn(w[wi], gv));
                 dw_term<FUSED, false>(dw, wi, __fmul_rn(a_at(k2), gv));
             }
+        }
         }
     }
     __syncthreads();
@@ -157,7 +161,7 @@ __device__ __forceinline__ void warp_row_add(float* row, int k, bool ok, float v
     __syncwarp();
 }
 
-template <bool B_NK, bool A_SMEM, bool FUSED = false>
+template <bool B_NK, bool A_SMEM, bool FUSED = false, bool SLICED = false>
 __global__ void __launch_bounds__(BWD_THREADS)
 mam_bwd_rowwarp_kernel(const float* __restrict__ a, const float* __restrict__ w, const float* __restrict__ g,
                        const int* __restrict__ argmax, const int* __restrict__ argmin,
@@ -177,9 +181,9 @@ mam_bwd_rowwarp_kernel(const float* __restrict__ a, const float* __restrict__ w,
     }
     __syncwarp();
     const float* grow = g + m * N;
-    for (int sl = 0; sl < slices; ++sl) {   // one [M,N] pair of index matrices per slice of K
-    const int* r1 = argmax + (long long)sl * M * N + m * N;
-    const int* r2 = argmin + (long long)sl * M * N + m * N;
+    for (int sl = 0; sl < (SLICED ? slices : 1); ++sl) {   // SLICED: one [M,N] pair of index matrices per slice of K
+    const int* r1 = argmax + (SLICED ? (long long)sl * M * N : 0) + m * N;
+    const int* r2 = argmin + (SLICED ? (long long)sl * M * N : 0) + m * N;
     for (long long nb = 0; nb < N; nb += 32 * U) {
         float gv[U], t1[U], t2[U];
         int k1[U], k2[U];

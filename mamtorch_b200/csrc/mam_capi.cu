@@ -2,6 +2,7 @@
 // Declarations and the reference interfaces each entry point replaces are in include/mam_b200.h.
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 #include <cuda.h>
 #include <cuda_runtime.h>
 
@@ -200,26 +201,27 @@ using SplitIdxCfg = FwdCfg<4, 8, 4, 2, 4, true, 2, false, true, true>;  // the s
 using IdxCfg0 = FwdCfg<4, 8, 4, 2, 4, true, 2, false, false>;   // 64x128 tile, 256 threads, scalar multiplies
 using IdxCfg1 = FwdCfg<4, 8, 4, 2, 4, true, 2, false>;          // 64x128 tile, 256 threads
 using IdxCfg2 = FwdCfg<4, 8, 4, 2, 4, true, 1, false>;
-using IdxCfg3 = FwdCfg<4, 8, 4, 2, 4, true, 4, false>;
+using IdxCfg3 = FwdCfg<4, 4, 4, 4, 4, true, 1, false>;          // 64x128 tile, 512 threads
 using IdxCfg4 = FwdCfg<8, 4, 2, 4, 4, true, 2, false, false>;   // A-heavy, scalar multiplies
 using IdxCfg5 = FwdCfg<8, 4, 2, 4, 4, true, 2, false>;          // 64x128 tile, 256 threads, A-heavy
 using IdxCfg6 = FwdCfg<4, 4, 4, 4, 4, true, 4, false>;          // 64x128 tile, 512 threads
-using IdxCfg7 = FwdCfg<4, 4, 6, 2, 4, true, 4, false>;          // 96x64 tile, 384 threads
+using IdxCfg7 = FwdCfg<4, 4, 4, 4, 4, true, 2, false>;          // 64x128 tile, 512 threads
 constexpr int N_VARIANTS = 8;
 const char* kValNames[N_VARIANTS] = {"val_8x8_t128x128_c256_u1_scalar", "val_8x8_t128x128_c256_u2",
                                      "val_8x8_t128x128_c256_u1", "val_4x8_t96x128_c384_u2", "val_4x8_t64x192_c384_u2",
                                      "val_4x8_t64x128_c256_u2_scalar", "val_4x8_t64x128_c256_u2b",
                                      "val_4x4_t128x64_c512_u4"};
 const char* kIdxNames[N_VARIANTS] = {"idx_4x8_t64x128_c256_u2_scalar", "idx_4x8_t64x128_c256_u2",
-                                     "idx_4x8_t64x128_c256_u1", "idx_4x8_t64x128_c256_u4",
+                                     "idx_4x8_t64x128_c256_u1", "idx_4x4_t64x128_c512_u1",
                                      "idx_8x4_t64x128_c256_u2_scalar", "idx_8x4_t64x128_c256_u2",
-                                     "idx_4x4_t64x128_c512_u4", "idx_4x4_t96x64_c384_u4"};
+                                     "idx_4x4_t64x128_c512_u4", "idx_4x4_t64x128_c512_u2"};
 int g_variant[2] = {-1, -1};  // [with_indices]
 int g_resolve_simple = 0;      // 1: use the thread-per-output resolver (cross-check)
 
 // Scratch for mam_fwd_kn_static_f32: lives in the library image, one copy per device.
 static __device__ __align__(256) unsigned char g_static_scratch[MAM_STATIC_SCRATCH_BYTES];
 void* g_static_scratch_addr[64] = {nullptr};  // device address per device, looked up on first use
+std::mutex g_static_scratch_mutex;
 
 int bad_ptr(const void* p) { return p == nullptr; }
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -241,7 +243,10 @@ int launch_csr(const float* a, const int64_t* crow, const int64_t* col, const fl
 
 // Tile configuration of the tiled forward for an M x N problem.
 int auto_variant(bool want_idx, int64_t M, int64_t N, const DevInfo& d) {
-    if (want_idx) return 1;  // 4x8 outputs per thread, 64x128 tile
+    // 4x8 outputs per thread, 64x128 tile, the k loop not unrolled beyond one 16-byte group: measured ~1 % ahead
+    // of the twice-unrolled form at 12608x768x3072, 12608x3072x768 and 4096^3 (2.914 / 2.785 / 6.423 against
+    // 2.947 / 2.803 / 6.464 ms); the 512-thread 4x4 form wins only the first of the three (2.880)
+    if (want_idx) return 2;
     // Candidates differ in speed per unit (measured, units/clk/SM) and in how well their tile
     // count fills whole waves of SMs; pick the best product of the two.
     struct Cand { int variant; long long bm, bn; double rate; };
@@ -688,15 +693,21 @@ int mam_fwd_kn_static_f32(const float* a, const float* b, float* y, int32_t* arg
     int dev = 0;
     MAM_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) return MAM_ERR_UNSUPPORTED;
-    if (g_static_scratch_addr[dev] == nullptr) {
+    void* scratch = nullptr;
+    {
         // In host code `g_static_scratch` is only a handle for the symbol, not a device address:
-        // ask the runtime where the array lives on the current device, once.
-        void* p = nullptr;
-        MAM_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
-        g_static_scratch_addr[dev] = p;
+        // ask the runtime where the array lives on the current device, once (first callers on several
+        // host threads take turns).
+        std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+        if (g_static_scratch_addr[dev] == nullptr) {
+            void* p = nullptr;
+            MAM_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
+            g_static_scratch_addr[dev] = p;
+        }
+        scratch = g_static_scratch_addr[dev];
     }
-    return mam_fwd_f32(a, b, MAM_B_KN, nullptr, nullptr, 0, 1.0f, 0.0f, y, argmax, argmin, M, K, N,
-                       g_static_scratch_addr[dev], MAM_STATIC_SCRATCH_BYTES, stream);
+    return mam_fwd_f32(a, b, MAM_B_KN, nullptr, nullptr, 0, 1.0f, 0.0f, y, argmax, argmin, M, K, N, scratch,
+                       MAM_STATIC_SCRATCH_BYTES, stream);
 }
 
 int mam_bwd_count_f32(const float* a, const float* b, int b_layout, const float* grad, const int32_t* argmax,
@@ -760,7 +771,7 @@ int mam_bwd_splits_f32(const float* a, const float* b, int b_layout, const float
     // the hits travel with the dW terms when the caller brought the scratch for the 16-byte records
     // (a caller that brings the scratch gets the records whatever the query's advice, except beyond 2^24 rows)
     const size_t fused_need = M < (1LL << 24) ? round256((size_t)K * (size_t)N * 16) : 0;
-    const bool fused = count && workspace != nullptr && fused_need != 0 && g_bwd_mode != 2;
+    const bool fused = count && workspace != nullptr && fused_need != 0 && g_bwd_mode != 2 && slices == 1;
     if (fused && (workspace_bytes < fused_need || (reinterpret_cast<uintptr_t>(workspace) & 255u)))
         return MAM_ERR_WORKSPACE;
     float* dw_dst = fused ? static_cast<float*>(workspace) : db;
@@ -819,7 +830,10 @@ int mam_bwd_splits_f32(const float* a, const float* b, int b_layout, const float
             return MAM_OK;
         };
         const bool nk = b_layout == MAM_B_NK;
-        if (fused)
+        if (slices > 1)   // (the sliced form always takes the plain reductions and, for hits, the second sweep)
+            st = nk ? (a_smem ? launch(mam_bwd_rowwarp_kernel<true, true, false, true>) : launch(mam_bwd_rowwarp_kernel<true, false, false, true>))
+                    : (a_smem ? launch(mam_bwd_rowwarp_kernel<false, true, false, true>) : launch(mam_bwd_rowwarp_kernel<false, false, false, true>));
+        else if (fused)
             st = nk ? (a_smem ? launch(mam_bwd_rowwarp_kernel<true, true, true>) : launch(mam_bwd_rowwarp_kernel<true, false, true>))
                     : (a_smem ? launch(mam_bwd_rowwarp_kernel<false, true, true>) : launch(mam_bwd_rowwarp_kernel<false, false, true>));
         else
@@ -844,7 +858,10 @@ int mam_bwd_splits_f32(const float* a, const float* b, int b_layout, const float
             return MAM_OK;
         };
         const bool nk = b_layout == MAM_B_NK, km = da_layout == MAM_DA_KM;
-        if (fused)
+        if (slices > 1)
+            st = nk ? (km ? launch(mam_bwd_kernel<true, true, false, false, true>) : launch(mam_bwd_kernel<true, false, false, false, true>))
+                    : (km ? launch(mam_bwd_kernel<false, true, false, false, true>) : launch(mam_bwd_kernel<false, false, false, false, true>));
+        else if (fused)
             st = nk ? (km ? launch(mam_bwd_kernel<true, true, false, true>) : launch(mam_bwd_kernel<true, false, false, true>))
                     : (km ? launch(mam_bwd_kernel<false, true, false, true>) : launch(mam_bwd_kernel<false, false, false, true>));
         else

@@ -68,29 +68,50 @@ def _flat_allreduce(tensors: Sequence[torch.Tensor], bucket_bytes: int) -> None:
 
 
 class OverlappedGradSync:
-    """All-reduces every parameter's gradient as soon as autograd has finished accumulating it.
+    """All-reduces every parameter's gradient without a staging copy, off the compute stream.
 
-    A hook on each parameter (`register_post_accumulate_grad_hook`) starts an asynchronous, in-place
-    all-reduce of `param.grad`; with NCCL it runs on the process group's own stream, ordered after the
-    kernel that produced the gradient, while the backward of the earlier layers carries on on the compute
-    stream.  The weight gradient of the last layer thus crosses NVLink under the backward of the layers
-    before it.  `finish()` makes the current stream wait for all started collectives -- call it once
-    after `backward()`, before the gradients are read.  Sums, like `allreduce_gradients` (pass
-    `average=True` for the mean).  `enabled = False` turns the hooks into no-ops."""
+    A hook on each parameter (`register_post_accumulate_grad_hook`) fires as soon as autograd has finished
+    accumulating its gradient.  In the default mode the hook starts an asynchronous, in-place all-reduce of
+    `param.grad` right away; with NCCL it runs on the process group's own stream, ordered after the kernel that
+    produced the gradient, while the backward of the earlier layers carries on on the compute stream: the
+    weight gradient of the last layer crosses NVLink under the backward of the layers before it.
 
-    def __init__(self, params: Iterable[torch.nn.Parameter], average: bool = False, group=None):
-        self.average, self.group, self.enabled = average, group, True
+    `deferred=True` only notes the gradients in the hooks; `start()` then launches all the (asynchronous)
+    all-reduces at once.  That is for a backward whose own kernels are bound by the same L2 / memory system the
+    collective's kernels use -- the MAM scatter backward is -- where running the two side by side costs more
+    than it hides, and the exchange is better put under whatever follows the backward (bookkeeping kernels,
+    the next data copy).
+
+    `finish()` makes the current stream wait for all started collectives -- call it once after `backward()`,
+    before the gradients are read.  Sums, like `allreduce_gradients` (pass `average=True` for the mean).
+    `enabled = False` turns the hooks into no-ops."""
+
+    def __init__(self, params: Iterable[torch.nn.Parameter], average: bool = False, group=None,
+                 deferred: bool = False):
+        self.average, self.group, self.enabled, self.deferred = average, group, True, deferred
         self._works: list = []
         self._grads: list[torch.Tensor] = []
+        self._pending: list[torch.Tensor] = []
         self._handles = [p.register_post_accumulate_grad_hook(self._hook) for p in params if p.requires_grad]
 
     def _hook(self, param: torch.nn.Parameter) -> None:
         if not self.enabled or param.grad is None:
             return
+        if self.deferred:
+            self._pending.append(param.grad)
+            return
         self._works.append(dist.all_reduce(param.grad, group=self.group, async_op=True))
         self._grads.append(param.grad)
 
+    def start(self) -> None:
+        """Deferred mode: launch the all-reduces of every gradient noted since the last finish()."""
+        for g in self._pending:
+            self._works.append(dist.all_reduce(g, group=self.group, async_op=True))
+            self._grads.append(g)
+        self._pending.clear()
+
     def finish(self) -> None:
+        self.start()
         for w in self._works:
             w.wait()
         if self.average:

@@ -64,6 +64,15 @@ def _worker(rank, world, port, out):
         sync.finish()
         hooked_ok &= torch.allclose(lin_w.grad, gs.T @ xs, rtol=1e-5, atol=1e-5)   # disabled: the rank's own gradient
         sync.remove()
+        # deferred mode: the hooks only note the gradients, start() launches, finish() waits
+        lin_w.grad = None
+        sync = OverlappedGradSync([lin_w], deferred=True)
+        ((xs @ lin_w.T) * gs).sum().backward()
+        hooked_ok &= torch.allclose(lin_w.grad, gs.T @ xs, rtol=1e-5, atol=1e-5)   # nothing exchanged yet
+        sync.start()
+        sync.finish()
+        hooked_ok &= torch.allclose(lin_w.grad, gy.T @ x, rtol=1e-5, atol=1e-5)
+        sync.remove()
         if rank == 0:
             y_full, imax_f, imin_f = mam_oracle.mam_forward(x, b)
             _, db_full = mam_oracle.mam_backward(x, b, gy, imax_f, imin_f)
