@@ -52,10 +52,10 @@ WORKLOAD = ("ViT-B/16 MAM MLP pair fwd+bwd, fp32, M=12608 tokens per rank, 768->
 M_TOTAL_OUTPUTS = M_TOKENS * (D_FF + D_MODEL)   # outputs of both layers per rank
 
 # DRAM bytes (read + write) of one launch of the index-tracking forward at M=4736, K=768, N=3072, from a
-# profiler capture of `bench.py --case step --shape 4736x768x3072 --reps 1`: 24.1 MB read (of which the
-# 9.4 MB weight does not depend on M) + 122.5 MB written.  The rest grows with the rows, so a launch at M rows
-# moves about 9.4 MB + 137.2 MB * M / 4736.
-TRAFFIC_CAPTURED_ROWS, TRAFFIC_CAPTURED_BYTES, TRAFFIC_WEIGHT_BYTES = 4736, 1.372e8, 9.4e6
+# profiler capture of `bench.py --case step --shape 4736x768x3072 --reps 1`: 24.2 MB read (of which the
+# 9.4 MB weight does not depend on M) + 64.4 MB written.  The rest grows with the rows, so a launch at M rows
+# moves about 9.4 MB + 79.2 MB * M / 4736.
+TRAFFIC_CAPTURED_ROWS, TRAFFIC_CAPTURED_BYTES, TRAFFIC_WEIGHT_BYTES = 4736, 7.92e7, 9.4e6
 
 SHARDED_M, SHARDED_K, SHARDED_N, SHARDED_SPARSITY = 65536, 4096, 4096, 0.9
 CONV_SHAPE = (128, 64, 56, 56, 128)      # B, C, H, W, F; 3x3, stride 1, padding 1
@@ -984,7 +984,7 @@ def main():
     peaks = fp32_peaks(sms, max_mhz)
     achieved = flops_per_launch / (kavg * 1e-3) / 1e12
     roofline = {"bound": "fp32_cuda_core", "kernel": "mam_fwd_tiled_kernel (index-tracking variant "
-                + L.mam_fwd_variant_name(1, args.fwd_variant if args.fwd_variant >= 0 else 2).decode() + ")",
+                + L.mam_fwd_variant_name(1, args.fwd_variant if args.fwd_variant >= 0 else 0).decode() + ")",
                 "achieved": achieved, "peak": peaks["fma_counted_tflops"], "unit": "TFLOP/s",
                 "frac": achieved / peaks["fma_counted_tflops"],
                 "peak_source": f"{sms} SMs x 128 lanes x 2 x {max_mhz:.0f} MHz (FMA counted as 2; no fp32 entry in "

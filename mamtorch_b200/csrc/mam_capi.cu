@@ -198,7 +198,7 @@ using ValCfg6 = FwdCfg<4, 8, 4, 2, 4, false, 2, true>;          // 64x128 tile, 
 using ValCfg7 = FwdCfg<4, 4, 8, 2, 6, false, 4, false>;         // 128x64 tile, 512 threads
 using SplitCfg = FwdCfg<4, 8, 4, 2, 4, false, 2, false, true, true>;   // 64x128 tile, slices of K summed in the kernel
 using SplitIdxCfg = FwdCfg<4, 8, 4, 2, 4, true, 2, false, true, true>;  // the same with chunk ids per slice
-using IdxCfg0 = FwdCfg<4, 8, 4, 2, 4, true, 2, false, false>;   // 64x128 tile, 256 threads, scalar multiplies
+using IdxCfg0 = FwdCfg<4, 8, 4, 2, 4, true, 1, false, true, false, true>;   // as IdxCfg2 with the paired-warp row mapping
 using IdxCfg1 = FwdCfg<4, 8, 4, 2, 4, true, 2, false>;          // 64x128 tile, 256 threads
 using IdxCfg2 = FwdCfg<4, 8, 4, 2, 4, true, 1, false>;
 using IdxCfg3 = FwdCfg<4, 4, 4, 4, 4, true, 1, false>;          // 64x128 tile, 512 threads
@@ -211,7 +211,7 @@ const char* kValNames[N_VARIANTS] = {"val_8x8_t128x128_c256_u1_scalar", "val_8x8
                                      "val_8x8_t128x128_c256_u1", "val_4x8_t96x128_c384_u2", "val_4x8_t64x192_c384_u2",
                                      "val_4x8_t64x128_c256_u2_scalar", "val_4x8_t64x128_c256_u2b",
                                      "val_4x4_t128x64_c512_u4"};
-const char* kIdxNames[N_VARIANTS] = {"idx_4x8_t64x128_c256_u2_scalar", "idx_4x8_t64x128_c256_u2",
+const char* kIdxNames[N_VARIANTS] = {"idx_4x8_t64x128_c256_u1_row8", "idx_4x8_t64x128_c256_u2",
                                      "idx_4x8_t64x128_c256_u1", "idx_4x4_t64x128_c512_u1",
                                      "idx_8x4_t64x128_c256_u2_scalar", "idx_8x4_t64x128_c256_u2",
                                      "idx_4x4_t64x128_c512_u4", "idx_4x4_t64x128_c512_u2"};
@@ -243,10 +243,11 @@ int launch_csr(const float* a, const int64_t* crow, const int64_t* col, const fl
 
 // Tile configuration of the tiled forward for an M x N problem.
 int auto_variant(bool want_idx, int64_t M, int64_t N, const DevInfo& d) {
-    // 4x8 outputs per thread, 64x128 tile, the k loop not unrolled beyond one 16-byte group: measured ~1 % ahead
-    // of the twice-unrolled form at 12608x768x3072, 12608x3072x768 and 4096^3 (2.914 / 2.785 / 6.423 against
-    // 2.947 / 2.803 / 6.464 ms); the 512-thread 4x4 form wins only the first of the three (2.880)
-    if (want_idx) return 2;
+    // 4x8 outputs per thread, 64x128 tile, the k loop not unrolled beyond one 16-byte group, paired-warp row
+    // mapping: the fastest of the index-producing forms at 12608x768x3072, 12608x3072x768 and 4096^3 alike
+    // (2.70 / 2.60 / 6.00 ms; the same without the row mapping 2.76 / 2.65 / 6.13; the 512-thread 4x4 form wins
+    // only the first of the three, 2.67)
+    if (want_idx) return 0;
     // Candidates differ in speed per unit (measured, units/clk/SM) and in how well their tile
     // count fills whole waves of SMs; pick the best product of the two.
     struct Cand { int variant; long long bm, bn; double rate; };

@@ -278,22 +278,26 @@ mam_csr_tiled_kernel(const __grid_constant__ CUtensorMap tmAT, const CsrTiledPar
     }
     __syncthreads();
 
-    // producer state (thread 0): stage p_ks of aT, columns [p_ks*64, +64) x rows [m0, m0+128)
+    // producer: stage p_ks of aT, columns [p_ks*64, +64) x rows [m0, m0+128).  Every thread steps the position;
+    // the warp that issues the copy changes from stage to stage, so that no warp is permanently the slowest.
     int p_ks = 0, p_stage = 0;
     uint32_t p_phase = 0;
-    auto produce_one = [&]() -> bool {
+    auto produce_one = [&](const bool issue) -> bool {
         if (p_ks >= nks) return true;
-        if (!mbar_wait_bounded(&empty_bar[p_stage], p_phase ^ 1u)) return false;
-        mbar_expect_tx(&full_bar[p_stage], CT_STAGE_BYTES);
-        tma_load_2d(smem + p_stage * CT_STAGE_BYTES, &tmAT, &full_bar[p_stage], (int)m0, p_ks * CT_KS);
+        bool good = true;
+        if (issue) {
+            good = mbar_wait_bounded(&empty_bar[p_stage], p_phase ^ 1u);
+            if (good) {
+                mbar_expect_tx(&full_bar[p_stage], CT_STAGE_BYTES);
+                tma_load_2d(smem + p_stage * CT_STAGE_BYTES, &tmAT, &full_bar[p_stage], (int)m0, p_ks * CT_KS);
+            }
+        }
         if (++p_stage == CT_STAGES) { p_stage = 0; p_phase ^= 1u; }
         ++p_ks;
-        return true;
+        return good;
     };
-    if (tid == 0) {
-        tma_prefetch_desc(&tmAT);
-        for (int i = 0; i < CT_LOOKAHEAD; ++i) produce_one();
-    }
+    if (tid == 0) tma_prefetch_desc(&tmAT);
+    for (int i = 0; i < CT_LOOKAHEAD; ++i) produce_one(tid == 0);
 
     const long long n_w = n_cta + warp * CT_WROWS;          // first W row of this warp
     const uint32_t id_addr = smem_u32(ids) + (uint32_t)tid * 4u;
@@ -349,7 +353,7 @@ mam_csr_tiled_kernel(const __grid_constant__ CUtensorMap tmAT, const CsrTiledPar
             pre = make_int4(0, 0, 0, 0);
             if (p0 + lane < p1) pre = __ldg(list4 + p0 + lane);
         }
-        if (tid == 0 && !produce_one()) atomicExch(prm.error, 1);
+        if (!produce_one(lane == 0 && warp == ks % CT_WARPS)) atomicExch(prm.error, 1);
         if (!mbar_wait_bounded(&full_bar[stage], phase)) {
             atomicExch(prm.error, 1);
             ok = false;
@@ -613,21 +617,25 @@ mam_spmm_tiled_kernel(const __grid_constant__ CUtensorMap tmB, const SpmmTiledPa
     }
     __syncthreads();
 
+    // producer: every thread steps the position, the issuing warp rotates (see mam_csr_tiled_kernel)
     int p_ks = 0, p_stage = 0;
     uint32_t p_phase = 0;
-    auto produce_one = [&]() -> bool {
+    auto produce_one = [&](const bool issue) -> bool {
         if (p_ks >= nks) return true;
-        if (!mbar_wait_bounded(&empty_bar[p_stage], p_phase ^ 1u)) return false;
-        mbar_expect_tx(&full_bar[p_stage], CT_STAGE_BYTES);
-        tma_load_2d(smem + p_stage * CT_STAGE_BYTES, &tmB, &full_bar[p_stage], (int)j0, p_ks * CT_KS);
+        bool good = true;
+        if (issue) {
+            good = mbar_wait_bounded(&empty_bar[p_stage], p_phase ^ 1u);
+            if (good) {
+                mbar_expect_tx(&full_bar[p_stage], CT_STAGE_BYTES);
+                tma_load_2d(smem + p_stage * CT_STAGE_BYTES, &tmB, &full_bar[p_stage], (int)j0, p_ks * CT_KS);
+            }
+        }
         if (++p_stage == SP_STAGES) { p_stage = 0; p_phase ^= 1u; }
         ++p_ks;
-        return true;
+        return good;
     };
-    if (tid == 0) {
-        tma_prefetch_desc(&tmB);
-        for (int i = 0; i < SP_LOOKAHEAD; ++i) produce_one();
-    }
+    if (tid == 0) tma_prefetch_desc(&tmB);
+    for (int i = 0; i < SP_LOOKAHEAD; ++i) produce_one(tid == 0);
 
     const long long n_w = n_cta + warp * SP_WROWS;
     int4* eb = eb_all + warp * CT_EB_PAIRS;
@@ -661,7 +669,7 @@ mam_spmm_tiled_kernel(const __grid_constant__ CUtensorMap tmB, const SpmmTiledPa
             pre = make_int4(0, 0, 0, 0);
             if (p0 + lane < p1) pre = __ldg(list4 + p0 + lane);
         }
-        if (tid == 0 && !produce_one()) atomicExch(prm.error, 1);
+        if (!produce_one(lane == 0 && warp == ks % CT_WARPS)) atomicExch(prm.error, 1);
         if (!mbar_wait_bounded(&full_bar[stage], phase)) {
             atomicExch(prm.error, 1);
             ok = false;

@@ -32,8 +32,14 @@ namespace mamb200 {
 constexpr int FWD_BK = 32;  // floats per row per stage = one 128-byte swizzle span
 
 template <int TM_, int TN_, int WM_, int WN_, int STAGES_, bool TRACK_, int UQ_ = 8, bool BATCH_ = false,
-          bool MUL2_ = true, bool SPLIT_ = false>
+          bool MUL2_ = true, bool SPLIT_ = false, bool ROW8_ = false>
 struct FwdCfg {
+    // Which rows of the tile a thread owns.  false: row(i) = warp_m*4*TM + lane_m + 4*i -- consecutive rows
+    // alternate between two swizzle keys, so every group of four k needs two a-addresses.  true: a pair of
+    // warps interleaves inside 32-row groups, row(i) = (warp_m/2)*8*TM + 8*i + (warp_m%2)*4 + lane_m -- all rows
+    // of a thread share (row & 7), one a-address per group of four k, the rest immediate offsets.
+    static constexpr bool ROW8 = ROW8_;
+    static_assert(!ROW8_ || (WM_ % 2 == 0), "paired warps");
     // K cut into slices of prm.split_chunks chunks: y = sum over slices of (max + min) of the slice, added in
     // ascending slice order -- the module's `splits` (mamtorch/nn/v4/fullyconnected.py:164-176) in one launch
     // With TRACK the slices' partial sums are banked in y itself (there is no room for a third accumulator set)
@@ -188,46 +194,58 @@ mam_fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     const int nk = (int)((K + FWD_BK - 1) / FWD_BK);
     const int tail_quads = (int)((K - (long long)(nk - 1) * FWD_BK) / 4);  // K % 4 == 0 is a precondition
 
-    // ------------------------------------------------------------ producer role (thread 0 only)
-    // Thread 0 walks the same (tile, chunk) sequence as the consumers, LOOKAHEAD chunks ahead.
-    // The stage it refills held the chunk computed two iterations ago, so the empty-barrier wait
-    // below is satisfied unless a peer warp lags by more than a whole chunk.
+    // ------------------------------------------------------------ producer role
+    // The loads run LOOKAHEAD chunks ahead of the chunk being computed, over the same (tile, chunk) sequence
+    // as the consumers.  The stage a load refills held the chunk computed two iterations ago, so the
+    // empty-barrier wait below is satisfied unless a peer warp lags by more than a whole chunk.  EVERY thread
+    // steps the producer's position (warp-uniform counters); who issues the copies rotates over the warps, chunk
+    // by chunk, so that the few dozen instructions of an issue do not make one warp -- and with it the whole CTA,
+    // which moves at the pace of its slowest warp -- permanently slower than the others.  (Convolution rows keep
+    // thread 0: the im2col cursor lives in the issuing thread.)
     long long p_tile = blockIdx.x;
     int p_kc = 0, p_stage = 0;
     uint32_t p_phase = 0;
     [[maybe_unused]] Im2colCursor p_cur{};
-    auto produce_one = [&]() -> bool {
+    auto produce_one = [&](const bool issue) -> bool {
         if (p_tile >= ntiles) return true;
-        if (!mbar_wait_bounded(&empty_bar[p_stage], p_phase ^ 1u)) return false;
-        const int tm = (int)(p_tile / ntn), tn = (int)(p_tile % ntn);
-        mbar_expect_tx(&full_bar[p_stage], Cfg::STAGE_BYTES);
-        unsigned char* sa = smem + p_stage * Cfg::STAGE_BYTES;
-        if constexpr (CONV) {
-            if (p_kc == 0) p_cur.start_tile(prm.conv, (long long)tm * Cfg::BM);
-            p_cur.load_and_advance(sa, &tmA, &full_bar[p_stage], prm.conv);
-        } else {
-            tma_load_2d(sa, &tmA, &full_bar[p_stage], p_kc * FWD_BK, tm * Cfg::BM);
+        bool ok = true;
+        if (issue) {
+            ok = mbar_wait_bounded(&empty_bar[p_stage], p_phase ^ 1u);
+            if (ok) {
+                const int tm = (int)(p_tile / ntn), tn = (int)(p_tile % ntn);
+                mbar_expect_tx(&full_bar[p_stage], Cfg::STAGE_BYTES);
+                unsigned char* sa = smem + p_stage * Cfg::STAGE_BYTES;
+                if constexpr (CONV) {
+                    if (p_kc == 0) p_cur.start_tile(prm.conv, (long long)tm * Cfg::BM);
+                    p_cur.load_and_advance(sa, &tmA, &full_bar[p_stage], prm.conv);
+                } else {
+                    tma_load_2d(sa, &tmA, &full_bar[p_stage], p_kc * FWD_BK, tm * Cfg::BM);
+                }
+                tma_load_2d(sa + Cfg::A_BYTES, &tmW, &full_bar[p_stage], p_kc * FWD_BK, tn * Cfg::BN);
+            }
         }
-        tma_load_2d(sa + Cfg::A_BYTES, &tmW, &full_bar[p_stage], p_kc * FWD_BK, tn * Cfg::BN);
         if (++p_stage == STAGES) { p_stage = 0; p_phase ^= 1u; }
         if (++p_kc == nk) { p_kc = 0; p_tile += gridDim.x; }
-        return true;
+        return ok;
     };
     if (tid == 0) {
         tma_prefetch_desc(&tmA);
         tma_prefetch_desc(&tmW);
-        for (int i = 0; i < Cfg::LOOKAHEAD; ++i) produce_one();
     }
+    for (int i = 0; i < Cfg::LOOKAHEAD; ++i) produce_one(tid == 0);
 
     // ---------------------------------------------------------------- consumers
     const int wm = warp / Cfg::WN, wn = warp % Cfg::WN;
     const int lane_m = lane >> 3, lane_n = lane & 7;
     // byte offsets of this thread's first A row / W row inside a stage; further rows are +i*512 / +j*1024
-    const uint32_t a_row0 = (uint32_t)(wm * 4 * TM + lane_m) * 128u;
+    // first row of a this thread owns inside the tile, and the distance between its rows
+    const int a_first = Cfg::ROW8 ? (wm >> 1) * 8 * TM + (wm & 1) * 4 + lane_m : wm * 4 * TM + lane_m;
+    constexpr int A_ROW_STEP = Cfg::ROW8 ? 8 : 4;
+    const uint32_t a_row0 = (uint32_t)a_first * 128u;
     const uint32_t w_row0 = (uint32_t)Cfg::A_BYTES + (uint32_t)(wn * 8 * TN + lane_n) * 128u;
     // swizzle: 16-byte group q of row r sits at group q ^ (r & 7).  Rows of this thread have
     // (r & 7) = lane_m (even i), lane_m + 4 (odd i) for A and lane_n for W.
-    const uint32_t a_key = (uint32_t)lane_m << 4, w_key = (uint32_t)lane_n << 4;
+    const uint32_t a_key = (uint32_t)(Cfg::ROW8 ? (a_first & 7) : lane_m) << 4, w_key = (uint32_t)lane_n << 4;
     const uint32_t id_addr = smem_u32(ids) + (uint32_t)tid * 2u;
 
     int stage = 0;
@@ -267,14 +285,14 @@ mam_fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                     next_split += prm.split_chunks;
                     if constexpr (TRACK) {
                         const long long slice = kc / prm.split_chunks - 1;   // the slice that just ended
-                        const long long mrow0 = (long long)tm * Cfg::BM + wm * 4 * TM + lane_m;
+                        const long long mrow0 = (long long)tm * Cfg::BM + a_first;
                         const long long ncol0 = (long long)tn * Cfg::BN + wn * 8 * TN + lane_n;
                         slice_base = kc;
 #pragma unroll
                         for (int i = 0; i < TM; ++i)
 #pragma unroll
                             for (int j = 0; j < TN; ++j) {
-                                const long long m = mrow0 + i * 4, n = ncol0 + j * 8;
+                                const long long m = mrow0 + i * A_ROW_STEP, n = ncol0 + j * 8;
                                 const uint32_t amax = id_addr + (uint32_t)(((i * TN + j) * 2 + 0) * Cfg::CONSUMERS * 2);
                                 const uint32_t amin = id_addr + (uint32_t)(((i * TN + j) * 2 + 1) * Cfg::CONSUMERS * 2);
                                 if (m < M && n < N) {
@@ -306,7 +324,8 @@ mam_fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                     }
                 }
             }
-            if (tid == 0 && !produce_one()) atomicExch(prm.error, 1);
+            const bool my_turn = CONV ? tid == 0 : (lane == 0 && warp == kc % Cfg::CONSUMER_WARPS);
+            if (!produce_one(my_turn)) atomicExch(prm.error, 1);
             if (!mbar_wait_bounded(&full_bar[stage], phase)) {
                 atomicExch(prm.error, 1);
                 ok = false;
@@ -317,16 +336,18 @@ mam_fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
             const uint32_t wp = sbase + w_row0;
             float lmax[TRACK ? TM : 1][TRACK ? TN : 1], lmin[TRACK ? TM : 1][TRACK ? TN : 1];
 
-            auto quad = [&](const int q, const bool first) {
+            // qoff = 16 * (index of the group of four k inside the chunk)
+            auto quad = [&](const uint32_t qoff, const bool first) {
                 // ap and wp are 128-byte aligned and the swizzled group offset is < 128, so OR is ADD
                 // and each address is one three-input logic op
-                const uint32_t xa0 = ap | (((uint32_t)q << 4) ^ a_key);
+                const uint32_t xa0 = ap | (qoff ^ a_key);
                 const uint32_t xa1 = xa0 ^ 64u;
-                const uint32_t xw = wp | (((uint32_t)q << 4) ^ w_key);
+                const uint32_t xw = wp | (qoff ^ w_key);
                 ulonglong2 av[TM];
                 static_for<0, TM>([&](auto ic) {
                     constexpr int i = decltype(ic)::value;
-                    av[i] = lds128_at<i * 512>((i & 1) ? xa1 : xa0);
+                    if constexpr (Cfg::ROW8) av[i] = lds128_at<i * 1024>(xa0);
+                    else av[i] = lds128_at<i * 512>((i & 1) ? xa1 : xa0);
                 });
                 static_for<0, TN>([&](auto jc) {
                     constexpr int j = decltype(jc)::value;
@@ -377,9 +398,10 @@ mam_fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
             // the chunk-local extremes), the rest run in a loop unrolled UQ groups at a time so
             // that the body stays inside the instruction cache
             const int nq = (kc + 1 < nk) ? FWD_BK / 4 : tail_quads;
-            quad(0, true);
+            quad(0u, true);
+            const uint32_t qend = (uint32_t)nq << 4;
 #pragma unroll(Cfg::UQ)
-            for (int q = 1; q < nq; ++q) quad(q, false);
+            for (uint32_t qoff = 16u; qoff < qend; qoff += 16u) quad(qoff, false);
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty_bar[stage]);
             if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -415,11 +437,11 @@ mam_fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         if (!ok) break;
 
         // ------------------------------------------------------------ epilogue
-        const long long mrow0 = (long long)tm * Cfg::BM + wm * 4 * TM + lane_m;
+        const long long mrow0 = (long long)tm * Cfg::BM + a_first;
         const long long ncol0 = (long long)tn * Cfg::BN + wn * 8 * TN + lane_n;
 #pragma unroll
         for (int i = 0; i < TM; ++i) {
-            const long long m = mrow0 + i * 4;
+            const long long m = mrow0 + i * A_ROW_STEP;
             if (m >= M) continue;
 #pragma unroll
             for (int j = 0; j < TN; ++j) {
@@ -520,31 +542,37 @@ mam_resolve_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     for (int i = tid; i < entries; i += C::THREADS) sts32_s(cursor_s + 4u * i, 0);
     __syncthreads();
 
-    // producer state (thread 0)
+    // producer: every thread steps the position, the warp that issues the copies rotates chunk by chunk (as in
+    // the main kernel; convolution rows keep thread 0, where the im2col cursor lives)
     int p_kc = 0, p_stage = 0;
     uint32_t p_phase = 0;
     [[maybe_unused]] Im2colCursor p_cur{};
-    auto produce_one = [&]() -> bool {
+    auto produce_one = [&](const bool issue) -> bool {
         if (p_kc >= nk) return true;
-        if (!mbar_wait_bounded(&empty_bar[p_stage], p_phase ^ 1u)) return false;
-        mbar_expect_tx(&full_bar[p_stage], C::STAGE_BYTES);
-        unsigned char* sa = smem + p_stage * C::STAGE_BYTES;
-        if constexpr (CONV) {
-            if (p_kc == 0) p_cur.start_tile(conv, m0);
-            p_cur.load_and_advance(sa, &tmA, &full_bar[p_stage], conv);
-        } else {
-            tma_load_2d(sa, &tmA, &full_bar[p_stage], p_kc * FWD_BK, (int)m0);
+        bool good = true;
+        if (issue) {
+            good = mbar_wait_bounded(&empty_bar[p_stage], p_phase ^ 1u);
+            if (good) {
+                mbar_expect_tx(&full_bar[p_stage], C::STAGE_BYTES);
+                unsigned char* sa = smem + p_stage * C::STAGE_BYTES;
+                if constexpr (CONV) {
+                    if (p_kc == 0) p_cur.start_tile(conv, m0);
+                    p_cur.load_and_advance(sa, &tmA, &full_bar[p_stage], conv);
+                } else {
+                    tma_load_2d(sa, &tmA, &full_bar[p_stage], p_kc * FWD_BK, (int)m0);
+                }
+                tma_load_2d(sa + C::A_BYTES, &tmW, &full_bar[p_stage], p_kc * FWD_BK, (int)n0);
+            }
         }
-        tma_load_2d(sa + C::A_BYTES, &tmW, &full_bar[p_stage], p_kc * FWD_BK, (int)n0);
         if (++p_stage == C::STAGES) { p_stage = 0; p_phase ^= 1u; }
         ++p_kc;
-        return true;
+        return good;
     };
     if (tid == 0) {
         tma_prefetch_desc(&tmA);
         tma_prefetch_desc(&tmW);
-        for (int i = 0; i < C::LOOKAHEAD; ++i) produce_one();
     }
+    for (int i = 0; i < C::LOOKAHEAD; ++i) produce_one(tid == 0);
 
     // ---- pass A: read this thread's chunk ids once (all loads in flight together) and take a place in the
     // bucket of each: the value an integer shared-memory atomic returns IS the task's rank, so the sort needs
@@ -638,7 +666,7 @@ mam_resolve_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     uint32_t phase = 0;
     [[maybe_unused]] int r_cc = 0, r_kh = 0, r_kw = 0;   // convolution: channel block and tap of the chunk being resolved
     for (int kc = 0; kc < nk; ++kc) {
-        if (tid == 0 && !produce_one()) atomicExch(error, 1);
+        if (!produce_one(CONV ? tid == 0 : (lane == 0 && warp == kc % C::WARPS))) atomicExch(error, 1);
         if (!mbar_wait_bounded(&full_bar[stage], phase)) {
             atomicExch(error, 1);
             return;

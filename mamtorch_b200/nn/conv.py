@@ -19,8 +19,11 @@ Each output pixel is one row of a GEMM-shaped MAM problem: M = B*Ho*Wo, K = C*kH
                       `conv_im2col` and the fully-connected kernels run on them;
   "taps"              the first in the backup's own reduction order (channels fastest, then kh, then
                       kw).  No patch rows exist: the kernels fetch 32-channel chunks of them from the
-                      channels-last input by im2col-mode TMA (`conv_forward_implicit`).  Needs
-                      C % 32 == 0 (otherwise the same order is produced through permuted patch rows).
+                      channels-last input by im2col-mode TMA (`conv_forward_implicit`).  A channel count
+                      that is not a multiple of 32 is padded up to one (zero channels in the copy of x, NaN
+                      channels in the weight: a NaN product never becomes an extreme), at Cp / C of the
+                      arithmetic; only where the copy engine cannot express the geometry at all is the same
+                      order produced through permuted patch rows.
 
 Values are identical in both; indices are always NUMBERED k = (c*kH + kh)*kW + kw and differ between
 the two orders only where a maximum or minimum is attained more than once (zero products of padding
@@ -128,6 +131,19 @@ def _forward_rows(x, weight, w2d, bias, dflat, alpha, beta, geom, taps, need_ind
         if x_nhwc.data_ptr() % 16 == 0:
             return _ops.conv_forward_implicit(x_nhwc, w_taps, bias, dflat, alpha, beta, kH, kW, sh, sw, ph, pw,
                                               need_indices)
+    Cp = -(-C // 32) * 32
+    if Cp != C and _ops.conv_implicit_applies(B, Cp, H, W, kH, kW, sh, sw, ph, pw):
+        # A channel count that is not a multiple of 32: the copy engine wants whole 32-channel chunks, so the
+        # channels-last copy of x is padded with zero channels and the weight with NaN channels.  A padded
+        # product is 0 * NaN = NaN, and fp32 max / min return the operand that is a number: the padded channels
+        # never reach a maximum, a minimum or an index (the indices' numbering (c*kH + kh)*kW + kw does not
+        # involve the channel count).  Costs Cp / C of the arithmetic, and still no patch rows.
+        x_nhwc = x.new_zeros((B, H, W, Cp))
+        x_nhwc[..., :C] = x.permute(0, 2, 3, 1)
+        w_pad = weight.new_full((Fo, kW, kH, Cp), float("nan"))
+        w_pad[..., :C] = weight.permute(0, 3, 2, 1)
+        return _ops.conv_forward_implicit(x_nhwc, w_pad.reshape(Fo, -1), bias, dflat, alpha, beta, kH, kW, sh, sw, ph,
+                                          pw, need_indices)
     # same reduction order through explicit patch rows with permuted columns
     perm = tap_order_permutation(C, kH, kW, x.device)
     rows = _ops.conv_im2col(x, kH, kW, sh, sw, ph, pw).index_select(1, perm)

@@ -345,3 +345,49 @@ def test_conv1d_without_patch_rows(cuda):
     yb.backward(gy)
     assert_grad_close(xa.grad.cpu().numpy(), xb.grad.cpu().numpy())
     assert_grad_close(taps.weight.grad.cpu().numpy(), rows.weight.grad.cpu().numpy())
+
+
+@pytest.mark.parametrize("geom", [
+    (6, 48, 28, 28, 3, 3, 1, 1, 1, 1, 40),     # 48 channels -> padded to 64
+    (16, 3, 64, 64, 3, 3, 1, 1, 1, 1, 24),     # an RGB first layer: 3 -> 32
+    (4, 33, 20, 31, 3, 2, 2, 1, 1, 0, 17),     # 33 -> 64, one real channel in the second chunk of every tap
+    (8, 100, 17, 17, 1, 1, 1, 1, 0, 0, 64),    # 1x1 kernel, 100 -> 128
+])
+@pytest.mark.parametrize("relu", [False, True])
+def test_no_patch_rows_for_channel_counts_that_are_not_multiples_of_32(geom, relu, cuda):
+    """reduction_order="taps" with C % 32 != 0: the channels are padded to a multiple of 32 -- zeros in the
+    channels-last copy of x, NaN in the weight -- and the padded products (NaN) must never show up in a value or
+    an index: everything equals the oracle in tap order on the unpadded problem, forward and backward."""
+    from mamtorch_b200.nn.conv import mam_conv2d
+
+    B, C, H, W, kH, kW, sh, sw, ph, pw, N = geom
+    assert C % 32 != 0 and _lib.lib().mam_conv_fwd_applies(B, -(-C // 32) * 32, H, W, kH, kW, sh, sw, ph, pw) == 1
+    g = torch.Generator().manual_seed(sum(geom))
+    x = torch.randn(B, C, H, W, generator=g)
+    w = torch.randn(N, C, kH, kW, generator=g) * (C * kH * kW) ** -0.5
+    if relu:
+        x, w = torch.relu(x), w.abs()      # zero ties everywhere: the first in tap order must win
+    y_ref, imax_ref, imin_ref = _tap_order_oracle(x, w, geom)
+    xd = x.to(cuda).requires_grad_()
+    wd = w.to(cuda).requires_grad_()
+    y, imax, imin = mam_conv2d(xd, wd, None, (sh, sw), (ph, pw), reduction_order="taps")
+    torch.cuda.synchronize()
+    assert capi.device_flag_ok()
+    flat = lambda t: t.permute(0, 2, 3, 1).reshape(-1, N)
+    assert not torch.isnan(y).any()
+    assert torch.equal(flat(y.detach()).cpu(), y_ref)
+    assert torch.equal(flat(imax).cpu().long(), imax_ref) and torch.equal(flat(imin).cpu().long(), imin_ref)
+    yv, _, _ = mam_conv2d(x.to(cuda), w.to(cuda), None, (sh, sw), (ph, pw), need_indices=False, reduction_order="taps")
+    assert torch.equal(yv, y.detach())
+    # backward against the patch-row module path on the same indices (no ties in the random case)
+    gy = torch.randn(y.shape, generator=g).to(cuda)
+    y.backward(gy)
+    xr = x.to(cuda).requires_grad_()
+    wr = w.to(cuda).requires_grad_()
+    yr, imax_r, _ = mam_conv2d(xr, wr, None, (sh, sw), (ph, pw))
+    assert torch.equal(yr, y)
+    if not relu:
+        assert torch.equal(imax_r, imax)
+        yr.backward(gy)
+        assert_grad_close(xd.grad.cpu().numpy(), xr.grad.cpu().numpy())
+        assert_grad_close(wd.grad.cpu().numpy(), wr.grad.cpu().numpy())
