@@ -85,18 +85,28 @@ struct Im2colRows {
 struct Im2colCursor {
     int n, h, w;        // image and base pixel (top-left patch corner) of the tile's first row
     int cc, kh, kw;     // channel block and tap of the next chunk
-    __device__ __forceinline__ void start_tile(const Im2colRows& cv, long long m0) {
+    long long m0_of;    // the tile (its first row) that n, h, w belong to; -1: none yet
+    // (cc, kh, kw) step with every chunk in every thread (warp-uniform counters); (n, h, w) cost three divisions
+    // and are formed only by a thread that issues a copy, once per tile it issues for
+    __device__ __forceinline__ void reset() { cc = kh = kw = 0; m0_of = -1; n = h = w = 0; }
+    __device__ __forceinline__ void locate(const Im2colRows& cv, long long m0) {
+        if (m0_of == m0) return;
+        m0_of = m0;
         const int hw = cv.Ho * cv.Wo;
         n = (int)(m0 / hw);
         const int rem = (int)(m0 - (long long)n * hw);
         const int ho = rem / cv.Wo;
         h = ho * cv.sh - cv.ph;
         w = (rem - ho * cv.Wo) * cv.sw - cv.pw;
-        cc = kh = kw = 0;
     }
-    __device__ __forceinline__ void load_and_advance(void* dst, const void* tmap, uint64_t* bar, const Im2colRows& cv) {
+    __device__ __forceinline__ void load(void* dst, const void* tmap, uint64_t* bar) const {
         tma_load_im2col_4d(dst, tmap, bar, cc * 32, w, h, n, (uint16_t)kw, (uint16_t)kh);
-        if (++cc == cv.c32) {
+    }
+    // to the next chunk; `wrap`: that chunk is the first of the next tile
+    __device__ __forceinline__ void advance(const Im2colRows& cv, bool wrap) {
+        if (wrap) {
+            cc = kh = kw = 0;
+        } else if (++cc == cv.c32) {
             cc = 0;
             if (++kh == cv.kH) { kh = 0; ++kw; }
         }
@@ -200,12 +210,12 @@ mam_fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     // empty-barrier wait below is satisfied unless a peer warp lags by more than a whole chunk.  EVERY thread
     // steps the producer's position (warp-uniform counters); who issues the copies rotates over the warps, chunk
     // by chunk, so that the few dozen instructions of an issue do not make one warp -- and with it the whole CTA,
-    // which moves at the pace of its slowest warp -- permanently slower than the others.  (Convolution rows keep
-    // thread 0: the im2col cursor lives in the issuing thread.)
+    // which moves at the pace of its slowest warp -- permanently slower than the others.
     long long p_tile = blockIdx.x;
     int p_kc = 0, p_stage = 0;
     uint32_t p_phase = 0;
-    [[maybe_unused]] Im2colCursor p_cur{};
+    [[maybe_unused]] Im2colCursor p_cur;
+    if constexpr (CONV) p_cur.reset();
     auto produce_one = [&](const bool issue) -> bool {
         if (p_tile >= ntiles) return true;
         bool ok = true;
@@ -216,8 +226,8 @@ mam_fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                 mbar_expect_tx(&full_bar[p_stage], Cfg::STAGE_BYTES);
                 unsigned char* sa = smem + p_stage * Cfg::STAGE_BYTES;
                 if constexpr (CONV) {
-                    if (p_kc == 0) p_cur.start_tile(prm.conv, (long long)tm * Cfg::BM);
-                    p_cur.load_and_advance(sa, &tmA, &full_bar[p_stage], prm.conv);
+                    p_cur.locate(prm.conv, (long long)tm * Cfg::BM);
+                    p_cur.load(sa, &tmA, &full_bar[p_stage]);
                 } else {
                     tma_load_2d(sa, &tmA, &full_bar[p_stage], p_kc * FWD_BK, tm * Cfg::BM);
                 }
@@ -225,7 +235,9 @@ mam_fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
             }
         }
         if (++p_stage == STAGES) { p_stage = 0; p_phase ^= 1u; }
-        if (++p_kc == nk) { p_kc = 0; p_tile += gridDim.x; }
+        const bool wrap = ++p_kc == nk;
+        if (wrap) { p_kc = 0; p_tile += gridDim.x; }
+        if constexpr (CONV) p_cur.advance(prm.conv, wrap);
         return ok;
     };
     if (tid == 0) {
@@ -324,7 +336,7 @@ mam_fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                     }
                 }
             }
-            const bool my_turn = CONV ? tid == 0 : (lane == 0 && warp == kc % Cfg::CONSUMER_WARPS);
+            const bool my_turn = lane == 0 && warp == kc % Cfg::CONSUMER_WARPS;
             if (!produce_one(my_turn)) atomicExch(prm.error, 1);
             if (!mbar_wait_bounded(&full_bar[stage], phase)) {
                 atomicExch(prm.error, 1);
@@ -543,10 +555,11 @@ mam_resolve_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     __syncthreads();
 
     // producer: every thread steps the position, the warp that issues the copies rotates chunk by chunk (as in
-    // the main kernel; convolution rows keep thread 0, where the im2col cursor lives)
+    // the main kernel)
     int p_kc = 0, p_stage = 0;
     uint32_t p_phase = 0;
-    [[maybe_unused]] Im2colCursor p_cur{};
+    [[maybe_unused]] Im2colCursor p_cur;
+    if constexpr (CONV) p_cur.reset();
     auto produce_one = [&](const bool issue) -> bool {
         if (p_kc >= nk) return true;
         bool good = true;
@@ -556,8 +569,8 @@ mam_resolve_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                 mbar_expect_tx(&full_bar[p_stage], C::STAGE_BYTES);
                 unsigned char* sa = smem + p_stage * C::STAGE_BYTES;
                 if constexpr (CONV) {
-                    if (p_kc == 0) p_cur.start_tile(conv, m0);
-                    p_cur.load_and_advance(sa, &tmA, &full_bar[p_stage], conv);
+                    p_cur.locate(conv, m0);
+                    p_cur.load(sa, &tmA, &full_bar[p_stage]);
                 } else {
                     tma_load_2d(sa, &tmA, &full_bar[p_stage], p_kc * FWD_BK, (int)m0);
                 }
@@ -566,6 +579,7 @@ mam_resolve_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         }
         if (++p_stage == C::STAGES) { p_stage = 0; p_phase ^= 1u; }
         ++p_kc;
+        if constexpr (CONV) p_cur.advance(conv, false);
         return good;
     };
     if (tid == 0) {
@@ -666,7 +680,7 @@ mam_resolve_tiled_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     uint32_t phase = 0;
     [[maybe_unused]] int r_cc = 0, r_kh = 0, r_kw = 0;   // convolution: channel block and tap of the chunk being resolved
     for (int kc = 0; kc < nk; ++kc) {
-        if (!produce_one(CONV ? tid == 0 : (lane == 0 && warp == kc % C::WARPS))) atomicExch(error, 1);
+        if (!produce_one(lane == 0 && warp == kc % C::WARPS)) atomicExch(error, 1);
         if (!mbar_wait_bounded(&full_bar[stage], phase)) {
             atomicExch(error, 1);
             return;
