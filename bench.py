@@ -249,7 +249,7 @@ def run_reference(args):
     if rank != 0:
         return
     cpu = CpuPath()
-    rows = 64
+    rows = 128
     for _ in range(max(1, min(args.warmup, 2))):
         cpu_mlp_pair_sample(cpu, rows, 1)
     t0 = time.perf_counter()
@@ -884,10 +884,12 @@ def main():
         assert err <= 1e-5, f"all-reduced dW differs from the sum of the per-rank gradients: {err}"
 
     # End-to-end leg: every step's activations and upstream gradient start in pinned host memory and
-    # its output and loss end there.  Copies run on their own stream, double-buffered, so the upload
-    # of step i+1 and the download of step i overlap the kernels of the neighbouring step -- what a
-    # data loader feeding this layer does.  All of it is inside the timed region.
-    copy_stream = torch.cuda.Stream(device=dev)
+    # its output and loss end there.  Copies run on their own streams -- one per direction, the link is full
+    # duplex -- double-buffered, so the upload of step i+1 and the download of step i overlap the kernels of
+    # the neighbouring step and each other: what a data loader feeding this layer does.  All of it is inside
+    # the timed region.
+    up_stream = torch.cuda.Stream(device=dev)
+    down_stream = torch.cuda.Stream(device=dev)
     x_buf = [torch.empty_like(x_dev) for _ in range(2)]
     gy_buf = [torch.empty_like(gy_dev) for _ in range(2)]
     y_buf = [torch.empty(64, 197, D_MODEL, device=dev) for _ in range(2)]
@@ -897,11 +899,11 @@ def main():
     down_done = [torch.cuda.Event() for _ in range(2)]
 
     def upload(slot):
-        with torch.cuda.stream(copy_stream):
-            copy_stream.wait_event(comp_done[slot])   # the buffers' previous step must be done with them
+        with torch.cuda.stream(up_stream):
+            up_stream.wait_event(comp_done[slot])   # the buffers' previous step must be done with them
             x_buf[slot].copy_(x_host, non_blocking=True)
             gy_buf[slot].copy_(gy_host, non_blocking=True)
-            up_done[slot].record(copy_stream)
+            up_done[slot].record(up_stream)
 
     def run_from_host(steps):
         main_stream = torch.cuda.current_stream()
@@ -918,12 +920,13 @@ def main():
             y_buf[slot].copy_(y.detach())
             loss_buf[slot].copy_((y.detach() * gy_buf[slot]).sum())
             comp_done[slot].record(main_stream)
-            with torch.cuda.stream(copy_stream):
-                copy_stream.wait_event(comp_done[slot])
+            with torch.cuda.stream(down_stream):
+                down_stream.wait_event(comp_done[slot])
                 y_host.copy_(y_buf[slot], non_blocking=True)
                 loss_host.copy_(loss_buf[slot], non_blocking=True)
-                down_done[slot].record(copy_stream)
-        main_stream.wait_stream(copy_stream)
+                down_done[slot].record(down_stream)
+        main_stream.wait_stream(up_stream)
+        main_stream.wait_stream(down_stream)
 
     for _ in range(args.warmup):
         step(x_dev, gy_dev)

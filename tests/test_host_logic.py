@@ -181,3 +181,45 @@ def test_tap_order_permutation_and_legacy_index():
         assert pos == (kw * kH + kh) * C + c
     # position in tap order == the legacy index of the reference's text
     assert torch.equal(to_legacy_index(perm, C, kH, kW), torch.arange(C * kH * kW))
+
+
+def test_entry_points_of_the_fused_training_paths_check_arguments_without_a_device():
+    L = _lib.lib()
+    null = None
+    one = ctypes.c_void_p(16)   # never dereferenced: every call below fails its argument check first
+    # hits riding on the dW reductions: where the size query advises it, and where it cannot be exact
+    assert L.mam_bwd_count_workspace_bytes(12608, 3072, 768) == 3072 * 768 * 16       # CTA-shared kernel, records in L2
+    assert L.mam_bwd_count_workspace_bytes(12608, 768, 3072) == 0                     # row-per-warp band: second sweep
+    assert L.mam_bwd_count_workspace_bytes(4096, 4096, 4096) == 0                     # records beyond L2
+    assert L.mam_bwd_count_workspace_bytes(1 << 24, 512, 512) == 0                    # fp32 counts no longer exact
+    assert L.mam_bwd_count_workspace_bytes(0, 512, 512) == 0
+    assert L.mam_bwd_splits_f32(one, one, 1, one, one, one, 0, one, 0, one, null, null, 1.0, 8, 64, 8, null, 0, null) == 1
+    assert L.mam_bwd_splits_f32(one, one, 1, one, one, one, 2, one, 7, one, null, null, 1.0, 8, 64, 8, null, 0, null) == 1
+    # dropout: rate outside [0, 1) is refused
+    assert L.mam_drop_f32(one, one, 16, 1.0, 1.0, 5, null) == 1
+    assert L.mam_drop_f32(one, one, 16, -0.1, 1.0, 5, null) == 1
+    assert L.mam_drop_f32(null, one, 16, 0.5, 1.0, 5, null) == 1
+    assert L.mam_drop_f32(one, one, 0, 0.5, 1.0, 5, null) == 1
+    # splits with indices: slice width must be a positive multiple of 32 below K
+    args = (one, one, null, null, 0, 1.0, 0.0, one, one, one, 64, 256, 64)
+    assert L.mam_fwd_splits_idx_f32(*args, 0, null) == 1
+    assert L.mam_fwd_splits_idx_f32(*args, 48, null) == 2
+    assert L.mam_fwd_splits_idx_f32(*args, 256, null) == 2
+    assert L.mam_fwd_splits_idx_f32(one, one, null, null, 0, 1.0, 0.0, one, null, one, 64, 256, 64, 64, null) == 1
+    # tuning knobs live in their own header and reject unknown knobs and values
+    assert L.mam_tune_set(3, 9) == 1 and L.mam_tune_set(7, 0) == 1 and L.mam_tune_set(3, 0) == 0
+    assert L.mam_fwd_variant_name(1, 0).decode().startswith("idx_") and L.mam_fwd_variant_name(1, -1) == b"auto"
+
+
+def test_overlapped_grad_sync_is_inert_without_gradients():
+    from mamtorch_b200.dist import OverlappedGradSync
+
+    p = torch.nn.Parameter(torch.zeros(3))
+    frozen = torch.nn.Parameter(torch.zeros(3), requires_grad=False)
+    sync = OverlappedGradSync([p, frozen], deferred=True)
+    assert len(sync._handles) == 1            # only parameters that can receive a gradient get a hook
+    sync.enabled = False
+    (p * 2).sum().backward()                  # hook fires, disabled: nothing noted, no process group needed
+    sync.finish()
+    assert torch.equal(p.grad, torch.full((3,), 2.0))
+    sync.remove()
