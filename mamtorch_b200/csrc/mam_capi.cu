@@ -199,22 +199,22 @@ using ValCfg7 = FwdCfg<4, 4, 8, 2, 6, false, 4, false>;         // 128x64 tile, 
 using SplitCfg = FwdCfg<4, 8, 4, 2, 4, false, 2, false, true, true>;   // 64x128 tile, slices of K summed in the kernel
 using SplitIdxCfg = FwdCfg<4, 8, 4, 2, 4, true, 2, false, true, true>;  // the same with chunk ids per slice
 using IdxCfg0 = FwdCfg<4, 8, 4, 2, 4, true, 1, false, true, false, true>;   // as IdxCfg2 with the paired-warp row mapping
-using IdxCfg1 = FwdCfg<4, 8, 4, 2, 4, true, 2, false>;          // 64x128 tile, 256 threads
+using IdxCfg1 = FwdCfg<4, 8, 4, 2, 4, true, 2, false, true, false, true>;   // as IdxCfg0, k loop unrolled twice
 using IdxCfg2 = FwdCfg<4, 8, 4, 2, 4, true, 1, false>;
 using IdxCfg3 = FwdCfg<4, 4, 4, 4, 4, true, 1, false>;          // 64x128 tile, 512 threads
-using IdxCfg4 = FwdCfg<8, 4, 2, 4, 4, true, 2, false, false>;   // A-heavy, scalar multiplies
+using IdxCfg4 = FwdCfg<8, 4, 2, 4, 4, true, 1, false, true, false, true>;   // 8x4 outputs per thread, paired-warp rows
 using IdxCfg5 = FwdCfg<8, 4, 2, 4, 4, true, 2, false>;          // 64x128 tile, 256 threads, A-heavy
 using IdxCfg6 = FwdCfg<4, 4, 4, 4, 4, true, 4, false>;          // 64x128 tile, 512 threads
-using IdxCfg7 = FwdCfg<4, 4, 4, 4, 4, true, 2, false>;          // 64x128 tile, 512 threads
+using IdxCfg7 = FwdCfg<4, 4, 4, 4, 4, true, 1, false, true, false, true>;   // 64x128 tile, 512 threads, paired-warp rows
 constexpr int N_VARIANTS = 8;
 const char* kValNames[N_VARIANTS] = {"val_8x8_t128x128_c256_u1_scalar", "val_8x8_t128x128_c256_u2",
                                      "val_8x8_t128x128_c256_u1", "val_4x8_t96x128_c384_u2", "val_4x8_t64x192_c384_u2",
                                      "val_4x8_t64x128_c256_u2_scalar", "val_4x8_t64x128_c256_u2b",
                                      "val_4x4_t128x64_c512_u4"};
-const char* kIdxNames[N_VARIANTS] = {"idx_4x8_t64x128_c256_u1_row8", "idx_4x8_t64x128_c256_u2",
+const char* kIdxNames[N_VARIANTS] = {"idx_4x8_t64x128_c256_u1_row8", "idx_4x8_t64x128_c256_u2_row8",
                                      "idx_4x8_t64x128_c256_u1", "idx_4x4_t64x128_c512_u1",
-                                     "idx_8x4_t64x128_c256_u2_scalar", "idx_8x4_t64x128_c256_u2",
-                                     "idx_4x4_t64x128_c512_u4", "idx_4x4_t64x128_c512_u2"};
+                                     "idx_8x4_t64x128_c256_u1_row8", "idx_8x4_t64x128_c256_u2",
+                                     "idx_4x4_t64x128_c512_u4", "idx_4x4_t64x128_c512_u1_row8"};
 int g_variant[2] = {-1, -1};  // [with_indices]
 int g_resolve_simple = 0;      // 1: use the thread-per-output resolver (cross-check)
 
@@ -251,7 +251,7 @@ int auto_variant(bool want_idx, int64_t M, int64_t N, const DevInfo& d) {
     // Candidates differ in speed per unit (measured, units/clk/SM) and in how well their tile
     // count fills whole waves of SMs; pick the best product of the two.
     struct Cand { int variant; long long bm, bn; double rate; };
-    const Cand cands[3] = {{2, 128, 128, 42.9}, {3, 96, 128, 40.0}, {6, 64, 128, 39.3}};
+    const Cand cands[3] = {{2, 128, 128, 42.9}, {3, 96, 128, 40.4}, {6, 64, 128, 41.0}};
     double best = -1.0;
     int variant = 2;
     for (const Cand& c : cands) {
