@@ -783,7 +783,8 @@ def run_reference_cuda(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=None,
+                    help="timed steps (default: 100 for this library, close to a second of device time; 20 for the CPU arms)")
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference", "reference_cuda"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -808,6 +809,8 @@ def main():
     ap.add_argument("--variant", type=int, default=-1, help="--case: tile configuration of the tiled forward")
     ap.add_argument("--dense-split", type=int, default=1, choices=[0, 1], help="--case dense_tf32: slice the last wave")
     args = ap.parse_args()
+    if args.steps is None:
+        args.steps = 100 if args.impl == "b200" and args.workload == "vit_mlp" else 20
     if args.case:
         return run_case(args)
     if args.workload == "sharded_sparse" and args.impl == "b200":
