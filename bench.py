@@ -956,6 +956,24 @@ def main():
         other_ms[name] = sum(per_launch) / extra_steps if per_launch else 0.0
     e2e_ms = D.timed(lambda: run_from_host(args.steps), 1)
     clocks = sampler.stop() if rank == 0 else None
+    # N > 1: what every rank's own GPU needs for the same step with the gradient exchange switched off, so that
+    # the distance between N ranks and one splits into "the slowest of N GPUs" and "the exchange"
+    no_sync_ranks = None
+    if sync is not None:
+        sync.enabled = False
+        own_steps = max(3, min(args.steps, 20))
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        D.barrier()
+        e0.record()
+        for _ in range(own_steps):
+            step(x_dev, gy_dev)
+        e1.record()
+        D.barrier()
+        sync.enabled = True
+        mine = torch.tensor([e0.elapsed_time(e1) / own_steps], device=dev)
+        every = [torch.empty_like(mine) for _ in range(world)]
+        D.dist.all_gather(every, mine)
+        no_sync_ranks = [round(float(t.item()), 4) for t in every]
     _lib.check(L.mam_check_device_flag(), "device wait flag")
 
     props = torch.cuda.get_device_properties(dev)
@@ -1014,6 +1032,8 @@ def main():
             "gpu_launches": 10 * args.steps, "clocks": clocks, "roofline": roofline}
     if grad_sum_check is not None:
         line["allreduced_dw_check"] = grad_sum_check
+    if no_sync_ranks is not None:
+        line["ms_per_step_without_exchange_by_rank"] = no_sync_ranks
     # per-step time of every kernel class and, for the two HBM-style kernels, algorithmic bytes over time
     # against the measured copy bandwidth (both layers: M x 768 x 3072 and M x 3072 x 768)
     hbm_peak = measured_hbm_gbs()
