@@ -94,6 +94,31 @@ def test_ties_zeros_and_signs(variant, cuda):
     _check_forward(a.numpy(), np.ascontiguousarray(w.numpy().T), y_ref, imax_ref, imin_ref, cuda, variant, capi.NK)
 
 
+RESOLVER_SHAPES = [(300, 260, 200), (65, 4, 63), (129, 2080, 131), (257, 96, 129), (520, 2500, 140), (64, 2048, 64),
+                   (1, 64, 1), (200, 416, 136)]
+
+
+@pytest.mark.parametrize("form", [0, 1])   # tiled, thread per output
+@pytest.mark.parametrize("shape", RESOLVER_SHAPES)
+def test_resolver_forms(shape, form, cuda):
+    """Both forms of the chunk-id -> index step, forced whatever the shape, against the C oracle; half of the
+    operands are small integers so that ties inside and across chunks are decided by the lowest-k rule."""
+    from mamtorch_b200 import _lib
+
+    M, K, N = shape
+    g = torch.Generator().manual_seed(M * 5 + K * 11 + N)
+    a = torch.randn(M, K, generator=g)
+    w = torch.randn(N, K, generator=g) * K ** -0.5
+    a[: M // 2] = torch.randint(-2, 3, (M // 2, K), generator=g).float()
+    w[: N // 2] = torch.randint(-2, 3, (N // 2, K), generator=g).float()
+    y_ref, imax_ref, imin_ref = c_oracle.forward(a.numpy(), w.numpy(), b_is_nk=True)
+    _lib.check(_lib.lib().mam_tune_set(2, form), "resolver form")
+    try:
+        _check_forward(a.numpy(), np.ascontiguousarray(w.numpy().T), y_ref, imax_ref, imin_ref, cuda, 0, capi.NK)
+    finally:
+        _lib.lib().mam_tune_set(2, 0)
+
+
 def test_unaligned_views_take_the_any_shape_path(cuda):
     """Pointers that are not 16-byte aligned cannot be described to TMA; the call must still work."""
     g = torch.Generator().manual_seed(5)
