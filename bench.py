@@ -116,9 +116,10 @@ class ClockSampler:
                 "samples": len(sm), "reasons": reasons}
 
 
-def bind_to_gpu_numa_node(local: int) -> None:
+def bind_to_gpu_numa_node(local: int):
     """Best effort: run this rank's host threads (and so first-touch its pinned buffers) on the NUMA
-    node its GPU hangs off, so that eight ranks do not pull their host copies through one node."""
+    node its GPU hangs off, so that eight ranks do not pull their host copies through one node.  Returns the
+    node it bound to, or None where the system does not say (or nothing was done)."""
     try:
         import torch
 
@@ -128,7 +129,7 @@ def bind_to_gpu_numa_node(local: int) -> None:
         path = f"/sys/bus/pci/devices/{dom:04x}:{bus:02x}:{dev:02x}.0/numa_node"
         node = int(open(path).read().strip())
         if node < 0:
-            return
+            return None
         cpus = set()
         for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
             lo, _, hi = part.partition("-")
@@ -136,8 +137,10 @@ def bind_to_gpu_numa_node(local: int) -> None:
         allowed = cpus & os.sched_getaffinity(0)
         if allowed:
             os.sched_setaffinity(0, allowed)
+            return node
     except (OSError, ValueError, AttributeError, RuntimeError):
         pass
+    return None
 
 
 # ------------------------------------------------------------------------------------------------
@@ -288,8 +291,9 @@ class Dist:
             raise SystemExit("bench.py needs a CUDA device: there is no CPU path")
         torch.cuda.set_device(self.local)
         self.dev = torch.device("cuda", self.local)
+        self.numa_node = None
         if self.world > 1:     # (a single rank keeps every core: it also times the CPU path)
-            bind_to_gpu_numa_node(self.local)
+            self.numa_node = bind_to_gpu_numa_node(self.local)
         if self.world > 1:
             os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
             dist.init_process_group("nccl", device_id=self.dev)
@@ -956,6 +960,24 @@ def main():
         other_ms[name] = sum(per_launch) / extra_steps if per_launch else 0.0
     e2e_ms = D.timed(lambda: run_from_host(args.steps), 1)
     clocks = sampler.stop() if rank == 0 else None
+    # N > 1: the e2e leg's copies alone, all ranks at once (both directions together, nothing else running): the
+    # floor the host side puts under the e2e step time at this N
+    copies_alone_ms = None
+    if world > 1:
+        def copies_only():
+            main_stream = torch.cuda.current_stream()
+            up_stream.wait_stream(main_stream)
+            down_stream.wait_stream(main_stream)
+            with torch.cuda.stream(up_stream):
+                x_buf[0].copy_(x_host, non_blocking=True)
+                gy_buf[0].copy_(gy_host, non_blocking=True)
+            with torch.cuda.stream(down_stream):
+                y_host.copy_(y_buf[0], non_blocking=True)
+            main_stream.wait_stream(up_stream)
+            main_stream.wait_stream(down_stream)
+
+        copies_only()
+        copies_alone_ms = D.timed(copies_only, 10) / 10
     # N > 1: what every rank's own GPU needs for the same step with the gradient exchange switched off, so that
     # the distance between N ranks and one splits into "the slowest of N GPUs" and "the exchange"
     no_sync_ranks = None
@@ -1034,6 +1056,11 @@ def main():
         line["allreduced_dw_check"] = grad_sum_check
     if no_sync_ranks is not None:
         line["ms_per_step_without_exchange_by_rank"] = no_sync_ranks
+    if copies_alone_ms is not None:
+        line["e2e"]["copies_alone_ms_per_step"] = copies_alone_ms
+        line["e2e"]["rank0_bound_to_numa_node"] = D.numa_node
+        line["e2e"]["copies_alone_note"] = ("this step's host->device and device->host copies with no kernel running, all "
+                                            "ranks at once, max over ranks: what the host side allows at this N")
     # per-step time of every kernel class and, for the two HBM-style kernels, algorithmic bytes over time
     # against the measured copy bandwidth (both layers: M x 768 x 3072 and M x 3072 x 768)
     hbm_peak = measured_hbm_gbs()
