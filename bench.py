@@ -117,19 +117,19 @@ class ClockSampler:
 
 
 def bind_to_gpu_numa_node(local: int):
-    """Best effort: run this rank's host threads (and so first-touch its pinned buffers) on the NUMA
-    node its GPU hangs off, so that eight ranks do not pull their host copies through one node.  Returns the
-    node it bound to, or None where the system does not say (or nothing was done)."""
+    """Best effort: run this rank's host threads on the NUMA node its GPU hangs off and ask the kernel to place
+    this process's memory there (the pinned buffers are allocated afterwards), so that eight ranks do not pull
+    their host copies through one node or across the socket link.  Returns what was done:
+    {"gpu_node", "cpus_bound", "memory_preferred"}, or None where the system does not name a node."""
     try:
         import torch
 
-        bus = torch.cuda.get_device_properties(local).pci_bus_id
-        dom = torch.cuda.get_device_properties(local).pci_domain_id
-        dev = torch.cuda.get_device_properties(local).pci_device_id
-        path = f"/sys/bus/pci/devices/{dom:04x}:{bus:02x}:{dev:02x}.0/numa_node"
+        props = torch.cuda.get_device_properties(local)
+        path = f"/sys/bus/pci/devices/{props.pci_domain_id:04x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0/numa_node"
         node = int(open(path).read().strip())
         if node < 0:
             return None
+        done = {"gpu_node": node, "cpus_bound": False, "memory_preferred": False}
         cpus = set()
         for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
             lo, _, hi = part.partition("-")
@@ -137,10 +137,15 @@ def bind_to_gpu_numa_node(local: int):
         allowed = cpus & os.sched_getaffinity(0)
         if allowed:
             os.sched_setaffinity(0, allowed)
-            return node
+            done["cpus_bound"] = True
+        if node < 63 and sys.platform.startswith("linux") and os.uname().machine == "x86_64":
+            # set_mempolicy(MPOL_PREFERRED, {node}): also helps where this rank's cores are all on another node
+            mask = ctypes.c_ulong(1 << node)
+            rc = ctypes.CDLL(None, use_errno=True).syscall(238, 1, ctypes.byref(mask), ctypes.c_ulong(64))
+            done["memory_preferred"] = rc == 0
+        return done
     except (OSError, ValueError, AttributeError, RuntimeError):
-        pass
-    return None
+        return None
 
 
 # ------------------------------------------------------------------------------------------------
@@ -793,10 +798,14 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference", "reference_cuda"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-other-configs", action="store_true", help="headline workload only")
-    ap.add_argument("--grad-sync", default="hooks", choices=["hooks", "deferred", "serial"],
+    ap.add_argument("--grad-sync", default="hooks", choices=["hooks", "deferred", "serial", "bucket"],
                     help="N > 1: all-reduce each weight gradient from its hook while the backward runs on (hooks, "
                          "default: measured best), all of them asynchronously right after the backward, under the "
-                         "selection-count kernels (deferred), or after the whole step (serial)")
+                         "selection-count kernels (deferred), after the whole step (serial), or all gradients packed "
+                         "into one flat buffer and one all-reduce after the step (bucket)")
+    ap.add_argument("--e2e-no-exchange", action="store_true",
+                    help="N > 1, diagnosis only: run the e2e leg with the gradient exchange off (its number is then not "
+                         "the workload's)")
     ap.add_argument("--fwd-variant", type=int, default=-1, help="tile configuration of the index-producing forward")
     ap.add_argument("--workload", default="vit_mlp", choices=["vit_mlp", "sharded_sparse"],
                     help="vit_mlp: the headline configuration (default); sharded_sparse: the large pruned layer, "
@@ -829,7 +838,7 @@ def main():
 
     import mamtorch_b200 as mamtorch
     from mamtorch_b200 import _lib
-    from mamtorch_b200.dist import OverlappedGradSync
+    from mamtorch_b200.dist import OverlappedGradSync, allreduce_gradients
 
     D = Dist(args)
     rank, world, local, dev = D.rank, D.world, D.local, D.dev
@@ -857,7 +866,20 @@ def main():
     params = [fc1.weight, fc2.weight, fc1.bias, fc2.bias]
     # N > 1: every parameter's gradient is all-reduced in place from a hook that fires as soon as autograd has
     # accumulated it, on NCCL's own stream; finish() makes the compute stream wait for the collectives
-    sync = OverlappedGradSync(params, deferred=args.grad_sync != "hooks") if world > 1 else None
+    class BucketSync:
+        """The plain alternative: after the step, all gradients packed into one flat buffer, one all-reduce."""
+        enabled = True
+
+        def start(self):
+            pass
+
+        def finish(self):
+            if self.enabled:
+                allreduce_gradients(params, bucket_bytes=1 << 30)
+
+    sync = None
+    if world > 1:
+        sync = BucketSync() if args.grad_sync == "bucket" else OverlappedGradSync(params, deferred=args.grad_sync != "hooks")
 
     def step(x, gy):
         for p in params:
@@ -892,18 +914,19 @@ def main():
 
     # End-to-end leg: every step's activations and upstream gradient start in pinned host memory and
     # its output and loss end there.  Copies run on their own streams -- one per direction, the link is full
-    # duplex -- double-buffered, so the upload of step i+1 and the download of step i overlap the kernels of
-    # the neighbouring step and each other: what a data loader feeding this layer does.  All of it is inside
-    # the timed region.
+    # duplex -- into three rotating sets of device buffers, so the uploads of steps i+1 and i+2 and the download
+    # of step i-1 overlap the kernels of step i and each other: what a data loader feeding this layer does.
+    # All of it is inside the timed region.
     up_stream = torch.cuda.Stream(device=dev)
     down_stream = torch.cuda.Stream(device=dev)
-    x_buf = [torch.empty_like(x_dev) for _ in range(2)]
-    gy_buf = [torch.empty_like(gy_dev) for _ in range(2)]
-    y_buf = [torch.empty(64, 197, D_MODEL, device=dev) for _ in range(2)]
-    loss_buf = [torch.empty((), device=dev) for _ in range(2)]
-    up_done = [torch.cuda.Event() for _ in range(2)]
-    comp_done = [torch.cuda.Event() for _ in range(2)]
-    down_done = [torch.cuda.Event() for _ in range(2)]
+    NBUF = 3   # input / output slots on the device: the upload of step i+2 may start while step i computes
+    x_buf = [torch.empty_like(x_dev) for _ in range(NBUF)]
+    gy_buf = [torch.empty_like(gy_dev) for _ in range(NBUF)]
+    y_buf = [torch.empty(64, 197, D_MODEL, device=dev) for _ in range(NBUF)]
+    loss_buf = [torch.empty((), device=dev) for _ in range(NBUF)]
+    up_done = [torch.cuda.Event() for _ in range(NBUF)]
+    comp_done = [torch.cuda.Event() for _ in range(NBUF)]
+    down_done = [torch.cuda.Event() for _ in range(NBUF)]
 
     def upload(slot):
         with torch.cuda.stream(up_stream):
@@ -912,17 +935,20 @@ def main():
             gy_buf[slot].copy_(gy_host, non_blocking=True)
             up_done[slot].record(up_stream)
 
+    # (no timing events inside this loop: at 8 ranks, with the host's copy rate near its limit, every
+    # timestamped event record in a stream measurably delayed that stream)
     def run_from_host(steps):
         main_stream = torch.cuda.current_stream()
         for ev in comp_done + down_done:
             ev.record(main_stream)
-        upload(0)
+        for j in range(min(NBUF - 1, steps)):
+            upload(j)
         for i in range(steps):
-            slot = i & 1
-            if i + 1 < steps:
-                upload(slot ^ 1)
+            slot = i % NBUF
+            if i + NBUF - 1 < steps:
+                upload((i + NBUF - 1) % NBUF)
             main_stream.wait_event(up_done[slot])
-            main_stream.wait_event(down_done[slot])          # y_buf[slot] of step i-2 has been downloaded
+            main_stream.wait_event(down_done[slot])          # y_buf[slot] of step i-NBUF has been downloaded
             y = step(x_buf[slot], gy_buf[slot])
             y_buf[slot].copy_(y.detach())
             loss_buf[slot].copy_((y.detach() * gy_buf[slot]).sum())
@@ -958,7 +984,11 @@ def main():
             step(x_dev, gy_dev)
         per_launch = timer.collect()
         other_ms[name] = sum(per_launch) / extra_steps if per_launch else 0.0
+    if sync is not None and args.e2e_no_exchange:
+        sync.enabled = False
     e2e_ms = D.timed(lambda: run_from_host(args.steps), 1)
+    if sync is not None:
+        sync.enabled = True
     clocks = sampler.stop() if rank == 0 else None
     # N > 1: the e2e leg's copies alone, all ranks at once (both directions together, nothing else running): the
     # floor the host side puts under the e2e step time at this N
@@ -978,6 +1008,8 @@ def main():
 
         copies_only()
         copies_alone_ms = D.timed(copies_only, 10) / 10
+        placements = [None] * world
+        D.dist.all_gather_object(placements, D.numa_node)
     # N > 1: what every rank's own GPU needs for the same step with the gradient exchange switched off, so that
     # the distance between N ranks and one splits into "the slowest of N GPUs" and "the exchange"
     no_sync_ranks = None
@@ -1057,8 +1089,10 @@ def main():
     if no_sync_ranks is not None:
         line["ms_per_step_without_exchange_by_rank"] = no_sync_ranks
     if copies_alone_ms is not None:
+        if args.e2e_no_exchange:
+            line["e2e"]["diagnosis_only"] = "gradient exchange off in this leg"
         line["e2e"]["copies_alone_ms_per_step"] = copies_alone_ms
-        line["e2e"]["rank0_bound_to_numa_node"] = D.numa_node
+        line["e2e"]["numa_placement_by_rank"] = placements
         line["e2e"]["copies_alone_note"] = ("this step's host->device and device->host copies with no kernel running, all "
                                             "ranks at once, max over ranks: what the host side allows at this N")
     # per-step time of every kernel class and, for the two HBM-style kernels, algorithmic bytes over time
