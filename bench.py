@@ -301,7 +301,12 @@ class Dist:
             self.numa_node = bind_to_gpu_numa_node(self.local)
         if self.world > 1:
             os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-            dist.init_process_group("nccl", device_id=self.dev)
+            opts = None
+            if os.environ.get("MAM_BENCH_NCCL_PRIORITY", "1") == "1":
+                # the collectives' kernels take the first SM resources that come free instead of queueing
+                # behind the whole grid of whatever compute kernel is running
+                opts = dist.ProcessGroupNCCL.Options(is_high_priority_stream=True)
+            dist.init_process_group("nccl", device_id=self.dev, pg_options=opts)
         self.dist = dist
 
     def barrier(self):
