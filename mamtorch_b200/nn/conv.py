@@ -84,10 +84,13 @@ class _MamConv2d(torch.autograd.Function):
         img = lambda t: t.view(B, Ho, Wo, Fo).permute(0, 3, 1, 2)
         amax, amin = img(amax), img(amin)
         ctx.mark_non_differentiable(amax, amin)
+        ctx.set_materialize_grads(False)   # no zero-filled index "gradients" before every backward call
         return img(y), amax, amin
 
     @staticmethod
     def backward(ctx, gy, _g1, _g2):
+        if gy is None:
+            return (None,) * 9
         x, w2d, amax, amin = ctx.saved_tensors
         B, C, H, W, Fo, kH, kW, sh, sw, ph, pw, Ho, Wo = ctx.geom
         g2d = gy.permute(0, 2, 3, 1).reshape(B * Ho * Wo, Fo).contiguous()

@@ -251,10 +251,15 @@ class _MamLinear(torch.autograd.Function):
         ctx.drop_rate, ctx.drop_seed = drop_rate, drop_seed
         ctx.has_bias, ctx.has_dense = bias is not None, dense is not None
         ctx.mark_non_differentiable(argmax, argmin)
+        # the index outputs get no gradient: without this, autograd fills two [M,N] int32 zero tensors for them
+        # before every backward call
+        ctx.set_materialize_grads(False)
         return y, argmax, argmin
 
     @staticmethod
     def backward(ctx, gy, _g1, _g2):
+        if gy is None:
+            return (None,) * 9
         x, weight, argmax, argmin = ctx.saved_tensors
         gy = gy.contiguous()
         if ctx.drop_rate > 0:

@@ -74,10 +74,13 @@ class _MamLinearCsr(torch.autograd.Function):
         ctx.save_for_backward(x, dense_weight, argmax, argmin)
         ctx.has_bias = bias is not None
         ctx.mark_non_differentiable(argmax, argmin)
+        ctx.set_materialize_grads(False)   # no zero-filled index "gradients" before every backward call
         return y, argmax, argmin
 
     @staticmethod
     def backward(ctx, gy, _a, _b):
+        if gy is None:
+            return (None,) * 6
         x, w, argmax, argmin = ctx.saved_tensors
         gy = gy.contiguous()
         dx, dw = torch.ops.mamtorch_b200.linear_backward(x, w, gy, argmax, argmin, 1.0)
