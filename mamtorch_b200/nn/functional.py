@@ -265,14 +265,14 @@ class _MamLinear(torch.autograd.Function):
         if ctx.drop_rate > 0:
             gy = _ops.drop_apply(gy, ctx.drop_rate, 1.0 / (1.0 - ctx.drop_rate), ctx.drop_seed)
         dx = dw = dbias = ddense = None
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            dbias = gy.sum(0)     # first: the layer above has only just written gy, much of it is still in L2
         if ctx.needs_input_grad[0] or ctx.needs_input_grad[1]:
             if ctx.hit_sink is not None:
                 dx, dw, hmax, hmin = _ops.linear_backward_count(x, weight, gy, argmax, argmin, ctx.alpha)
                 ctx.hit_sink.argmax, ctx.hit_sink.hits = argmax, (hmax, hmin)
             else:
                 dx, dw = _ops.linear_backward(x, weight, gy, argmax, argmin, ctx.alpha)
-        if ctx.has_bias and ctx.needs_input_grad[2]:
-            dbias = gy.sum(0)
         if ctx.has_dense and ctx.needs_input_grad[3]:
             ddense = gy * ctx.beta
         return dx, dw, dbias, ddense, None, None, None, None, None
