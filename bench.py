@@ -607,7 +607,7 @@ def run_case(args):
         torch.cuda.synchronize()
         _lib.check(L.mam_check_device_flag(), "device wait flag")
         print(f"ok conv {args.shape} order {args.order} {'fwd' if args.fwd_only else 'fwd+bwd'} checksum "
-              f"{float(y.double().sum()):.6e} ms_per_rep {e0.elapsed_time(e1) / max(args.reps, 1):.4f} "
+              f"{float(y.detach().double().sum()):.6e} ms_per_rep {e0.elapsed_time(e1) / max(args.reps, 1):.4f} "
               f"peak_alloc_MB {torch.cuda.max_memory_allocated() / 1e6:.0f}")
         return
     M, K, N = (int(v) for v in args.shape.lower().split("x"))

@@ -305,7 +305,8 @@ int run_tiled(const float* a, const float* w, float* y, int32_t* argmax, int32_t
                 default: return launch_tiled<ValCfg2, true>(a, w, prm, d, cs, cv);
             }
         }
-        st = launch_tiled<IdxCfg1, true>(a, w, prm, d, cs, cv);
+        st = g_variant[1] == 1 ? launch_tiled<IdxCfg1, true>(a, w, prm, d, cs, cv)
+                               : launch_tiled<IdxCfg0, true>(a, w, prm, d, cs, cv);
     } else if (!want_idx) {
         switch (variant) {
             case 0: st = launch_tiled<ValCfg0>(a, w, prm, d, cs); break;

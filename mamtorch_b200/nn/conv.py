@@ -93,7 +93,10 @@ class _MamConv2d(torch.autograd.Function):
             return (None,) * 9
         x, w2d, amax, amin = ctx.saved_tensors
         B, C, H, W, Fo, kH, kW, sh, sw, ph, pw, Ho, Wo = ctx.geom
-        g2d = gy.permute(0, 2, 3, 1).reshape(B * Ho * Wo, Fo).contiguous()
+        g_rows = gy.permute(0, 2, 3, 1)
+        if not g_rows.is_contiguous() and gy.is_cuda and gy.dtype == torch.float32:
+            g_rows = _ops.conv_channels_last(gy)   # the library's batched transpose: ~3x torch's strided copy
+        g2d = g_rows.reshape(B * Ho * Wo, Fo).contiguous()
         dx = dw = dbias = ddense = None
         if ctx.needs_input_grad[0] or ctx.needs_input_grad[1]:
             if (_backward_form != "fold" and Fo * C * kH * kW < 2 ** 31
