@@ -432,6 +432,21 @@ at::Tensor conv_channels_last(const at::Tensor& x) {
                  "mam_nchw_to_nhwc_f32");
     return out;
 }
+// A fresh contiguous [C,R] transpose of the matrix a[R,C] (the same batched-transpose kernel, one image of R
+// channels and C pixels); several times faster than a strided torch copy.
+at::Tensor transpose2d(const at::Tensor& a) {
+    TORCH_CHECK(a.is_cuda() && a.scalar_type() == at::kFloat && a.dim() == 2, "a must be a float32 CUDA matrix");
+    auto ac = a.contiguous();
+    const int64_t R = ac.size(0), C = ac.size(1);
+    c10::cuda::CUDAGuard guard(a.device());
+    auto out = at::empty({C, R}, ac.options());
+    if (out.numel() == 0) return out;
+    if (R > 65535LL * 32) return ac.t().contiguous();
+    auto stream = at::cuda::getCurrentCUDAStream();
+    check_status(mam_nchw_to_nhwc_f32(ac.data_ptr<float>(), out.data_ptr<float>(), 1, R, 1, C, stream.stream()),
+                 "mam_nchw_to_nhwc_f32");
+    return out;
+}
 // Whether conv_forward_implicit can take a convolution of this geometry (no device needed).
 bool conv_implicit_applies(int64_t B, int64_t C, int64_t H, int64_t W, int64_t kH, int64_t kW, int64_t sh, int64_t sw,
                            int64_t ph, int64_t pw) {
@@ -822,6 +837,7 @@ TORCH_LIBRARY(mamtorch_b200, m) {
     m.def("linear_forward_splits_idx(Tensor x, Tensor weight, Tensor? bias, Tensor? dense, float alpha, float beta, int split_width) -> Tensor[]");
     m.def("linear_backward_splits(Tensor x, Tensor weight, Tensor grad, Tensor argmax, Tensor argmin, float scale) -> Tensor[]");
     m.def("conv_channels_last(Tensor x) -> Tensor");
+    m.def("transpose2d(Tensor a) -> Tensor");
     m.def("conv_forward_implicit(Tensor x_nhwc, Tensor w_taps, Tensor? bias, Tensor? dense, float alpha, float beta, int kH, int kW, int sh, int sw, int ph, int pw, bool need_indices) -> Tensor[]");
     m.def("conv_implicit_applies(int B, int C, int H, int W, int kH, int kW, int sh, int sw, int ph, int pw) -> bool", &conv_implicit_applies);
     m.def("conv_col2im(Tensor cols_t, int B, int C, int H, int W, int kH, int kW, int sh, int sw, int ph, int pw) -> Tensor");
@@ -848,6 +864,7 @@ TORCH_LIBRARY_IMPL(mamtorch_b200, CUDA, m) {
     m.impl("conv_im2col", &conv_im2col);
     m.impl("conv_forward_implicit", &conv_forward_implicit);
     m.impl("conv_channels_last", &conv_channels_last);
+    m.impl("transpose2d", &transpose2d);
     m.impl("linear_forward_splits", &linear_forward_splits);
     m.impl("linear_forward_splits_idx", &linear_forward_splits_idx);
     m.impl("linear_backward_splits", &linear_backward_splits);

@@ -101,6 +101,11 @@ def _(x):
     return x.new_empty((B, H, W, C))
 
 
+@torch.library.register_fake("mamtorch_b200::transpose2d")
+def _(a):
+    return a.new_empty((a.shape[1], a.shape[0]))
+
+
 @torch.library.register_fake("mamtorch_b200::conv_forward_implicit")
 def _(x_nhwc, w_taps, bias, dense, alpha, beta, kH, kW, sh, sw, ph, pw, need_indices):
     B, H, W, C = x_nhwc.shape
@@ -198,10 +203,11 @@ class _DenseLinear(torch.autograd.Function):
         x, weight = ctx.saved_tensors
         g = g.contiguous()
         dx = dw = None
+        tr = _ops.transpose2d if g.is_cuda and g.dtype == torch.float32 else (lambda t: t.t().contiguous())
         if ctx.needs_input_grad[0]:
-            dx = _ops.dense_nt(g, weight.t().contiguous())          # [M,N] . [K,N]^T
+            dx = _ops.dense_nt(g, tr(weight))          # [M,N] . [K,N]^T
         if ctx.needs_input_grad[1]:
-            dw = _ops.dense_nt(g.t().contiguous(), x.t().contiguous())  # [N,M] . [K,M]^T
+            dw = _ops.dense_nt(tr(g), tr(x))           # [N,M] . [K,M]^T
         return dx, dw
 
 

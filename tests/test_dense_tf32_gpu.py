@@ -99,3 +99,12 @@ def test_unsupported_shapes_are_reported(cuda):
     out = torch.zeros(4, 5, device=cuda)
     p = lambda t: ctypes.c_void_p(t.data_ptr())
     assert _lib.lib().mam_dense_tf32(p(a), p(w), p(out), 1.0, 0.0, 4, 6, 5, None) == 2
+
+
+@pytest.mark.parametrize("shape", [(1, 1), (33, 65), (4096, 768), (257, 1000), (5, 70001)])
+def test_transpose2d_matches_torch(shape, cuda):
+    """The transpose the dense term's gradient products use: bit-identical to torch's strided copy."""
+    a = torch.randn(*shape, device=cuda)
+    out = torch.ops.mamtorch_b200.transpose2d(a)
+    assert out.is_contiguous() and torch.equal(out, a.t().contiguous())
+    assert torch.equal(torch.ops.mamtorch_b200.transpose2d(a.t()), a.contiguous())   # strided input
