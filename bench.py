@@ -954,13 +954,16 @@ def main():
                 upload((i + NBUF - 1) % NBUF)
             main_stream.wait_event(up_done[slot])
             main_stream.wait_event(down_done[slot])          # y_buf[slot] of step i-NBUF has been downloaded
-            y = step(x_buf[slot], gy_buf[slot])
-            y_buf[slot].copy_(y.detach())
-            loss_buf[slot].copy_((y.detach() * gy_buf[slot]).sum())
+            y = step(x_buf[slot], gy_buf[slot]).detach()
+            # the step's metric: <y, gy>, one pass over both, written where the download reads it
+            torch.dot(y.reshape(-1), gy_buf[slot].reshape(-1), out=loss_buf[slot])
+            # y is downloaded from where the forward left it; the reference kept here holds its memory until
+            # this slot's turn comes again, by which time the compute stream has waited for the download
+            y_buf[slot] = y
             comp_done[slot].record(main_stream)
             with torch.cuda.stream(down_stream):
                 down_stream.wait_event(comp_done[slot])
-                y_host.copy_(y_buf[slot], non_blocking=True)
+                y_host.copy_(y_buf[slot].view_as(y_host), non_blocking=True)
                 loss_host.copy_(loss_buf[slot], non_blocking=True)
                 down_done[slot].record(down_stream)
         main_stream.wait_stream(up_stream)
